@@ -1,0 +1,295 @@
+// C ABI of the tree-attention decode engine: argument validation, kernel
+// selection and launches.  Declarations and the mapping to the reference's
+// Python entry points are in include/fasttree_b200.h.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "fasttree_b200.h"
+#include "ft_common.cuh"
+#include "ft_stage1_generic.cuh"
+#include "ft_stage1_mma.cuh"
+#include "ft_stage2.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+std::atomic<int64_t> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define FT_CUDA_OK(expr)                                                                      \
+  do {                                                                                        \
+    cudaError_t e_ = (expr);                                                                  \
+    if (e_ != cudaSuccess) return fail(FT_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
+
+int check_common(const ft_decode_args* a) {
+  if (a == nullptr) return fail(FT_ERR_INVALID_ARGUMENT, "args is NULL");
+  if (a->dtype != FT_F16 && a->dtype != FT_BF16 && a->dtype != FT_F32)
+    return fail(FT_ERR_INVALID_ARGUMENT, "dtype %d is not one of FT_F16/FT_BF16/FT_F32", a->dtype);
+  if (a->batch < 0 || a->num_qo_heads <= 0 || a->num_kv_heads <= 0 || a->head_dim <= 0)
+    return fail(FT_ERR_INVALID_ARGUMENT, "batch/heads/head_dim must be positive (batch %d, hq %d, hkv %d, d %d)",
+                a->batch, a->num_qo_heads, a->num_kv_heads, a->head_dim);
+  if (a->num_qo_heads % a->num_kv_heads != 0)
+    return fail(FT_ERR_INVALID_ARGUMENT, "num_qo_heads %d is not a multiple of num_kv_heads %d", a->num_qo_heads,
+                a->num_kv_heads);
+  // the reference asserts head_dim in {16,32,64,128,256} (kernel_bench/fasttree.py:439)
+  const int d = a->head_dim;
+  if (!(d == 16 || d == 32 || d == 64 || d == 128 || d == 256))
+    return fail(FT_ERR_UNSUPPORTED, "head_dim %d is not one of 16, 32, 64, 128, 256", d);
+  if (a->num_partial_rows < 0) return fail(FT_ERR_INVALID_ARGUMENT, "num_partial_rows is negative");
+  if (a->mid_o == nullptr || a->mid_lse == nullptr)
+    return fail(FT_ERR_INVALID_ARGUMENT, "mid_o / mid_lse scratch is NULL");
+  if (!aligned16(a->mid_o) || a->mid_o_stride0 % 4 != 0 || a->mid_o_stride1 % 4 != 0)
+    return fail(FT_ERR_UNSUPPORTED, "mid_o must be 16-byte aligned with strides that are multiples of 4 floats");
+  return FT_OK;
+}
+
+int check_stage1(const ft_decode_args* a) {
+  if (a->q == nullptr || a->k_buffer == nullptr || a->v_buffer == nullptr)
+    return fail(FT_ERR_INVALID_ARGUMENT, "q / k_buffer / v_buffer is NULL");
+  if (a->kv_rows <= 0) return fail(FT_ERR_INVALID_ARGUMENT, "kv_rows must be positive");
+  for (int ph = 0; ph < 2; ++ph)
+    if (a->phase_node_nums[ph] < 0 || a->phase_node_offsets[ph] < 0)
+      return fail(FT_ERR_INVALID_ARGUMENT, "phase %d: negative vnode count or offset", ph);
+  if (a->phase_node_nums[0] + a->phase_node_nums[1] > 0) {
+    if (!a->vnode_to_kv_entries || !a->vnode_to_kv_offs || !a->vnode_to_kv_lens || !a->vnode_to_q_entries ||
+        !a->vnode_to_q_offs || !a->vnode_to_q_lens)
+      return fail(FT_ERR_INVALID_ARGUMENT, "a vnode table pointer is NULL");
+    if (a->kv_entries_len <= 0) return fail(FT_ERR_INVALID_ARGUMENT, "kv_entries_len must be positive");
+  }
+  if (a->num_kv_heads > 65535) return fail(FT_ERR_UNSUPPORTED, "more than 65535 kv heads");
+  return FT_OK;
+}
+
+// Can the warp-MMA kernel take these arguments?  Returns a reason or NULL.
+const char* mma_obstacle(const ft_decode_args* a) {
+  if (a->dtype == FT_F32) return "fp32 inputs";
+  if (a->head_dim != 64 && a->head_dim != 128) return "head_dim not 64 or 128";
+  if (!aligned16(a->q) || !aligned16(a->k_buffer) || !aligned16(a->v_buffer)) return "q/k/v not 16-byte aligned";
+  if (a->q_stride0 % 8 || a->q_stride1 % 8 || a->k_stride0 % 8 || a->k_stride1 % 8 || a->v_stride0 % 8 ||
+      a->v_stride1 % 8)
+    return "a q/k/v stride is not a multiple of 8 elements";
+  return nullptr;
+}
+
+int pick_path(const ft_decode_args* a) {
+  if (a->path == FT_PATH_GENERIC) return FT_PATH_GENERIC;
+  const char* why = mma_obstacle(a);
+  if (a->path == FT_PATH_MMA || a->path == FT_PATH_TCGEN05) {
+    if (why != nullptr) return fail(FT_ERR_UNSUPPORTED, "tensor-core path unavailable: %s", why);
+    return FT_PATH_MMA;
+  }
+  if (a->path != FT_PATH_AUTO) return fail(FT_ERR_INVALID_ARGUMENT, "unknown path %d", a->path);
+  return why == nullptr ? FT_PATH_MMA : FT_PATH_GENERIC;
+}
+
+ft::Stage1Params stage1_params(const ft_decode_args* a) {
+  ft::Stage1Params p;
+  p.q = a->q;
+  p.k = a->k_buffer;
+  p.v = a->v_buffer;
+  p.kv_entries = a->vnode_to_kv_entries;
+  p.kv_offs = a->vnode_to_kv_offs;
+  p.kv_lens = a->vnode_to_kv_lens;
+  p.q_entries = a->vnode_to_q_entries;
+  p.q_offs = a->vnode_to_q_offs;
+  p.q_lens = a->vnode_to_q_lens;
+  p.mid_o = a->mid_o;
+  p.mid_lse = a->mid_lse;
+  p.q_s0 = a->q_stride0;
+  p.q_s1 = a->q_stride1;
+  p.k_s0 = a->k_stride0;
+  p.k_s1 = a->k_stride1;
+  p.v_s0 = a->v_stride0;
+  p.v_s1 = a->v_stride1;
+  p.mo_s0 = a->mid_o_stride0;
+  p.mo_s1 = a->mid_o_stride1;
+  p.ml_s0 = a->mid_lse_stride0;
+  p.kv_rows = a->kv_rows;
+  p.kv_entries_len = a->kv_entries_len;
+  p.num_partial_rows = a->num_partial_rows;
+  p.batch = a->batch;
+  p.group = a->num_qo_heads / a->num_kv_heads;
+  p.head_dim = a->head_dim;
+  p.node_offset = 0;
+  p.node_count = 0;
+  p.sm_scale = a->sm_scale;
+  return p;
+}
+
+template <typename T, int D>
+int launch_mma(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
+  using C = ft::MmaCfg<D>;
+  static bool configured[64] = {};
+  int dev = 0;
+  FT_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    FT_CUDA_OK(cudaFuncSetAttribute(ft::stage1_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    C::SMEM_BYTES));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  dim3 grid(p.node_count, hkv);
+  ft::stage1_mma_kernel<T, D><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(p);
+  FT_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FT_OK;
+}
+
+template <typename T>
+int launch_generic(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
+  dim3 grid(p.node_count, hkv);
+  ft::stage1_generic_kernel<T><<<grid, 128, 0, st>>>(p);
+  FT_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FT_OK;
+}
+
+int launch_stage1_range(const ft_decode_args* a, int path, int offset, int count) {
+  if (count <= 0) return FT_OK;
+  ft::Stage1Params p = stage1_params(a);
+  p.node_offset = offset;
+  p.node_count = count;
+  cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+  const int hkv = a->num_kv_heads;
+  if (path == FT_PATH_MMA) {
+    if (a->dtype == FT_F16)
+      return a->head_dim == 128 ? launch_mma<__half, 128>(p, hkv, st) : launch_mma<__half, 64>(p, hkv, st);
+    return a->head_dim == 128 ? launch_mma<__nv_bfloat16, 128>(p, hkv, st) : launch_mma<__nv_bfloat16, 64>(p, hkv, st);
+  }
+  switch (a->dtype) {
+    case FT_F16: return launch_generic<__half>(p, hkv, st);
+    case FT_BF16: return launch_generic<__nv_bfloat16>(p, hkv, st);
+    default: return launch_generic<float>(p, hkv, st);
+  }
+}
+
+template <typename T>
+int launch_stage2(const ft::Stage2Params& p, cudaStream_t st) {
+  const int64_t pairs = (int64_t)p.batch * p.heads;
+  if (pairs == 0) return FT_OK;
+  const int64_t blocks = (pairs + 3) / 4;
+  if (blocks > 0x7fffffffLL) return fail(FT_ERR_TOO_LARGE, "batch x heads too large for one launch");
+  ft::stage2_merge_kernel<T><<<(unsigned)blocks, 128, 0, st>>>(p);
+  FT_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FT_OK;
+}
+
+__global__ void bump_kv_lens_kernel(int32_t* kv_lens, const int32_t* last, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const int v = last[i];
+    if (v >= 0) atomicAdd(kv_lens + v, 1);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int ft_version(void) { return 100; }
+
+int ft_decode_args_size(void) { return static_cast<int>(sizeof(ft_decode_args)); }
+
+const char* ft_last_error(void) { return g_err; }
+
+int64_t ft_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* ft_stage1_path_name(const ft_decode_args* args) {
+  int rc = check_common(args);
+  if (rc != FT_OK) return nullptr;
+  const int path = pick_path(args);
+  if (path < 0) return nullptr;
+  return path == FT_PATH_MMA ? "mma" : "generic";
+}
+
+int ft_stage1(const ft_decode_args* a) {
+  int rc = check_common(a);
+  if (rc != FT_OK) return rc;
+  rc = check_stage1(a);
+  if (rc != FT_OK) return rc;
+  const int path = pick_path(a);
+  if (path < 0) return path;
+  const int n0 = a->phase_node_nums[0], n1 = a->phase_node_nums[1];
+  const int o0 = a->phase_node_offsets[0], o1 = a->phase_node_offsets[1];
+  // The kernels size themselves from each vnode's q_len, so two adjacent phases go out as one grid.
+  if (n0 > 0 && n1 > 0 && o1 == o0 + n0) return launch_stage1_range(a, path, o0, n0 + n1);
+  rc = launch_stage1_range(a, path, o0, n0);
+  if (rc != FT_OK) return rc;
+  return launch_stage1_range(a, path, o1, n1);
+}
+
+int ft_stage2(const ft_decode_args* a) {
+  int rc = check_common(a);
+  if (rc != FT_OK) return rc;
+  if (a->o == nullptr) return fail(FT_ERR_INVALID_ARGUMENT, "o is NULL");
+  if (a->batch > 0 && (!a->req_to_vnode_entries || !a->req_to_vnode_offs || !a->req_to_vnode_lens))
+    return fail(FT_ERR_INVALID_ARGUMENT, "a request table pointer is NULL");
+  ft::Stage2Params p;
+  p.r2v_entries = a->req_to_vnode_entries;
+  p.r2v_offs = a->req_to_vnode_offs;
+  p.r2v_lens = a->req_to_vnode_lens;
+  p.mid_o = a->mid_o;
+  p.mid_lse = a->mid_lse;
+  p.o = a->o;
+  p.o_lse = a->o_lse;
+  p.mo_s0 = a->mid_o_stride0;
+  p.mo_s1 = a->mid_o_stride1;
+  p.ml_s0 = a->mid_lse_stride0;
+  p.o_s0 = a->o_stride0;
+  p.o_s1 = a->o_stride1;
+  p.num_partial_rows = a->num_partial_rows;
+  p.batch = a->batch;
+  p.heads = a->num_qo_heads;
+  p.head_dim = a->head_dim;
+  cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+  switch (a->dtype) {
+    case FT_F16: return launch_stage2<__half>(p, st);
+    case FT_BF16: return launch_stage2<__nv_bfloat16>(p, st);
+    default: return launch_stage2<float>(p, st);
+  }
+}
+
+int ft_decode(const ft_decode_args* a) {
+  int rc = ft_stage1(a);
+  if (rc != FT_OK) return rc;
+  return ft_stage2(a);
+}
+
+int ft_bump_kv_lens(int32_t* vnode_to_kv_lens, const int32_t* last_vnodes, int32_t n, void* stream) {
+  if (n < 0) return fail(FT_ERR_INVALID_ARGUMENT, "n is negative");
+  if (n == 0) return FT_OK;
+  if (vnode_to_kv_lens == nullptr || last_vnodes == nullptr)
+    return fail(FT_ERR_INVALID_ARGUMENT, "vnode_to_kv_lens / last_vnodes is NULL");
+  bump_kv_lens_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(vnode_to_kv_lens, last_vnodes, n);
+  FT_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FT_OK;
+}
+
+int ft_read_device_status(void* stream, int32_t* flags) {
+  if (flags == nullptr) return fail(FT_ERR_INVALID_ARGUMENT, "flags is NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  FT_CUDA_OK(cudaStreamSynchronize(st));
+  int host = 0;
+  FT_CUDA_OK(cudaMemcpyFromSymbol(&host, ft::g_device_status, sizeof(int)));
+  if (host != 0) {
+    const int zero = 0;
+    FT_CUDA_OK(cudaMemcpyToSymbol(ft::g_device_status, &zero, sizeof(int)));
+  }
+  *flags = host;
+  return FT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,87 @@
+// Shared device-side definitions of the tree-attention decode kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "fasttree_b200.h"
+
+namespace ft {
+
+// One word per device; kernels OR error bits into it instead of faulting.
+__device__ int g_device_status = 0;
+
+__device__ __forceinline__ void flag_error(int bit) { atomicOr(&g_device_status, bit); }
+
+// Everything a stage-1 kernel needs, passed by value.
+struct Stage1Params {
+  const void* q;
+  const void* k;
+  const void* v;
+  const int32_t* kv_entries;
+  const int32_t* kv_offs;
+  const int32_t* kv_lens;
+  const int32_t* q_entries;
+  const int32_t* q_offs;
+  const int32_t* q_lens;
+  float* mid_o;
+  float* mid_lse;
+  int64_t q_s0, q_s1, k_s0, k_s1, v_s0, v_s1, mo_s0, mo_s1, ml_s0;
+  int64_t kv_rows;
+  int64_t kv_entries_len;
+  int64_t num_partial_rows;
+  int32_t batch;
+  int32_t group;        // query heads per KV head
+  int32_t head_dim;
+  int32_t node_offset;  // first vnode of this launch
+  int32_t node_count;   // vnodes in this launch
+  float sm_scale;
+};
+
+struct Stage2Params {
+  const int32_t* r2v_entries;
+  const int32_t* r2v_offs;
+  const int32_t* r2v_lens;
+  const float* mid_o;
+  const float* mid_lse;
+  void* o;
+  float* o_lse;
+  int64_t mo_s0, mo_s1, ml_s0, o_s0, o_s1;
+  int64_t num_partial_rows;
+  int32_t batch;
+  int32_t heads;
+  int32_t head_dim;
+};
+
+template <typename T>
+__device__ __forceinline__ float to_float(T x);
+template <>
+__device__ __forceinline__ float to_float<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float to_float<__half>(__half x) { return __half2float(x); }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float x);
+template <>
+__device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_max(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+  return x;
+}
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
+}  // namespace ft

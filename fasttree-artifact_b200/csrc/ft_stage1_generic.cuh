@@ -1,0 +1,120 @@
+// Stage 1, scalar fp32 kernel: any storage type, any head_dim <= 256.
+//
+// One CTA per (vnode, kv head), as in the reference launch grid
+// (kernel_bench/fasttree.py:448-451).  Each warp owns one packed query row
+// (request slot x group member) at a time, lanes span the head dimension, and
+// the KV chunk is walked four tokens per step with a warp-shuffle online
+// softmax.  It is the correctness path for fp32 inputs and unusual head sizes;
+// the 16-bit / head_dim 64,128 cases go to the tensor-core kernels.
+#pragma once
+
+#include "ft_common.cuh"
+
+namespace ft {
+
+template <typename T>
+__global__ void __launch_bounds__(128) stage1_generic_kernel(Stage1Params p) {
+  constexpr int MAXJ = 8;  // 8 x 32 lanes = head_dim up to 256
+  constexpr int TB = 4;    // tokens per step
+  const int vn = blockIdx.x + p.node_offset;
+  const int kvh = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_off = p.q_offs[vn], q_len = p.q_lens[vn];
+  const int kv_off = p.kv_offs[vn], kv_len = p.kv_lens[vn];
+  const int G = p.group, D = p.head_dim;
+  const int rows = q_len * G;
+  const T* __restrict__ kbase = reinterpret_cast<const T*>(p.k) + (int64_t)kvh * p.k_s1;
+  const T* __restrict__ vbase = reinterpret_cast<const T*>(p.v) + (int64_t)kvh * p.v_s1;
+
+  for (int row = warp; row < rows; row += 4) {
+    const int slot = row / G, g = row - slot * G;
+    const int64_t prow = (int64_t)q_off + slot;
+    if (prow < 0 || prow >= p.num_partial_rows) {
+      if (lane == 0) flag_error(FT_DEV_BAD_ROW_INDEX);
+      continue;
+    }
+    const int req = p.q_entries[prow];
+    if (req < 0 || req >= p.batch) {
+      if (lane == 0) flag_error(FT_DEV_BAD_Q_INDEX);
+      continue;
+    }
+    const int head = kvh * G + g;
+    const T* __restrict__ qp = reinterpret_cast<const T*>(p.q) + (int64_t)req * p.q_s0 + (int64_t)head * p.q_s1;
+    float qreg[MAXJ], acc[MAXJ];
+#pragma unroll
+    for (int j = 0; j < MAXJ; ++j) {
+      const int d = lane + 32 * j;
+      qreg[j] = d < D ? to_float<T>(qp[d]) : 0.f;
+      acc[j] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+    for (int t0 = 0; t0 < kv_len; t0 += TB) {
+      int64_t rowid[TB];
+      float s[TB];
+#pragma unroll
+      for (int u = 0; u < TB; ++u) {
+        const int64_t e = (int64_t)kv_off + t0 + u;
+        int64_t idx = -1;
+        if (t0 + u < kv_len) {
+          if (e >= 0 && e < p.kv_entries_len) idx = p.kv_entries[e];
+          if (idx < 0 || idx >= p.kv_rows) {
+            if (lane == 0) flag_error(FT_DEV_BAD_KV_INDEX);
+            idx = -1;
+          }
+        }
+        rowid[u] = idx;
+        float part = 0.f;
+        if (idx >= 0) {
+          const T* __restrict__ kp = kbase + idx * p.k_s0;
+#pragma unroll
+          for (int j = 0; j < MAXJ; ++j) {
+            const int d = lane + 32 * j;
+            if (d < D) part = fmaf(qreg[j], to_float<T>(kp[d]), part);
+          }
+        }
+        s[u] = part;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int u = 0; u < TB; ++u) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
+      }
+      float m_new = m;
+#pragma unroll
+      for (int u = 0; u < TB; ++u) {
+        s[u] = rowid[u] >= 0 ? s[u] * p.sm_scale : -INFINITY;  // scale after the dot, in fp32 (fasttree.py:376)
+        m_new = fmaxf(m_new, s[u]);
+      }
+      if (m_new == -INFINITY) continue;  // nothing valid yet
+      const float corr = expf(m - m_new);
+      l *= corr;
+#pragma unroll
+      for (int j = 0; j < MAXJ; ++j) acc[j] *= corr;
+#pragma unroll
+      for (int u = 0; u < TB; ++u) {
+        if (rowid[u] < 0) continue;
+        const float pr = expf(s[u] - m_new);
+        l += pr;
+        // the reference casts the probabilities to V's type before P*V (fasttree.py:391)
+        const float pv = to_float<T>(from_float<T>(pr));
+        const T* __restrict__ vp = vbase + rowid[u] * p.v_s0;
+#pragma unroll
+        for (int j = 0; j < MAXJ; ++j) {
+          const int d = lane + 32 * j;
+          if (d < D) acc[j] = fmaf(pv, to_float<T>(vp[d]), acc[j]);
+        }
+      }
+      m = m_new;
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    float* __restrict__ op = p.mid_o + prow * p.mo_s0 + (int64_t)head * p.mo_s1;
+#pragma unroll
+    for (int j = 0; j < MAXJ; ++j) {
+      const int d = lane + 32 * j;
+      if (d < D) op[d] = acc[j] * inv;
+    }
+    if (lane == 0) p.mid_lse[prow * p.ml_s0 + head] = l > 0.f ? logf(l) + m : -INFINITY;
+  }
+}
+
+}  // namespace ft

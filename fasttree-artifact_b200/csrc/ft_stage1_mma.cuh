@@ -1,0 +1,407 @@
+// Stage 1, warp-level tensor-core kernel (mma.sync m16n8k16, fp16/bf16 inputs,
+// fp32 accumulate), head_dim 64 or 128.
+//
+// One CTA (4 warps) per (vnode, kv head).  The vnode's query rows are the
+// requests of the vnode x the GQA group, packed as row = slot * G + g.  Rows
+// are processed 64 at a time, 16 per warp.  When a vnode has fewer than 64
+// rows the spare warps do not idle: with <= 16 rows the four warps each take a
+// quarter of every 64-token KV tile (two halves for <= 32 rows) and their
+// running (max, sum, acc) are merged through shared memory at the end - the
+// memory-bound shape of leaf and low-fan-out nodes.
+//
+// K/V rows are gathered by row id (vnode_to_kv_entries) with 16-byte cp.async
+// copies into a 3-stage shared-memory ring; every 256-byte row is XOR-swizzled
+// at 16-byte granularity so that ldmatrix reads are bank-conflict free.  Each
+// KV byte is read from global memory once per (vnode, 64-row block).
+//
+// Arithmetic follows kernel_bench/fasttree.py:360-413: scores scaled after the
+// dot product in fp32, online softmax, probabilities rounded to the storage
+// type before P*V, outputs normalised, lse = log(sum) + max.
+#pragma once
+
+#include "ft_common.cuh"
+
+namespace ft {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* ptr) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(ptr));
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;  // 0 source bytes -> the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                                        uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int D>
+struct MmaCfg {
+  static constexpr int THREADS = 128;
+  static constexpr int TILE = 64;               // tokens per pipeline stage
+  static constexpr int STAGES = 3;
+  static constexpr int ROWB = D * 2;            // bytes of one Q/K/V row (16-bit elements)
+  static constexpr int CPR = D / 8;             // 16-byte chunks per row
+  static constexpr int TPP = THREADS / CPR;     // rows one pass of the CTA covers
+  static constexpr int PASSES = TILE / TPP;
+  static constexpr int QROWS = 64;
+  static constexpr int Q_BYTES = QROWS * ROWB;
+  static constexpr int STAGE_BYTES = TILE * ROWB;  // one K or V tile
+  static constexpr int PIPE_BYTES = STAGES * 2 * STAGE_BYTES;
+  static constexpr int OSTRIDE = D + 4;         // floats per staged output row
+  static constexpr int EPI_BYTES = 4 * 16 * OSTRIDE * 4 + 2 * 4 * 16 * 4;
+  static constexpr int SMEM_BYTES = Q_BYTES + (PIPE_BYTES > EPI_BYTES ? PIPE_BYTES : EPI_BYTES);
+  __device__ static __forceinline__ uint32_t swz(int row, int chunk) {
+    return static_cast<uint32_t>(row * ROWB + ((chunk ^ (row & 7)) << 4));
+  }
+};
+
+// One 64-token tile for one warp: NB = 8-token blocks this warp owns (2, 4 or 8).
+template <typename T, int D, int NB>
+__device__ __forceinline__ void mma_tile(const uint32_t k_sm, const uint32_t v_sm, const int tok0,
+                                         const int first_pos, const int kv_len, const bool masked,
+                                         const float scale2, const uint32_t (&qf)[D / 16][4],
+                                         float (&o_acc)[D / 8][4], float (&m_run)[2], float (&l_run)[2],
+                                         const int lane) {
+  using C = MmaCfg<D>;
+  const int t4 = lane & 3;
+  float s[NB][4];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+
+  // S = Q K^T.  K rows sit [token][d]; that is the "col" operand as stored.
+#pragma unroll
+  for (int kk2 = 0; kk2 < D / 32; ++kk2) {
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      uint32_t kb[4];
+      ldmatrix_x4(kb, k_sm + C::swz(tok0 + nb * 8 + (lane & 7), 4 * kk2 + (lane >> 3)));
+      mma16816<T>(s[nb], qf[2 * kk2], kb[0], kb[1]);
+      mma16816<T>(s[nb], qf[2 * kk2 + 1], kb[2], kb[3]);
+    }
+  }
+
+  // scale (log2 domain), mask the tail of the chunk
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float x = s[nb][e] * scale2;
+      if (masked) {
+        const int pos = first_pos + nb * 8 + 2 * t4 + (e & 1);
+        if (pos >= kv_len) x = -INFINITY;
+      }
+      s[nb][e] = x;
+    }
+  }
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) {
+    mx0 = fmaxf(mx0, fmaxf(s[nb][0], s[nb][1]));
+    mx1 = fmaxf(mx1, fmaxf(s[nb][2], s[nb][3]));
+  }
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+  const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
+  const float c0 = fast_exp2(m_run[0] - ms0), c1 = fast_exp2(m_run[1] - ms1);
+  m_run[0] = mn0;
+  m_run[1] = mn1;
+  l_run[0] *= c0;
+  l_run[1] *= c1;
+#pragma unroll
+  for (int nd = 0; nd < D / 8; ++nd) {
+    o_acc[nd][0] *= c0;
+    o_acc[nd][1] *= c0;
+    o_acc[nd][2] *= c1;
+    o_acc[nd][3] *= c1;
+  }
+
+  // P = exp2(S - max); the sum uses the fp32 values, the MMA the rounded ones
+  uint32_t pf[NB / 2][4];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) {
+    const float p0 = fast_exp2(s[nb][0] - ms0), p1 = fast_exp2(s[nb][1] - ms0);
+    const float p2 = fast_exp2(s[nb][2] - ms1), p3 = fast_exp2(s[nb][3] - ms1);
+    l_run[0] += p0 + p1;
+    l_run[1] += p2 + p3;
+    pf[nb >> 1][(nb & 1) * 2 + 0] = pack2<T>(p0, p1);
+    pf[nb >> 1][(nb & 1) * 2 + 1] = pack2<T>(p2, p3);
+  }
+
+  // O += P V.  V rows sit [token][d]; the transposing ldmatrix yields the "col" operand.
+#pragma unroll
+  for (int kt = 0; kt < NB / 2; ++kt) {
+#pragma unroll
+    for (int nd2 = 0; nd2 < D / 16; ++nd2) {
+      uint32_t vb[4];
+      ldmatrix_x4_trans(vb, v_sm + C::swz(tok0 + kt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * nd2 + (lane >> 4)));
+      mma16816<T>(o_acc[2 * nd2], pf[kt], vb[0], vb[1]);
+      mma16816<T>(o_acc[2 * nd2 + 1], pf[kt], vb[2], vb[3]);
+    }
+  }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
+  using C = MmaCfg<D>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t q_sm = smem_u32(smem);
+  const uint32_t pipe_sm = q_sm + C::Q_BYTES;
+  float* epi_o = reinterpret_cast<float*>(smem + C::Q_BYTES);
+  float* epi_m = epi_o + 4 * 16 * C::OSTRIDE;
+  float* epi_l = epi_m + 4 * 16;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int vn = blockIdx.x + p.node_offset;
+  const int kvh = blockIdx.y;
+  const int q_off = p.q_offs[vn], q_len = p.q_lens[vn];
+  const int kv_off = p.kv_offs[vn], kv_len = max(p.kv_lens[vn], 0);
+  const int G = p.group;
+  const int rows = q_len * G;
+  if (rows <= 0) return;
+  const float scale2 = p.sm_scale * 1.4426950408889634f;
+  const int ntiles = (kv_len + C::TILE - 1) / C::TILE;
+  const int ld_c = tid % C::CPR, ld_r = tid / C::CPR;
+
+  const T* __restrict__ kbase = reinterpret_cast<const T*>(p.k) + (int64_t)kvh * p.k_s1 + ld_c * 8;
+  const T* __restrict__ vbase = reinterpret_cast<const T*>(p.v) + (int64_t)kvh * p.v_s1 + ld_c * 8;
+
+  auto load_idx = [&](int tile, int (&idx)[C::PASSES]) {
+#pragma unroll
+    for (int ps = 0; ps < C::PASSES; ++ps) {
+      const int pos = tile * C::TILE + ps * C::TPP + ld_r;
+      int v = -1;
+      if (pos < kv_len) {
+        const int64_t e = (int64_t)kv_off + pos;
+        if (e >= 0 && e < p.kv_entries_len) v = p.kv_entries[e];
+        if (v < 0 || v >= p.kv_rows) {
+          flag_error(FT_DEV_BAD_KV_INDEX);
+          v = -1;
+        }
+      }
+      idx[ps] = v;
+    }
+  };
+  auto issue_tile = [&](int stage, const int (&idx)[C::PASSES]) {
+    const uint32_t k_sm = pipe_sm + stage * 2 * C::STAGE_BYTES;
+    const uint32_t v_sm = k_sm + C::STAGE_BYTES;
+#pragma unroll
+    for (int ps = 0; ps < C::PASSES; ++ps) {
+      const int r = ps * C::TPP + ld_r;
+      const bool ok = idx[ps] >= 0;
+      const int64_t row = ok ? idx[ps] : 0;
+      cp_async16(k_sm + C::swz(r, ld_c), kbase + row * p.k_s0, ok);
+      cp_async16(v_sm + C::swz(r, ld_c), vbase + row * p.v_s0, ok);
+    }
+  };
+
+  for (int row0 = 0; row0 < rows; row0 += C::QROWS) {
+    const int rows_here = min(C::QROWS, rows - row0);
+    const int n_rb = (rows_here + 15) >> 4;                 // 16-row blocks in use: 1..4
+    const int rb_log = n_rb <= 1 ? 0 : (n_rb <= 2 ? 1 : 2);  // warps are dealt to 1, 2 or 4 row blocks
+    const int ways = 4 >> rb_log;                           // warps sharing one row block split the tile
+    const int my_rb = warp & ((1 << rb_log) - 1);
+    const int my_way = warp >> rb_log;
+    const bool active = my_rb < n_rb;
+
+    // ---- gather the row ids first (independent loads), then start the copies
+    constexpr int QPASSES = C::QROWS / C::TPP;
+    int64_t q_src[QPASSES];
+    const int q_passes = (n_rb * 16 + C::TPP - 1) / C::TPP;
+#pragma unroll
+    for (int ps = 0; ps < QPASSES; ++ps) {
+      q_src[ps] = -1;
+      const int prow = row0 + ps * C::TPP + ld_r;
+      if (ps < q_passes && prow < rows) {
+        const int slot = prow / G, gg = prow - slot * G;
+        const int64_t part = (int64_t)q_off + slot;
+        if (part >= 0 && part < p.num_partial_rows) {
+          const int req = p.q_entries[part];
+          if (req >= 0 && req < p.batch)
+            q_src[ps] = (int64_t)req * p.q_s0 + (int64_t)(kvh * G + gg) * p.q_s1 + ld_c * 8;
+          else
+            flag_error(FT_DEV_BAD_Q_INDEX);
+        } else {
+          flag_error(FT_DEV_BAD_ROW_INDEX);
+        }
+      }
+    }
+    int idx[C::STAGES][C::PASSES];
+#pragma unroll
+    for (int s = 0; s < C::STAGES; ++s) {
+      if (s < ntiles) load_idx(s, idx[s]);
+    }
+#pragma unroll
+    for (int ps = 0; ps < QPASSES; ++ps) {
+      if (ps < q_passes) {
+        const bool ok = q_src[ps] >= 0;
+        cp_async16(q_sm + C::swz(ps * C::TPP + ld_r, ld_c),
+                   reinterpret_cast<const T*>(p.q) + (ok ? q_src[ps] : 0), ok);
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < C::STAGES - 1; ++s) {
+      if (s < ntiles) issue_tile(s, idx[s]);
+      cp_async_commit();
+    }
+    // idx[STAGES-1] now holds the row ids of the next tile to be issued
+
+    float o_acc[D / 8][4];
+#pragma unroll
+    for (int nd = 0; nd < D / 8; ++nd) o_acc[nd][0] = o_acc[nd][1] = o_acc[nd][2] = o_acc[nd][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    uint32_t qf[D / 16][4];
+
+    for (int j = 0; j < ntiles; ++j) {
+      cp_async_wait<C::STAGES - 2>();  // tile j (and Q) have landed for this thread
+      __syncthreads();                 // ... for every thread; and tile j-1's stage is free again
+      const int nt = j + C::STAGES - 1;
+      if (nt < ntiles) issue_tile(nt % C::STAGES, idx[C::STAGES - 1]);
+      cp_async_commit();
+      if (nt + 1 < ntiles) load_idx(nt + 1, idx[C::STAGES - 1]);
+      if (j == 0 && active) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          ldmatrix_x4(qf[kk], q_sm + C::swz(my_rb * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * kk + (lane >> 4)));
+      }
+      if (active) {
+        const uint32_t k_sm = pipe_sm + (j % C::STAGES) * 2 * C::STAGE_BYTES;
+        const uint32_t v_sm = k_sm + C::STAGE_BYTES;
+        const bool masked = (j + 1) * C::TILE > kv_len;
+        if (ways == 4) {
+          const int tok0 = my_way * 16;
+          mma_tile<T, D, 2>(k_sm, v_sm, tok0, j * C::TILE + tok0, kv_len, masked, scale2, qf, o_acc, m_run, l_run,
+                            lane);
+        } else if (ways == 2) {
+          const int tok0 = my_way * 32;
+          mma_tile<T, D, 4>(k_sm, v_sm, tok0, j * C::TILE + tok0, kv_len, masked, scale2, qf, o_acc, m_run, l_run,
+                            lane);
+        } else {
+          mma_tile<T, D, 8>(k_sm, v_sm, 0, j * C::TILE, kv_len, masked, scale2, qf, o_acc, m_run, l_run, lane);
+        }
+      }
+    }
+    cp_async_wait<0>();
+    __syncthreads();  // the ring is idle: its memory becomes the output staging area
+
+    if (active) {
+      float l0 = l_run[0], l1 = l_run[1];
+      l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+      l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+      const int g8 = lane >> 2, t4 = lane & 3;
+      float* dst0 = epi_o + (warp * 16 + g8) * C::OSTRIDE + 2 * t4;
+      float* dst1 = dst0 + 8 * C::OSTRIDE;
+#pragma unroll
+      for (int nd = 0; nd < D / 8; ++nd) {
+        *reinterpret_cast<float2*>(dst0 + nd * 8) = make_float2(o_acc[nd][0], o_acc[nd][1]);
+        *reinterpret_cast<float2*>(dst1 + nd * 8) = make_float2(o_acc[nd][2], o_acc[nd][3]);
+      }
+      if (t4 == 0) {
+        epi_m[warp * 16 + g8] = m_run[0];
+        epi_m[warp * 16 + g8 + 8] = m_run[1];
+        epi_l[warp * 16 + g8] = l0;
+        epi_l[warp * 16 + g8 + 8] = l1;
+      }
+    }
+    __syncthreads();
+
+    // ---- merge the warps that shared a row block, normalise, write the partial rows
+    {
+      const int r = tid >> 3, seg = tid & 7;
+      for (int rb = 0; rb < n_rb; ++rb) {
+        const int prow = row0 + rb * 16 + r;
+        if (prow >= rows) continue;
+        const int slot = prow / G, gg = prow - slot * G;
+        const int64_t part = (int64_t)q_off + slot;
+        if (part < 0 || part >= p.num_partial_rows) continue;  // flagged above
+        float M = -INFINITY;
+        for (int w = 0; w < ways; ++w) M = fmaxf(M, epi_m[(rb + (w << rb_log)) * 16 + r]);
+        float L = 0.f;
+        float4 out[D / 32];
+#pragma unroll
+        for (int i = 0; i < D / 32; ++i) out[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int w = 0; w < ways; ++w) {
+          const int ww = rb + (w << rb_log);
+          const float mw = epi_m[ww * 16 + r];
+          const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - M);
+          L = fmaf(epi_l[ww * 16 + r], f, L);
+          const float4* src = reinterpret_cast<const float4*>(epi_o + (ww * 16 + r) * C::OSTRIDE);
+#pragma unroll
+          for (int i = 0; i < D / 32; ++i) {
+            const float4 x = src[seg + 8 * i];
+            out[i].x = fmaf(f, x.x, out[i].x);
+            out[i].y = fmaf(f, x.y, out[i].y);
+            out[i].z = fmaf(f, x.z, out[i].z);
+            out[i].w = fmaf(f, x.w, out[i].w);
+          }
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        const int head = kvh * G + gg;
+        float4* dst = reinterpret_cast<float4*>(p.mid_o + part * p.mo_s0 + (int64_t)head * p.mo_s1);
+#pragma unroll
+        for (int i = 0; i < D / 32; ++i)
+          dst[seg + 8 * i] = make_float4(out[i].x * inv, out[i].y * inv, out[i].z * inv, out[i].w * inv);
+        if (seg == 0)
+          p.mid_lse[part * p.ml_s0 + head] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
+      }
+    }
+    __syncthreads();  // staging area and Q tile are reused by the next 64-row block
+  }
+}
+
+}  // namespace ft

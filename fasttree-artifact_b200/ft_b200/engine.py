@@ -1,0 +1,192 @@
+"""Host glue between torch tensors and the C ABI (ft_decode / ft_stage1 / ft_stage2).
+
+Mirrors the call contract of the reference's ``fasttree_decode``
+(kernel_bench/fasttree.py:582-642): the caller owns every tensor, kernels are
+enqueued on torch's current CUDA stream, nothing synchronises with the host and
+nothing is allocated per call.  Bad arguments raise ``FastTreeError`` /
+``ValueError`` instead of silently producing garbage.
+"""
+import ctypes
+
+import torch
+
+from . import lib as _lib
+
+_DTYPES = {torch.float16: _lib.FT_F16, torch.bfloat16: _lib.FT_BF16, torch.float32: _lib.FT_F32}
+
+_ARG_CACHE = {}
+_ARG_CACHE_MAX = 256
+
+
+def _require_cuda(name, t):
+    if not isinstance(t, torch.Tensor):
+        raise ValueError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise ValueError(f"{name} is on {t.device}; the engine has no CPU path - tensors must live on a CUDA device")
+
+
+def _table(name, t):
+    _require_cuda(name, t)
+    if t.dtype != torch.int32:
+        raise ValueError(f"{name} must be int32, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return t
+
+
+def _pair(name, x):
+    x = list(x)
+    if len(x) != 2:
+        raise ValueError(f"{name} must have two entries (one per phase)")
+    return int(x[0]), int(x[1])
+
+
+def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, vnode_to_kv_lens,
+               vnode_to_q_entries, vnode_to_q_offs, vnode_to_q_lens, req_to_vnode_entries,
+               req_to_vnode_offs, req_to_vnode_lens, mid_o, mid_lse, phase_node_nums, phase_node_offsets,
+               phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap=-1, path="auto", o_lse=None,
+               stream=None):
+    """Validate the tensors and fill a :class:`DecodeArgs` struct."""
+    for name, t in (("q", q), ("k_buffer", k_buffer), ("v_buffer", v_buffer), ("o", o),
+                    ("mid_o", mid_o), ("mid_lse", mid_lse)):
+        _require_cuda(name, t)
+    if q.dim() != 3 or o.dim() != 3 or k_buffer.dim() != 3 or v_buffer.dim() != 3:
+        raise ValueError("q, o must be [batch, heads, head_dim] and k/v buffers [rows, kv_heads, head_dim]")
+    if q.dtype not in _DTYPES:
+        raise ValueError(f"unsupported dtype {q.dtype}")
+    if not (k_buffer.dtype == v_buffer.dtype == o.dtype == q.dtype):
+        raise ValueError("q, k_buffer, v_buffer and o must share one dtype")
+    if q.shape[-1] != k_buffer.shape[-1] or q.shape[-1] != v_buffer.shape[-1]:
+        raise ValueError("head_dim of q, k_buffer and v_buffer differ")          # reference: assert Lq == Lk
+    if o.shape != q.shape:
+        raise ValueError("o must have the shape of q")
+    for name, t in (("q", q), ("k_buffer", k_buffer), ("v_buffer", v_buffer), ("o", o), ("mid_o", mid_o)):
+        if t.stride(-1) != 1:
+            raise ValueError(f"{name}: the head_dim axis must be contiguous")
+    if mid_o.dtype != torch.float32 or mid_lse.dtype != torch.float32:
+        raise ValueError("mid_o / mid_lse must be float32")
+    if mid_o.dim() != 3 or mid_lse.dim() != 2 or mid_lse.stride(1) != 1:
+        raise ValueError("mid_o must be [rows, heads, head_dim] and mid_lse [rows, heads]")
+    if mid_o.shape[1] < q.shape[1] or mid_o.shape[2] != q.shape[2] or mid_lse.shape[1] < q.shape[1]:
+        raise ValueError("mid_o / mid_lse are too small for the head count of q")
+    if k_buffer.shape != v_buffer.shape:
+        raise ValueError("k_buffer and v_buffer differ in shape")
+    tabs = [_table(n, t) for n, t in (
+        ("vnode_to_kv_entries", vnode_to_kv_entries), ("vnode_to_kv_offs", vnode_to_kv_offs),
+        ("vnode_to_kv_lens", vnode_to_kv_lens), ("vnode_to_q_entries", vnode_to_q_entries),
+        ("vnode_to_q_offs", vnode_to_q_offs), ("vnode_to_q_lens", vnode_to_q_lens),
+        ("req_to_vnode_entries", req_to_vnode_entries), ("req_to_vnode_offs", req_to_vnode_offs),
+        ("req_to_vnode_lens", req_to_vnode_lens))]
+    n0, n1 = _pair("phase_node_nums", phase_node_nums)
+    f0, f1 = _pair("phase_node_offsets", phase_node_offsets)
+    nv = vnode_to_kv_offs.numel()
+    for cnt, off in ((n0, f0), (n1, f1)):
+        if cnt < 0 or off < 0 or off + cnt > nv:
+            raise ValueError("phase_node_nums / phase_node_offsets do not fit the vnode tables")
+    if min(vnode_to_kv_lens.numel(), vnode_to_q_offs.numel(), vnode_to_q_lens.numel()) < nv:
+        raise ValueError("vnode tables differ in length")
+    batch = q.shape[0]
+    if req_to_vnode_offs.numel() < batch or req_to_vnode_lens.numel() < batch:
+        raise ValueError("request tables are shorter than the batch")
+    if o_lse is not None:
+        _require_cuda("o_lse", o_lse)
+        if o_lse.dtype != torch.float32 or not o_lse.is_contiguous() or o_lse.numel() < batch * q.shape[1]:
+            raise ValueError("o_lse must be a contiguous float32 [batch, heads] tensor")
+    if path not in _lib.PATHS:
+        raise ValueError(f"path must be one of {sorted(_lib.PATHS)}")
+
+    a = _lib.DecodeArgs()
+    a.q, a.k_buffer, a.v_buffer, a.o = q.data_ptr(), k_buffer.data_ptr(), v_buffer.data_ptr(), o.data_ptr()
+    a.o_lse = o_lse.data_ptr() if o_lse is not None else None
+    a.dtype = _DTYPES[q.dtype]
+    a.batch, a.num_qo_heads, a.head_dim = batch, q.shape[1], q.shape[2]
+    a.num_kv_heads = k_buffer.shape[1]
+    a.path = _lib.PATHS[path]
+    a.kv_rows = k_buffer.shape[0]
+    a.q_stride0, a.q_stride1 = q.stride(0), q.stride(1)
+    a.k_stride0, a.k_stride1 = k_buffer.stride(0), k_buffer.stride(1)
+    a.v_stride0, a.v_stride1 = v_buffer.stride(0), v_buffer.stride(1)
+    a.o_stride0, a.o_stride1 = o.stride(0), o.stride(1)
+    (a.vnode_to_kv_entries, a.vnode_to_kv_offs, a.vnode_to_kv_lens, a.vnode_to_q_entries,
+     a.vnode_to_q_offs, a.vnode_to_q_lens, a.req_to_vnode_entries, a.req_to_vnode_offs,
+     a.req_to_vnode_lens) = [t.data_ptr() for t in tabs]
+    a.kv_entries_len = vnode_to_kv_entries.numel()
+    a.num_partial_rows = min(mid_o.shape[0], mid_lse.shape[0], vnode_to_q_entries.numel())
+    a.phase_node_nums[0], a.phase_node_nums[1] = n0, n1
+    a.phase_node_offsets[0], a.phase_node_offsets[1] = f0, f1
+    a.phase_q_tile_sizes[0], a.phase_q_tile_sizes[1] = _pair("phase_q_tile_sizes", phase_q_tile_sizes)
+    a.phase_kv_tile_sizes[0], a.phase_kv_tile_sizes[1] = _pair("phase_kv_tile_sizes", phase_kv_tile_sizes)
+    a.mid_o, a.mid_lse = mid_o.data_ptr(), mid_lse.data_ptr()
+    a.mid_o_stride0, a.mid_o_stride1 = mid_o.stride(0), mid_o.stride(1)
+    a.mid_lse_stride0 = mid_lse.stride(0)
+    a.sm_scale = float(sm_scale)
+    a.logit_cap = float(logit_cap)
+    a.stream = stream if stream is not None else torch.cuda.current_stream(q.device).cuda_stream
+    return a
+
+
+def _cached_args(tensors, rest, path, o_lse):
+    """Argument structs are memoised on the identity of the tensors (address,
+    shape, strides), so a steady-state decode loop pays for one dict lookup."""
+    q = tensors[0]
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    key = (tuple((t.data_ptr(), tuple(t.shape), t.stride(0)) for t in tensors),
+           tuple(tuple(x) if isinstance(x, (list, tuple)) else x for x in rest), path,
+           o_lse.data_ptr() if o_lse is not None else 0, stream)
+    a = _ARG_CACHE.get(key)
+    if a is None:
+        (pn, po, pq, pk, sm_scale, logit_cap) = rest
+        a = build_args(*tensors, pn, po, pq, pk, sm_scale, logit_cap, path=path, o_lse=o_lse, stream=stream)
+        if len(_ARG_CACHE) >= _ARG_CACHE_MAX:
+            _ARG_CACHE.clear()
+        _ARG_CACHE[key] = a
+    return a
+
+
+def _call(fn_name, q, k_buffer, v_buffer, o, kv_entries, kv_offs, kv_lens, q_entries, q_offs, q_lens,
+          r2v_entries, r2v_offs, r2v_lens, mid_o, mid_lse, phase_node_nums, phase_node_offsets,
+          phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap, path, o_lse):
+    tensors = (q, k_buffer, v_buffer, o, kv_entries, kv_offs, kv_lens, q_entries, q_offs, q_lens,
+               r2v_entries, r2v_offs, r2v_lens, mid_o, mid_lse)
+    rest = (phase_node_nums, phase_node_offsets, phase_q_tile_sizes, phase_kv_tile_sizes,
+            float(sm_scale), float(logit_cap))
+    a = _cached_args(tensors, rest, path, o_lse)
+    lib = _lib.load()
+    if q.device.index != torch.cuda.current_device():
+        with torch.cuda.device(q.device):
+            rc = getattr(lib, fn_name)(ctypes.byref(a))
+    else:
+        rc = getattr(lib, fn_name)(ctypes.byref(a))
+    _lib.check(rc)
+
+
+def decode(*args, logit_cap=-1, path="auto", o_lse=None):
+    """Stage 1 + stage 2.  Positional arguments are those of the reference's
+    ``fasttree_decode`` up to and including ``sm_scale``."""
+    _call("ft_decode", *args, logit_cap, path, o_lse)
+
+
+def stage1(*args, logit_cap=-1, path="auto"):
+    _call("ft_stage1", *args, logit_cap, path, None)
+
+
+def stage2(*args, logit_cap=-1, o_lse=None):
+    _call("ft_stage2", *args, logit_cap, "auto", o_lse)
+
+
+def stage1_path_name(*args, logit_cap=-1, path="auto"):
+    tensors, rest = args[:15], args[15:]
+    a = build_args(*tensors, *rest, logit_cap, path=path)
+    name = _lib.load().ft_stage1_path_name(ctypes.byref(a))
+    if name is None:
+        _lib.check(-1)
+    return name.decode()
+
+
+def bump_kv_lens(vnode_to_kv_lens, last_vnodes):
+    """``vnode_to_kv_lens[last_vnodes] += 1`` on the device, current stream."""
+    _table("vnode_to_kv_lens", vnode_to_kv_lens)
+    _table("last_vnodes", last_vnodes)
+    stream = torch.cuda.current_stream(vnode_to_kv_lens.device).cuda_stream
+    _lib.check(_lib.load().ft_bump_kv_lens(vnode_to_kv_lens.data_ptr(), last_vnodes.data_ptr(),
+                                           last_vnodes.numel(), stream))

@@ -1,0 +1,383 @@
+"""Host planner: radix tree -> vnode tables for the decode kernels.
+
+Two splitters share one table emitter:
+
+* ``plan_reference``  reproduces the reference planner bit for bit
+  (kernel_bench/fasttree.py:64-262: greedy split-K/split-Q edge heuristic on a
+  padding cost model, CTA-count driven KV-split / tile adaptation tuned for a
+  132-SM part).  Kept so that plans, partial buffers and outputs can be compared
+  one-to-one with the reference.
+* ``plan_b200``       the splitter sized for a 148-SM B200: tasks are
+  (node KV chunk x request group); chunk lengths are balanced so the grid fills
+  the machine a few times over, with as few partial rows as possible, and nodes
+  with enough query rows are routed to the 128-row tensor-core tile.
+
+Both are pure functions of (tree, parameters): no randomness, no dependence on
+dict/set iteration order, ties broken by node id.
+
+The emitted table family is the reference's (fasttree.py:282-296):
+``vnode_to_kv_entries/offs/lens``, ``vnode_to_q_entries/offs/lens``,
+``req_to_vnode_entries/offs/lens`` (entries are partial-ROW ids),
+``phase_node_nums/offsets``.
+"""
+from collections import deque
+from dataclasses import dataclass, field
+
+import numpy as np
+
+PAD_ENTRIES = 32  # the reference appends 32 x -1 to both index lists (fasttree.py:261-262)
+
+
+@dataclass
+class VirtualNode:
+    """One context-queries pairing before it is cut into tasks."""
+    kv_ranges: list        # [(row_begin, row_end), ...] root-most segment first
+    requests: np.ndarray   # request ids, in partial-row order
+    q_tile: int            # requests per task
+    kv_split: int          # tokens per task
+
+
+@dataclass
+class Plan:
+    vnode_to_kv_entries: np.ndarray
+    vnode_to_kv_offs: np.ndarray
+    vnode_to_kv_lens: np.ndarray
+    vnode_to_q_entries: np.ndarray
+    vnode_to_q_offs: np.ndarray
+    vnode_to_q_lens: np.ndarray
+    req_to_vnode_entries: np.ndarray
+    req_to_vnode_offs: np.ndarray
+    req_to_vnode_lens: np.ndarray
+    phase_node_nums: list
+    phase_node_offsets: list
+    node_assignments: list
+    phase_q_tile_sizes: list = field(default_factory=list)
+    phase_kv_tile_sizes: list = field(default_factory=list)
+    kv_split_sizes: list = field(default_factory=list)
+    info: dict = field(default_factory=dict)
+
+    @property
+    def num_partial_rows(self):
+        return int(self.vnode_to_q_entries.size)
+
+    @property
+    def num_vnodes(self):
+        return int(self.vnode_to_kv_offs.size)
+
+    def tables(self):
+        return (self.vnode_to_kv_entries, self.vnode_to_kv_offs, self.vnode_to_kv_lens,
+                self.vnode_to_q_entries, self.vnode_to_q_offs, self.vnode_to_q_lens,
+                self.req_to_vnode_entries, self.req_to_vnode_offs, self.req_to_vnode_lens)
+
+
+# --------------------------------------------------------------------- emitter
+def emit_tables(vnodes, batch_size, small_tile, order_key=None):
+    """Cut every virtual node into (KV chunk x request tile) tasks and build the
+    reference-format tables.  Tasks whose request count exceeds ``small_tile``
+    form phase 0, the others phase 1 (stable partition, fasttree.py:246-259).
+    ``order_key(kv_len, q_len)`` optionally sorts the tasks inside each phase
+    (stable, descending) so that long tasks are scheduled first."""
+    kv_chunks, kv_offs, kv_lens, q_chunks, q_offs, q_lens = [], [], [], [], [], []
+    kv_total = q_total = 0
+    for vn in vnodes:
+        reqs = np.asarray(vn.requests, dtype=np.int32)
+        nreq = int(reqs.size)
+        if nreq == 0:
+            continue
+        segs = [np.arange(b, e, dtype=np.int32) for (b, e) in vn.kv_ranges]
+        length = int(sum(s.size for s in segs))
+        if length == 0:
+            continue
+        kv_chunks.extend(segs)
+        n_kv = -(-length // vn.kv_split)
+        n_q = -(-nreq // vn.q_tile)
+        c_off = np.arange(n_kv, dtype=np.int64) * vn.kv_split
+        c_len = np.minimum(c_off + vn.kv_split, length) - c_off
+        t_off = np.arange(n_q, dtype=np.int64) * vn.q_tile
+        t_len = np.minimum(t_off + vn.q_tile, nreq) - t_off
+        # chunk-major, request-tile-minor; every chunk repeats the full request list
+        kv_offs.append(np.repeat(kv_total + c_off, n_q))
+        kv_lens.append(np.repeat(c_len, n_q))
+        q_base = q_total + np.arange(n_kv, dtype=np.int64) * nreq
+        q_offs.append((q_base[:, None] + t_off[None, :]).reshape(-1))
+        q_lens.append(np.tile(t_len, n_kv))
+        q_chunks.append(np.tile(reqs, n_kv))
+        kv_total += length
+        q_total += n_kv * nreq
+
+    def cat(parts, dtype=np.int64):
+        return np.concatenate(parts).astype(dtype) if parts else np.zeros(0, dtype=dtype)
+
+    kv_offs, kv_lens, q_offs, q_lens = cat(kv_offs), cat(kv_lens), cat(q_offs), cat(q_lens)
+    q_entries = cat(q_chunks, np.int32)
+    if kv_total + PAD_ENTRIES >= 2 ** 31 or q_total >= 2 ** 31:
+        raise ValueError("plan does not fit int32 tables")
+
+    # request -> partial rows: rows grouped by request id, original order kept inside a group
+    order = np.argsort(q_entries, kind="stable").astype(np.int32)
+    counts = np.bincount(q_entries, minlength=batch_size).astype(np.int64)
+    if counts.size > batch_size:
+        raise ValueError("a request id in the tree is >= batch_size")
+    r2v_lens = counts.astype(np.int32)
+    r2v_offs = (np.cumsum(counts) - counts).astype(np.int32)
+
+    big = np.flatnonzero(q_lens > small_tile)
+    small = np.flatnonzero(q_lens <= small_tile)
+    if order_key is not None:
+        big = big[np.argsort(-order_key(kv_lens[big], q_lens[big]), kind="stable")]
+        small = small[np.argsort(-order_key(kv_lens[small], q_lens[small]), kind="stable")]
+    perm = np.concatenate([big, small])
+    pad = np.full(PAD_ENTRIES, -1, dtype=np.int32)
+    return dict(
+        vnode_to_kv_entries=np.concatenate([cat(kv_chunks, np.int32), pad]),
+        vnode_to_kv_offs=kv_offs[perm].astype(np.int32), vnode_to_kv_lens=kv_lens[perm].astype(np.int32),
+        vnode_to_q_entries=q_entries,
+        vnode_to_q_offs=q_offs[perm].astype(np.int32), vnode_to_q_lens=q_lens[perm].astype(np.int32),
+        req_to_vnode_entries=np.concatenate([order, pad]),
+        req_to_vnode_offs=r2v_offs, req_to_vnode_lens=r2v_lens,
+        phase_node_nums=[int(big.size), int(small.size)],
+        phase_node_offsets=[0, int(big.size)],
+    )
+
+
+# ------------------------------------------------------- reference-compatible
+def _children(tree):
+    kids = [[] for _ in tree]
+    for i in range(1, len(tree)):
+        kids[tree[i].parent].append(i)
+    return kids
+
+
+def _pad_cost(n_q, n_k, tsq, tsk, alpha, beta, group):
+    """alpha * (empty rows of the last request tile) * G * n_k
+       + beta * (empty columns of a short KV tile) * n_q * G     (fasttree.py:30-45)"""
+    ph = 0 if n_q > tsq[1] else 1
+    empty_rows = tsq[ph] - ((n_q - 1) % tsq[ph] + 1)
+    empty_cols = max(0, tsk[ph] - n_k)
+    return alpha * empty_rows * group * n_k + beta * empty_cols * n_q * group
+
+
+def greedy_edge_assignments(tree, params):
+    """Per parent->child edge: 1 if the child's requests should take the
+    parent's accumulated KV along (no extra partial row to merge), 0 if the
+    child keeps a vnode of its own (fasttree.py:64-96)."""
+    kids = _children(tree)
+    tsq, tsk = params.TSQs, params.TSKs
+    a, b, g, grp = params.alpha, params.beta, params.gamma, params.kv_group_num
+    run_len = [nd.seqlen for nd in tree]
+    assign = [0] * len(tree)
+    frontier = deque((0,))
+    while frontier:
+        v = frontier.popleft()
+        n_here = len(tree[v].requests)
+        for c in kids[v]:
+            n_c = len(tree[c].requests)
+            own = (_pad_cost(n_here, run_len[v], tsq, tsk, a, b, grp)
+                   + _pad_cost(n_c, run_len[c], tsq, tsk, a, b, grp) + g * n_c)
+            carried = (_pad_cost(n_here - n_c, run_len[v], tsq, tsk, a, b, grp)
+                       + _pad_cost(n_c, run_len[c] + run_len[v], tsq, tsk, a, b, grp))
+            if own > carried:
+                assign[c] = 1
+                n_here -= n_c
+                run_len[c] += run_len[v]
+            frontier.append(c)
+    return assign
+
+
+def _requests_served(tree, assign):
+    """Requests each node's own vnode serves: a leaf serves its request, an inner
+    node the requests of every child subtree that did not carry its KV away.
+    The order inside a node follows the reference's leaf-to-root queue
+    (fasttree.py:126-141), which fixes the partial-row order."""
+    n = len(tree)
+    served = [[] for _ in range(n)]
+    waiting = [nd.num_children for nd in tree]
+    ready = deque()
+    for i, nd in enumerate(tree):
+        if nd.num_children == 0:
+            served[i] = list(nd.requests)
+            ready.append(i)
+    while ready:
+        v = ready.popleft()
+        par = tree[v].parent
+        if v != 0 and assign[v] == 0:
+            served[par].extend(tree[v].requests)
+        waiting[par] -= 1            # par == -1 at the root lands on the last node, as in the reference
+        if waiting[par] == 0:
+            ready.append(par)
+    return served
+
+
+def _chain_ranges(tree, kv_ptrs, assign, i):
+    """Row ranges of node i preceded by every ancestor it carries (assign == 1)."""
+    chain = [(kv_ptrs[i], kv_ptrs[i + 1])]
+    up = i
+    while assign[up] == 1:
+        up = tree[up].parent
+        chain.append((kv_ptrs[up], kv_ptrs[up + 1]))
+    chain.reverse()
+    return chain
+
+
+def plan_reference(tree, kv_ptrs, batch_size, num_kv_heads, kv_split_sizes, para_threshs1, para_threshs2,
+                   params, log=None):
+    """Bit-exact re-implementation of the reference planner.  Mutates
+    ``params.TSQs/TSKs`` exactly where the reference does (fasttree.py:181-186)."""
+    tsq = list(params.TSQs)
+    split = [kv_split_sizes[0], kv_split_sizes[0]]
+    assign, served = None, None
+    for rnd in range(3):
+        assign = greedy_edge_assignments(tree, params)
+        served = _requests_served(tree, assign)
+        ctas = [0, 0]
+        for i, reqs in enumerate(served):
+            if not reqs:
+                continue
+            length = sum(e - b for b, e in _chain_ranges(tree, kv_ptrs, assign, i))
+            ph = 0 if len(reqs) > tsq[1] else 1
+            ctas[ph] += -(-len(reqs) // tsq[ph]) * -(-length // split[ph])
+        ctas = [c * num_kv_heads for c in ctas]
+        if log is not None:
+            log.append(("parallelisms", list(ctas)))
+        if rnd == 0:
+            short = [ph for ph in range(2) if 0 < ctas[ph] < para_threshs1[ph]]
+            for ph in short:
+                split[ph] = kv_split_sizes[1]
+            if not short:
+                break
+        elif rnd == 1:
+            if 0 < ctas[0] < para_threshs2[0]:
+                keep = 1
+            elif 0 < ctas[1] < para_threshs2[1]:
+                keep = 0
+            else:
+                break
+            tsq = [tsq[keep], tsq[keep]]
+            params.set_q_tile_sizes(tsq)
+            params.set_kv_tile_sizes([params.TSKs[keep], params.TSKs[keep]])
+
+    vnodes = []
+    for i, reqs in enumerate(served):
+        if not reqs:
+            continue
+        ph = 0 if len(reqs) > tsq[1] else 1
+        vnodes.append(VirtualNode(_chain_ranges(tree, kv_ptrs, assign, i), np.asarray(reqs, dtype=np.int32),
+                                  q_tile=tsq[0], kv_split=split[ph]))   # request tiles always use the big tile (:194,215)
+    tabs = emit_tables(vnodes, batch_size, small_tile=tsq[1])
+    return Plan(node_assignments=assign, phase_q_tile_sizes=list(tsq), phase_kv_tile_sizes=list(params.TSKs),
+                kv_split_sizes=split, info={"planner": "reference"}, **tabs)
+
+
+# ------------------------------------------------------------------ B200 splitter
+@dataclass(frozen=True)
+class B200Model:
+    """Machine constants the splitter plans against (one B200: 148 SMs; the
+    warp-MMA stage-1 kernel keeps two 112 KiB CTAs resident per SM)."""
+    num_sms: int = 148
+    ctas_per_sm: int = 2
+    waves: float = 2.0              # aim for this many rounds of resident CTAs
+    tile_tokens: int = 64           # KV tile of the stage-1 kernels
+    rows_per_cta: int = 64          # query rows (requests x group) one CTA holds
+    min_chunk: int = 128            # never cut a node's KV finer than this many tokens
+    nominal_split: int = 512        # chunk length assumed while deciding the edges
+    ridge_flop_per_byte: float = 90.0   # warp-MMA flops that cost as much time as one streamed byte
+    task_overhead_bytes: int = 16384    # fixed cost of one more CTA, in streamed-byte equivalents
+    elem_bytes: int = 2
+
+
+def _task_cost(n_req, length, group, head_dim, m):
+    """Cost, in streamed-byte equivalents per KV head, of pairing ``n_req``
+    requests with ``length`` tokens: KV streamed once per 64-row block (or the
+    tensor-core time if larger), fp32 partial rows written and read back once per
+    chunk, and a fixed cost per CTA."""
+    if n_req <= 0 or length <= 0:
+        return 0.0
+    rows = n_req * group
+    row_blocks = -(-rows // m.rows_per_cta)
+    chunks = -(-length // m.nominal_split)
+    stream = row_blocks * length * 2 * head_dim * m.elem_bytes
+    tensor = (-(-rows // 16) * 16) * length * 4 * head_dim / m.ridge_flop_per_byte
+    partial = chunks * rows * (head_dim + 1) * 4 * 2
+    return max(stream, tensor) + partial + row_blocks * chunks * m.task_overhead_bytes
+
+
+def b200_edge_assignments(tree, group, head_dim, m):
+    """Same greedy walk as the reference heuristic (breadth first, children in id
+    order, the parent's remaining request count shrinking as children carry its
+    KV away) but on a cost model that charges what a B200 pays for: re-reading the
+    parent's KV for the carrying child, partial-row traffic, and per-CTA overhead."""
+    kids = _children(tree)
+    run_len = [nd.seqlen for nd in tree]
+    assign = [0] * len(tree)
+    frontier = deque((0,))
+    while frontier:
+        v = frontier.popleft()
+        n_here = len(tree[v].requests)
+        for c in kids[v]:
+            n_c = len(tree[c].requests)
+            own = _task_cost(n_here, run_len[v], group, head_dim, m) + _task_cost(n_c, run_len[c], group, head_dim, m)
+            carried = (_task_cost(n_here - n_c, run_len[v], group, head_dim, m)
+                       + _task_cost(n_c, run_len[c] + run_len[v], group, head_dim, m))
+            if carried < own:
+                assign[c] = 1
+                n_here -= n_c
+                run_len[c] += run_len[v]
+            frontier.append(c)
+    return assign
+
+
+def plan_b200(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, params, model=None):
+    """Tree -> balanced (node KV chunk x request group) tasks for one B200.
+
+    1. edges: :func:`b200_edge_assignments`;
+    2. request groups: ``rows_per_cta // G`` requests per task;
+    3. KV chunks: a global per-task byte target = streamed bytes of the whole step
+       / (SMs x resident CTAs x waves); each virtual node is cut into equal chunks
+       (multiples of the 64-token tile, never below ``min_chunk``) so that no task
+       exceeds the target - long shared prefixes are split, short leaves are not,
+       which keeps the number of partial rows low;
+    4. order: longest tasks first inside each phase (stable).
+
+    ``num_kv_heads`` is the LOCAL head count of this GPU (the grid is tasks x
+    local KV heads), so a head-sharded rank plans finer chunks.  Writes the
+    request/KV tile sizes it used back into ``params`` like the reference does."""
+    m = model or getattr(params, "b200_model", None) or B200Model()
+    group = max(1, num_qo_heads // num_kv_heads)
+    q_tile = max(1, m.rows_per_cta // group)
+    small_tile = max(1, min(q_tile, 16 // group if group <= 16 else 1))
+    assign = b200_edge_assignments(tree, group, head_dim, m)
+
+    carried_away = [set() for _ in tree]
+    for i in range(1, len(tree)):
+        if assign[i] == 1:
+            carried_away[tree[i].parent].update(tree[i].requests)
+    specs = []
+    row_bytes = 2 * head_dim * m.elem_bytes
+    total_stream = 0
+    for i, nd in enumerate(tree):
+        reqs = sorted(set(nd.requests) - carried_away[i])
+        if not reqs:
+            continue
+        ranges = _chain_ranges(tree, kv_ptrs, assign, i)
+        length = sum(e - b for b, e in ranges)
+        if length <= 0:
+            continue
+        specs.append((ranges, reqs, length))
+        total_stream += -(-len(reqs) // q_tile) * length * row_bytes
+    slots = m.num_sms * m.ctas_per_sm * m.waves
+    target = max(total_stream * num_kv_heads / slots, m.min_chunk * row_bytes)
+
+    vnodes = []
+    for ranges, reqs, length in specs:
+        want = int(round(length * row_bytes / target))
+        n_chunks = max(1, min(want, -(-length // m.min_chunk)))
+        chunk = -(-length // n_chunks)
+        chunk = -(-chunk // m.tile_tokens) * m.tile_tokens
+        vnodes.append(VirtualNode(ranges, np.asarray(reqs, dtype=np.int32), q_tile=q_tile, kv_split=chunk))
+    tabs = emit_tables(vnodes, batch_size, small_tile=small_tile,
+                       order_key=lambda kv_len, q_len: kv_len * 64 + np.minimum(q_len, 63))
+    params.set_q_tile_sizes([q_tile, small_tile])
+    params.set_kv_tile_sizes([m.tile_tokens, m.tile_tokens])
+    return Plan(node_assignments=assign, phase_q_tile_sizes=[q_tile, small_tile],
+                phase_kv_tile_sizes=[m.tile_tokens, m.tile_tokens], kv_split_sizes=[],
+                info={"planner": "b200", "target_bytes": float(target), "vnodes": len(vnodes)}, **tabs)

@@ -1,0 +1,109 @@
+"""Drop-in for the reference's ``kernel_bench/fasttree.py``.
+
+Exports the three names the harnesses import (kernel_bench/benchmark.py:7):
+``FastTreeParams``, ``fasttree_preparation`` and ``fasttree_decode``, with the
+reference's signatures and the reference's 13-slot auxiliary tuple.  The
+planner runs on the host (ft_b200.planner); the decode call goes to hand-written
+sm_100a CUDA through the C ABI (include/fasttree_b200.h).  There is no Triton
+and no CPU fallback: tensors must be CUDA tensors and the shared library must be
+present, otherwise the calls raise.
+"""
+import os
+import sys
+
+import torch
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if _PKG not in sys.path:
+    sys.path.insert(0, _PKG)
+
+from ft_b200 import engine as _engine      # noqa: E402
+from ft_b200 import planner as _planner    # noqa: E402
+
+
+class FastTreeParams:
+    """Hyper-parameter bag (reference: kernel_bench/fasttree.py:7-27).
+
+    ``alpha``/``beta``/``gamma`` weigh request-tile padding, KV-tile padding and
+    the cost of one more partial row; ``TSQs``/``TSKs`` are the per-phase request
+    and KV tile sizes; ``kv_group_num`` is query heads per KV head.  ``planner``
+    selects the splitter: ``"b200"`` (default) or ``"reference"`` (bit-identical
+    tables to the reference planner).  As in the reference, the planner may
+    overwrite ``TSQs``/``TSKs`` with the tile sizes it settled on."""
+    alpha = 0.66
+    beta = 0.33
+    gamma = 0.1
+    TSQs = [64, 16]
+    TSKs = [32, 128]
+    kv_group_num = 1
+    planner = "b200"
+    verbose = False
+
+    def set_values(self, alpha, beta, gamma):
+        self.alpha = alpha
+        self.beta = beta
+        self.gamma = gamma
+
+    def set_kv_group_num(self, kv_group_num):
+        self.kv_group_num = kv_group_num
+
+    def set_q_tile_sizes(self, TSQs):
+        self.TSQs = TSQs
+
+    def set_kv_tile_sizes(self, TSKs):
+        self.TSKs = TSKs
+
+    def set_planner(self, name):
+        if name not in ("b200", "reference"):
+            raise ValueError("planner must be 'b200' or 'reference'")
+        self.planner = name
+
+
+def build_plan(tree_info, KV_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, KV_SPLIT_SIZES,
+               para_threshs1, para_threshs2, params):
+    """Host-only part of :func:`fasttree_preparation`: returns an
+    ``ft_b200.planner.Plan`` of numpy tables."""
+    log = [] if params.verbose else None
+    if params.planner == "reference":
+        plan = _planner.plan_reference(tree_info, KV_ptrs, batch_size, num_kv_heads, KV_SPLIT_SIZES,
+                                       para_threshs1, para_threshs2, params, log=log)
+    else:
+        plan = _planner.plan_b200(tree_info, KV_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, params)
+    if log:
+        for what, val in log:
+            print(f"{what}:", val)
+    return plan
+
+
+def fasttree_preparation(tree_info, KV_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim,
+                         KV_SPLIT_SIZES, para_threshs1, para_threshs2, params: FastTreeParams,
+                         device="cuda"):
+    """Plan the tree and upload the tables.  Returns ``(aux, node_assignments)``
+    where ``aux`` is the 13-tuple that is splatted into :func:`fasttree_decode`
+    (reference: kernel_bench/fasttree.py:99-110, 282-296): nine int32 tables,
+    ``mid_o [R,Hq,D]`` and ``mid_lse [R,Hq]`` fp32 scratch, ``phase_node_nums``
+    and ``phase_node_offsets``."""
+    plan = build_plan(tree_info, KV_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim,
+                      KV_SPLIT_SIZES, para_threshs1, para_threshs2, params)
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise ValueError("fasttree_preparation uploads to a CUDA device; the engine has no CPU path")
+    tabs = tuple(torch.from_numpy(t).to(dev) for t in plan.tables())
+    rows = plan.num_partial_rows
+    mid_o = torch.empty((rows, num_qo_heads, head_dim), dtype=torch.float32, device=dev)
+    mid_lse = torch.empty((rows, num_qo_heads), dtype=torch.float32, device=dev)
+    aux = tabs + (mid_o, mid_lse, list(plan.phase_node_nums), list(plan.phase_node_offsets))
+    return aux, plan.node_assignments
+
+
+def fasttree_decode(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, vnode_to_kv_lens,
+                    vnode_to_q_entries, vnode_to_q_offs, vnode_to_q_lens, req_to_vnode_entries,
+                    req_to_vnode_offs, req_to_vnode_lens, mid_o, mid_lse, phase_node_nums, phase_node_offsets,
+                    phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap=-1):
+    """One decode step of tree attention; writes ``o`` in place on the current
+    CUDA stream (reference: kernel_bench/fasttree.py:582-642).  ``logit_cap`` is
+    accepted and ignored, as in the reference (:603)."""
+    _engine.decode(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, vnode_to_kv_lens,
+                   vnode_to_q_entries, vnode_to_q_offs, vnode_to_q_lens, req_to_vnode_entries,
+                   req_to_vnode_offs, req_to_vnode_lens, mid_o, mid_lse, phase_node_nums, phase_node_offsets,
+                   phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap=logit_cap)

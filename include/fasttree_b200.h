@@ -1,0 +1,153 @@
+/*
+ * fasttree_b200 - C ABI of the B200 (sm_100a) tree-attention decode engine.
+ *
+ * The library replaces the device half of the FastTree artifact's decode path.
+ * Every entry point is `extern "C"`, takes plain device pointers, sizes and
+ * element strides, returns an int status (0 = ok, negative = error, text via
+ * ft_last_error()), never throws, never aborts and - unless its comment says
+ * otherwise - never allocates device memory: the caller owns all tensors, the
+ * plan tables and the partial-result scratch, exactly as in the reference
+ * (kernel_bench/fasttree.py:265-280, fasttree_sglang_plugin_v0_2_13/metadata.py:40-58).
+ *
+ * Reference interfaces replaced (paths inside PanZaifeng/FastTree-Artifact):
+ *   ft_decode   <- fasttree_decode            kernel_bench/fasttree.py:582-642
+ *                                             (= fasttree_sglang_plugin_v0_2_13/attn_kernels.py:288-348)
+ *   ft_stage1   <- _fasttree_decode_stage1    kernel_bench/fasttree.py:416-479 (kernel :299-413)
+ *   ft_stage2   <- _fasttree_decode_stage2    kernel_bench/fasttree.py:549-579 (kernel :482-546)
+ *   ft_bump_kv_lens <- prepare_for_fasttree_step
+ *                                             fasttree_sglang_plugin_v0_2_13/schedule.py:278-283
+ */
+#ifndef FASTTREE_B200_H_
+#define FASTTREE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Storage type of Q, K, V and O.  Accumulation and softmax are always fp32. */
+enum ft_dtype { FT_F16 = 0, FT_BF16 = 1, FT_F32 = 2 };
+
+/* Which stage-1 kernel family to use. */
+enum ft_path {
+  FT_PATH_AUTO = 0,    /* pick per launch from dtype / head_dim / rows per task */
+  FT_PATH_GENERIC = 1, /* scalar fp32 kernel: any dtype, head_dim <= 256 */
+  FT_PATH_MMA = 2,     /* mma.sync tensor-core kernel, 16-bit types, head_dim 64/128 */
+  FT_PATH_TCGEN05 = 3  /* tcgen05/TMEM kernel for 128-row tasks, 16-bit types, head_dim 128 */
+};
+
+/* Status codes. */
+enum ft_status {
+  FT_OK = 0,
+  FT_ERR_INVALID_ARGUMENT = -1, /* null pointer, negative size, bad stride ... */
+  FT_ERR_UNSUPPORTED = -2,      /* head_dim / dtype / alignment the chosen path cannot do */
+  FT_ERR_CUDA = -3,             /* a CUDA runtime call failed; see ft_last_error() */
+  FT_ERR_DEVICE_STATUS = -4,    /* a kernel flagged bad plan data (index out of range, wait ran out) */
+  FT_ERR_TOO_LARGE = -5         /* problem exceeds a fixed capacity of the entry point */
+};
+
+/* Bits of the device status word (ft_read_device_status). */
+enum ft_device_flag {
+  FT_DEV_BAD_KV_INDEX = 1,  /* a gathered K/V row index was outside [0, kv_rows) */
+  FT_DEV_BAD_Q_INDEX = 2,   /* a request id was outside [0, batch) */
+  FT_DEV_BAD_ROW_INDEX = 4, /* a partial-row id was outside [0, num_partial_rows) */
+  FT_DEV_WAIT_TIMEOUT = 8   /* a bounded barrier wait gave up */
+};
+
+/*
+ * One decode step over one layer.  Field meanings follow the positional
+ * arguments of the reference's fasttree_decode (kernel_bench/fasttree.py:582-604).
+ * All pointers are device pointers; strides are in ELEMENTS of the respective
+ * tensor; the innermost (head_dim) stride is 1.
+ */
+typedef struct ft_decode_args {
+  /* tensors -------------------------------------------------------------- */
+  const void* q;          /* [batch, num_qo_heads, head_dim]                    */
+  const void* k_buffer;   /* [kv_rows, num_kv_heads, head_dim] (KV pool / tree) */
+  const void* v_buffer;   /* same shape as k_buffer                            */
+  void* o;                /* [batch, num_qo_heads, head_dim], written          */
+  float* o_lse;           /* optional [batch, num_qo_heads] merged LSE, or NULL */
+  int32_t dtype;          /* enum ft_dtype                                     */
+  int32_t batch;
+  int32_t num_qo_heads;
+  int32_t num_kv_heads;
+  int32_t head_dim;
+  int32_t path;           /* enum ft_path                                      */
+  int64_t kv_rows;
+  int64_t q_stride0, q_stride1;
+  int64_t k_stride0, k_stride1;
+  int64_t v_stride0, v_stride1;
+  int64_t o_stride0, o_stride1;
+  /* plan tables (int32, device) ------------------------------------------ */
+  const int32_t* vnode_to_kv_entries; /* K/V row ids; in the serving path this is the flat req_to_token table */
+  int64_t kv_entries_len;             /* number of readable entries                       */
+  const int32_t* vnode_to_kv_offs;    /* [num_vnodes] start of the vnode's row-id run     */
+  const int32_t* vnode_to_kv_lens;    /* [num_vnodes]                                     */
+  const int32_t* vnode_to_q_entries;  /* [num_partial_rows] request id of partial row r   */
+  const int32_t* vnode_to_q_offs;     /* [num_vnodes] first partial row of the vnode      */
+  const int32_t* vnode_to_q_lens;     /* [num_vnodes] requests (= partial rows) in it     */
+  const int32_t* req_to_vnode_entries;/* partial-row ids grouped by request               */
+  const int32_t* req_to_vnode_offs;   /* [batch]                                          */
+  const int32_t* req_to_vnode_lens;   /* [batch]                                          */
+  int64_t num_partial_rows;
+  int32_t phase_node_nums[2];         /* vnodes per phase (reference: big / small request tiles) */
+  int32_t phase_node_offsets[2];
+  int32_t phase_q_tile_sizes[2];      /* accepted for signature compatibility; the kernels size themselves from q_lens */
+  int32_t phase_kv_tile_sizes[2];
+  /* scratch (caller-owned) ------------------------------------------------ */
+  float* mid_o;                       /* [num_partial_rows, num_qo_heads, head_dim] */
+  float* mid_lse;                     /* [num_partial_rows, num_qo_heads]           */
+  int64_t mid_o_stride0, mid_o_stride1;
+  int64_t mid_lse_stride0;
+  /* scalars --------------------------------------------------------------- */
+  float sm_scale;
+  float logit_cap;                    /* accepted and ignored, as in the reference (fasttree.py:603) */
+  void* stream;                       /* cudaStream_t                               */
+} ft_decode_args;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int ft_version(void);
+
+/* sizeof(ft_decode_args) as compiled into the library, for bindings to check
+ * their mirror of the struct against. */
+int ft_decode_args_size(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* ft_last_error(void);
+
+/* Stage 1 + stage 2 on args->stream; no host synchronisation.
+ * Replaces fasttree_decode (kernel_bench/fasttree.py:582-642). */
+int ft_decode(const ft_decode_args* args);
+
+/* Partial attention of every vnode into mid_o / mid_lse (normalised partial
+ * outputs and log(sum)+max, the reference's convention).
+ * Replaces _fasttree_decode_stage1 (kernel_bench/fasttree.py:416-479). */
+int ft_stage1(const ft_decode_args* args);
+
+/* Log-sum-exp merge of each request's partial rows into o (and o_lse).
+ * Replaces _fasttree_decode_stage2 (kernel_bench/fasttree.py:549-579). */
+int ft_stage2(const ft_decode_args* args);
+
+/* vnode_to_kv_lens[last_vnodes[i]] += 1 for i < n, on the device: the token
+ * just generated joins each request's last private KV chunk.
+ * Replaces prepare_for_fasttree_step (fasttree_sglang_plugin_v0_2_13/schedule.py:278-283). */
+int ft_bump_kv_lens(int32_t* vnode_to_kv_lens, const int32_t* last_vnodes, int32_t n, void* stream);
+
+/* Synchronises `stream`, copies the device status word of the current device
+ * to *flags (bits of enum ft_device_flag) and clears it.  Kernels only ever
+ * OR bits into the word when they meet bad plan data; they skip the access
+ * instead of faulting. */
+int ft_read_device_status(void* stream, int32_t* flags);
+
+/* Number of kernels this library has launched from the calling process. */
+int64_t ft_launch_count(void);
+
+/* Name of the stage-1 kernel family ft_stage1 would use for these arguments
+ * ("generic", "mma", "tcgen05"), or NULL with ft_last_error() set. */
+const char* ft_stage1_path_name(const ft_decode_args* args);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FASTTREE_B200_H_ */

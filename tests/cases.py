@@ -64,7 +64,7 @@ DECODE_CASES = {
     "mini3_fp32": ("1,3,7", "70,33,21", 8, 2, 128, "fp32", 7, [16, 4], 1.0),
     "mini3_fp16": ("1,3,7", "70,33,21", 8, 2, 128, "fp16", 7, [16, 4], 1.0),
     "mini3_bf16_as_fp32": ("1,3,7", "70,33,21", 8, 2, 128, "bf16", 7, [16, 4], 0.5),
-    "merge_d64_fp16": ("1,2,20", "8,40,19", 4, 4, 64, "fp16", 11, [64, 16], 1.0),
+    "merge_d64_fp16": ("1,2,16", "8,40,19", 8, 2, 64, "fp16", 11, [16, 4], 1.0),
     "rand3_fp16": (None, dict(levels=3, seed=5, max_children=6, lam=2.0, len_lo=3, len_hi=90),
                    16, 4, 128, "fp16", 21, [16, 4], 1.0),
     "cfg2_fp16": ("1,64", "4096,256", 32, 8, 128, "fp16", 2024, [16, 4], 1.0),

@@ -254,9 +254,9 @@ def main():
         tree = ref_tree_from_spec(ref_tree, ref_gen, "1,3,7", "70,33,21", tmp)
         save_decode("mini3_bf16_as_fp32", run_ref_decode(ref_ft, ref_in, tree, 8, 2, 128, torch.bfloat16, 7,
                                                          [16, 4], q_scale=0.5, compute_dtype=torch.float32))
-        # merges (assignment 1) happen on this one: a short root under wide fan-out, MHA, head_dim 64
-        tree = ref_tree_from_spec(ref_tree, ref_gen, "1,2,20", "8,40,19", tmp)
-        save_decode("merge_d64_fp16", run_ref_decode(ref_ft, ref_in, tree, 4, 4, 64, torch.float16, 11, [64, 16]))
+        # two children carry the short root's KV (assignment 1) on this one; head_dim 64
+        tree = ref_tree_from_spec(ref_tree, ref_gen, "1,2,16", "8,40,19", tmp)
+        save_decode("merge_d64_fp16", run_ref_decode(ref_ft, ref_in, tree, 8, 2, 64, torch.float16, 11, [16, 4]))
         # irregular tree, small contexts
         onodes = ref_inputs.random_tree(3, 5, max_children=6, lam=2.0, len_lo=3, len_hi=90)
         tree = ref_tree_from_oracle_nodes(ref_tree, onodes, tmp)

@@ -1,0 +1,295 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against
+(a) the outputs the reference's own kernels wrote (golden fixtures),
+(b) the CPU oracle on the same seeded inputs, and
+(c) size-independent properties at the benchmark sizes.
+
+Tolerances (stated once): 16-bit storage - max-abs error <= 2e-3 against the
+fp32 ground truth and against the reference's output; partial and merged LSE
+within 1e-4 relative (+1e-5 absolute).  fp32 storage - 2e-5.
+"""
+import numpy as np
+import pytest
+import torch
+
+import cases
+import gpu_utils
+from oracle import ref_attention, ref_inputs
+
+import fasttree
+from ft_b200 import engine, lib
+
+pytestmark = pytest.mark.gpu
+
+ATOL16 = 2e-3
+ATOL32 = 2e-5
+
+
+def atol_for(dtype):
+    return ATOL32 if dtype == torch.float32 else ATOL16
+
+
+def paths_for(c):
+    fast = c["dtype"] != torch.float32 and c["d"] in (64, 128)
+    return ["generic", "mma"] if fast else ["generic"]
+
+
+SMALL = [n for n in cases.DECODE_CASES if n != "cfg2_fp16"]
+
+
+@pytest.mark.parametrize("name", SMALL)
+@pytest.mark.parametrize("planner", ["reference", "b200"])
+def test_golden_cases_match_reference_output(name, planner):
+    c = cases.build_decode_case(name)
+    gold = c["gold"]
+    scale = 1.0 / c["d"] ** 0.5
+    truth, truth_lse = ref_attention.per_leaf_attention(c["nodes"], c["ptrs"], c["q"], c["k"], c["v"], scale)
+    tol = atol_for(c["dtype"])
+    for path in paths_for(c):
+        run, out = gpu_utils.run_case(c, planner=planner, path=path)
+        assert lib.read_device_status() == 0
+        assert torch.isfinite(out).all(), (name, planner, path)
+        assert (out - torch.from_numpy(gold["o"])).abs().max().item() <= tol, (name, planner, path)
+        assert (out - truth).abs().max().item() <= tol, (name, planner, path)
+        np.testing.assert_allclose(run.o_lse.cpu().numpy(), truth_lse.numpy(), rtol=1e-4, atol=1e-5)
+        if planner == "reference":
+            # same plan as the reference -> the partial buffers are comparable row by row
+            for tname, t in zip(cases.TABLES, run.aux[:9]):
+                np.testing.assert_array_equal(t.cpu().numpy(), gold[tname], err_msg=tname)
+            np.testing.assert_allclose(run.mid_lse.cpu().numpy(), gold["mid_lse"], rtol=1e-4, atol=1e-5)
+            assert np.abs(run.mid_o.cpu().numpy() - gold["mid_o"]).max() <= tol
+
+
+@pytest.mark.parametrize("planner", ["reference", "b200"])
+def test_bf16_case(planner):
+    """bf16 storage; the fixture holds the reference kernels' result on the exact
+    fp32 up-cast of the same bf16 tensors."""
+    c = cases.build_decode_case("mini3_bf16_as_fp32")
+    assert c["dtype"] == torch.bfloat16
+    for path in ("generic", "mma"):
+        _, out = gpu_utils.run_case(c, planner=planner, path=path)
+        # the output itself is rounded to bf16 (8 bits of mantissa): allow one bf16 ulp of the largest value
+        bound = ATOL16 + float(np.abs(c["gold"]["o"]).max()) * 2 ** -8
+        assert (out - torch.from_numpy(c["gold"]["o"])).abs().max().item() <= bound, path
+
+
+@pytest.mark.parametrize("planner", ["reference", "b200"])
+def test_full_size_fp16_config(planner):
+    """Benchmark configuration 2 (N=[1,64], C=[4096,256], 32/8 heads, fp16) at full
+    size against the reference kernels' output and the fp32 ground truth."""
+    c = cases.build_decode_case("cfg2_fp16")
+    truth, truth_lse = ref_attention.per_leaf_attention(c["nodes"], c["ptrs"], c["q"], c["k"], c["v"],
+                                                        1.0 / 128 ** 0.5)
+    run, out = gpu_utils.run_case(c, planner=planner, path="auto")
+    assert lib.read_device_status() == 0
+    assert (out - truth).abs().max().item() <= ATOL16
+    assert (out - torch.from_numpy(c["gold"]["o"].astype(np.float32))).abs().max().item() <= ATOL16
+    np.testing.assert_allclose(run.o_lse.cpu().numpy(), truth_lse.numpy(), rtol=1e-4, atol=1e-5)
+    if planner == "reference":
+        np.testing.assert_allclose(run.mid_lse.cpu().numpy(), c["gold"]["mid_lse"], rtol=1e-4, atol=1e-5)
+    # the reference-signature entry point gives the same bits as the explicit call
+    again = run.decode_via_dropin()
+    assert torch.equal(again, out)
+
+
+def adhoc(sizes, lens, hq, hkv, d, dtype, seed, q_scale=1.0):
+    nodes = ref_inputs.layered_tree(sizes, lens)
+    q, k, v, ptrs, batch = ref_inputs.draw_qkv(nodes, hq, hkv, d, dtype, seed, q_scale)
+    return dict(nodes=nodes, q=q, k=k, v=v, ptrs=ptrs, batch=batch, hq=hq, hkv=hkv, d=d, dtype=dtype,
+                tsq=cases.q_tiles_for_group(hq // hkv))
+
+
+EDGE_TREES = [
+    # (level sizes, level lens, hq, hkv, d)           what it exercises
+    ([1], [1], 4, 4, 128),                            # single node, single token
+    ([1], [300], 8, 8, 128),                          # single node, several tiles + tail
+    ([1, 3, 9], [1, 1, 1], 16, 4, 128),               # one-token nodes
+    ([1, 5], [63, 65], 8, 2, 128),                    # kv_len = tile -+ 1
+    ([1, 5], [64, 128], 8, 2, 64),                    # exact tiles, head_dim 64
+    ([1, 15], [200, 7], 32, 8, 128),                  # 15 requests x G=4 = 60 rows: last row block ragged
+    ([1, 17], [130, 9], 32, 8, 128),                  # 17 requests -> two request tiles (16 + 1)
+    ([1, 3], [90, 40], 64, 8, 128),                   # G=8: 24 rows -> two warps per row block
+    ([1, 9], [150, 33], 24, 8, 128),                  # G=3: rows do not align with 16-row blocks
+    ([1, 2, 4], [40, 30, 20], 16, 16, 64),            # MHA, head_dim 64
+    ([1, 2], [700, 20], 128, 1, 128),                 # G=128: one request spans two 64-row blocks
+]
+
+
+@pytest.mark.parametrize("spec", EDGE_TREES, ids=lambda s: "n%s_c%s_h%d-%d_d%d" % (
+    "-".join(map(str, s[0])), "-".join(map(str, s[1])), s[2], s[3], s[4]))
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32], ids=["fp16", "bf16", "fp32"])
+def test_edge_shapes_against_oracle(spec, dtype):
+    sizes, lens, hq, hkv, d = spec
+    c = adhoc(sizes, lens, hq, hkv, d, dtype, seed=3, q_scale=0.5)
+    scale = 1.0 / d ** 0.5
+    truth, truth_lse = ref_attention.per_leaf_attention(c["nodes"], c["ptrs"], c["q"], c["k"], c["v"], scale)
+    tol = atol_for(dtype)
+    if dtype == torch.bfloat16:
+        tol += float(truth.abs().max()) * 2 ** -8     # output rounding to bf16
+    for planner in ("reference", "b200"):
+        for path in paths_for(c):
+            run, out = gpu_utils.run_case(c, planner=planner, path=path)
+            assert lib.read_device_status() == 0
+            assert (out - truth).abs().max().item() <= tol, (planner, path)
+            np.testing.assert_allclose(run.o_lse.cpu().numpy(), truth_lse.numpy(), rtol=1e-4, atol=2e-5)
+            # stage-1 partials against the oracle's per-vnode restatement on the very same plan
+            tabs = [t.cpu().numpy() for t in run.aux[:6]]
+            mid_o, mid_lse = ref_attention.stage1_partials(c["q"], c["k"], c["v"], *tabs, scale)
+            np.testing.assert_allclose(run.mid_lse.cpu().numpy(), mid_lse.numpy(), rtol=1e-4, atol=2e-5)
+            assert (run.mid_o.cpu() - mid_o).abs().max().item() <= tol
+
+
+def test_scattered_pool_rows_and_2d_index_table():
+    """Serving-style addressing: K/V rows live at arbitrary pool slots and the
+    row-id list is a 2-D int32 table (req_to_token) addressed by flat offsets."""
+    c = cases.build_decode_case("rand3_fp16")
+    run = gpu_utils.EngineRun(c["nodes"], c["ptrs"], c["batch"], c["q"], c["k"], c["v"], c["hq"], c["hkv"],
+                              c["d"], c["tsq"], planner="b200")
+    base = run.decode(path="mma")
+    rows = c["k"].shape[0]
+    g = torch.Generator().manual_seed(5)
+    pool_rows = rows + 37
+    slot_of = torch.randperm(pool_rows, generator=g)[:rows]
+    k_pool = torch.randn(pool_rows, c["hkv"], c["d"], generator=g).to(c["dtype"])
+    v_pool = torch.randn(pool_rows, c["hkv"], c["d"], generator=g).to(c["dtype"])
+    k_pool[slot_of] = c["k"]
+    v_pool[slot_of] = c["v"]
+    entries = run.aux[0].cpu()
+    remapped = torch.where(entries >= 0, slot_of[entries.clamp(min=0)].to(torch.int32), entries)
+    width = 64
+    pad = (-remapped.numel()) % width
+    table = torch.cat([remapped, torch.full((pad,), -1, dtype=torch.int32)]).view(-1, width).cuda()
+    aux = (table,) + run.aux[1:]
+    o = torch.empty_like(run.q)
+    for path in ("mma", "generic"):
+        o.fill_(float("nan"))
+        engine.decode(run.q, k_pool.cuda(), v_pool.cuda(), o, *aux, run.tiles[0], run.tiles[1], run.scale,
+                      path=path)
+        torch.cuda.synchronize()
+        assert lib.read_device_status() == 0
+        assert (o.float().cpu() - base).abs().max().item() <= (0 if path == "mma" else ATOL16)
+
+
+def test_strided_kv_buffers():
+    """K and V interleaved in one buffer: row stride and head stride are not the
+    packed ones; last axis stays contiguous (the reference passes strides 0 and 1
+    of each buffer, kernel_bench/fasttree.py:456-461)."""
+    c = cases.build_decode_case("mini3_fp16")
+    run = gpu_utils.EngineRun(c["nodes"], c["ptrs"], c["batch"], c["q"], c["k"], c["v"], c["hq"], c["hkv"],
+                              c["d"], c["tsq"], planner="b200")
+    base = run.decode(path="mma")
+    both = torch.stack([c["k"], c["v"]], dim=2).cuda()          # [rows, hkv, 2, d]
+    k_view, v_view = both[:, :, 0], both[:, :, 1]
+    assert k_view.stride(1) == 2 * c["d"]
+    o = torch.empty_like(run.q)
+    for path in ("mma", "generic"):
+        engine.decode(run.q, k_view, v_view, o, *run.aux, run.tiles[0], run.tiles[1], run.scale, path=path)
+        torch.cuda.synchronize()
+        assert (o.float().cpu() - base).abs().max().item() <= (0 if path == "mma" else ATOL16)
+
+
+def test_bad_plan_data_is_flagged_not_faulted():
+    """Out-of-range row ids are skipped and reported through the device status
+    word; the context stays usable."""
+    c = cases.build_decode_case("mini3_fp16")
+    run = gpu_utils.EngineRun(c["nodes"], c["ptrs"], c["batch"], c["q"], c["k"], c["v"], c["hq"], c["hkv"],
+                              c["d"], c["tsq"], planner="b200")
+    good = run.decode(path="mma")
+    assert lib.read_device_status() == 0
+    entries = run.aux[0]
+    saved = entries[3].item()
+    for path in ("mma", "generic"):
+        entries[3] = 10 ** 8
+        run.decode(path=path)
+        assert lib.read_device_status() & lib.FT_DEV_BAD_KV_INDEX
+        entries[3] = saved
+        assert lib.read_device_status() == 0
+        assert torch.equal(run.decode(path="mma"), good)
+    q_entries = run.aux[3]
+    saved = q_entries[0].item()
+    q_entries[0] = c["batch"] + 5
+    run.decode(path="mma")
+    assert lib.read_device_status() & lib.FT_DEV_BAD_Q_INDEX
+    q_entries[0] = saved
+    assert torch.equal(run.decode(path="mma"), good)
+
+
+def test_argument_errors():
+    c = cases.build_decode_case("mini3_fp16")
+    run = gpu_utils.EngineRun(c["nodes"], c["ptrs"], c["batch"], c["q"], c["k"], c["v"], c["hq"], c["hkv"],
+                              c["d"], c["tsq"], planner="b200")
+    args = [run.q, run.k, run.v, run.o, *run.aux, run.tiles[0], run.tiles[1], run.scale]
+    with pytest.raises(ValueError):                       # CPU tensor: no CPU path
+        engine.decode(run.q.cpu(), *args[1:])
+    with pytest.raises(ValueError):                       # mismatching dtypes
+        engine.decode(run.q.float(), *args[1:])
+    with pytest.raises(ValueError):                       # int64 table
+        engine.decode(*args[:5], run.aux[1].long(), *args[6:])
+    with pytest.raises(lib.FastTreeError) as err:          # fp32 cannot take the tensor-core path
+        engine.decode(run.q.float(), run.k.float(), run.v.float(), run.o.float(), *args[4:], path="mma")
+    assert err.value.code == -2
+    q96 = torch.zeros(c["batch"], c["hq"], 96, dtype=torch.float16, device="cuda")
+    kv96 = torch.zeros(run.k.shape[0], c["hkv"], 96, dtype=torch.float16, device="cuda")
+    mid96 = torch.zeros(run.mid_o.shape[0], c["hq"], 96, device="cuda")
+    with pytest.raises(lib.FastTreeError) as err:          # head_dim outside {16,32,64,128,256}
+        engine.decode(q96, kv96, kv96, torch.empty_like(q96), *run.aux[:9], mid96, run.aux[10], *args[15:])
+    assert err.value.code == -2
+
+
+def test_bump_kv_lens():
+    lens = torch.tensor([5, 6, 7, 8], dtype=torch.int32, device="cuda")
+    last = torch.tensor([3, 1], dtype=torch.int32, device="cuda")
+    engine.bump_kv_lens(lens, last)
+    torch.cuda.synchronize()
+    assert lens.tolist() == [5, 7, 7, 9]
+
+
+# ------------------------------------------------------------ benchmark sizes
+FULL = {
+    "cfg3": dict(sizes=[1, 16, 256], lens=[2048, 512, 64], hq=32, hkv=8, dtype=torch.bfloat16, q_scale=0.5),
+    "cfg4": dict(sizes=[1, 1024], lens=[16384, 32], hq=64, hkv=8, dtype=torch.bfloat16, q_scale=1.0),
+}
+
+
+def gpu_inputs(nodes, hq, hkv, d, dtype, seed, q_scale):
+    """Seeded inputs drawn on the GPU (sizes here are too large for the CPU draw
+    order to matter; the oracle reads them back for its sample)."""
+    batch = ref_inputs.assign_requests(nodes)
+    ptrs = ref_inputs.kv_prefix_sums(nodes)
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    k = torch.randn(ptrs[-1], hkv, d, generator=g, device="cuda", dtype=torch.float32).to(dtype)
+    v = torch.randn(ptrs[-1], hkv, d, generator=g, device="cuda", dtype=torch.float32).to(dtype)
+    q = (torch.randn(batch, hq, d, generator=g, device="cuda", dtype=torch.float32) * q_scale).to(dtype)
+    return q, k, v, ptrs, batch
+
+
+@pytest.mark.parametrize("name", sorted(FULL))
+def test_benchmark_sizes_properties(name):
+    """At full benchmark size: (1) a sample of requests against the fp32 oracle,
+    (2) both planners agree, (3) linearity in V: decode(V1 + V2) = decode(V1) + decode(V2)
+    because the softmax weights depend on Q and K only, (4) deterministic repeat."""
+    f = FULL[name]
+    d = 128
+    nodes = ref_inputs.layered_tree(f["sizes"], f["lens"])
+    q, k, v, ptrs, batch = gpu_inputs(nodes, f["hq"], f["hkv"], d, f["dtype"], 17, f["q_scale"])
+    tsq = cases.q_tiles_for_group(f["hq"] // f["hkv"])
+    runs = {pl: gpu_utils.EngineRun(nodes, ptrs, batch, q, k, v, f["hq"], f["hkv"], d, tsq, planner=pl)
+            for pl in ("b200", "reference")}
+    outs = {pl: r.decode() for pl, r in runs.items()}
+    assert lib.read_device_status() == 0
+    sample = [0, 1, batch // 2, batch - 1]
+    truth, truth_lse = ref_attention.per_leaf_attention(nodes, ptrs, q.cpu(), k.cpu(), v.cpu(), 1.0 / d ** 0.5,
+                                                        requests=sample)
+    tol = ATOL16 + float(truth.abs().max()) * 2 ** -8
+    for pl in outs:
+        assert (outs[pl][sample] - truth).abs().max().item() <= tol, pl
+        np.testing.assert_allclose(runs[pl].o_lse.cpu().numpy()[sample], truth_lse.numpy(), rtol=1e-4, atol=2e-5)
+    assert (outs["b200"] - outs["reference"]).abs().max().item() <= 2 * tol
+    r = runs["b200"]
+    assert torch.equal(r.decode(), outs["b200"])
+    v2 = torch.randn_like(v)
+    r.v = v2
+    o2 = r.decode()
+    r.v = (v.float() + v2.float()).to(f["dtype"])
+    o12 = r.decode()
+    lin_tol = 3 * tol + float(o12.abs().max()) * 2 ** -7       # V1+V2 is itself rounded to bf16
+    assert (o12 - (outs["b200"] + o2)).abs().max().item() <= lin_tol

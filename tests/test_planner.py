@@ -1,0 +1,183 @@
+"""Host planner tests (CPU only): the reference-compatible splitter against the
+reference's own tables, and structural properties of the B200 splitter."""
+import numpy as np
+import pytest
+
+import cases
+from oracle import ref_inputs
+
+import fasttree                      # the drop-in module (fasttree-artifact_b200/kernel_bench)
+from ft_b200 import planner
+from kv_tree_simple import KVTreeNode, retrive_from_file, validate_tree
+import tree_generation
+
+PLANNER_GOLD = cases.load_planner_golden()
+
+
+def product_tree(onodes):
+    """Oracle tree -> the product's node type, with requests assigned by the
+    reference rule (leaves in id order)."""
+    out = [KVTreeNode(n.parent, n.id, n.seqlen, n.num_children) for n in onodes]
+    nreq = 0
+    for nd in out:
+        if nd.num_children == 0:
+            cur = nd.id
+            while cur != -1:
+                out[cur].requests.append(nreq)
+                cur = out[cur].parent
+            nreq += 1
+    ptrs = [0]
+    for nd in out:
+        ptrs.append(ptrs[-1] + nd.seqlen)
+    return out, nreq, ptrs
+
+
+def make_params(hq, hkv, tsq, abg=(0.66, 0.33, 0.1), planner_name="reference"):
+    p = fasttree.FastTreeParams()
+    p.set_values(*abg)
+    p.set_q_tile_sizes(list(tsq))
+    p.set_kv_tile_sizes([32, 32])
+    p.set_kv_group_num(hq // hkv)
+    p.set_planner(planner_name)
+    return p
+
+
+@pytest.mark.parametrize("key", sorted(PLANNER_GOLD))
+def test_reference_mode_is_bit_identical_to_reference_planner(key):
+    gold = PLANNER_GOLD[key]
+    onodes, hq, hkv, kw = cases.tree_for_planner_key(key)
+    tree, batch, ptrs = product_tree(onodes)
+    p = make_params(hq, hkv, cases.q_tiles_for_group(hq // hkv), abg=kw["abg"])
+    plan = fasttree.build_plan(tree, ptrs, batch, hq, hkv, 128, kw["split"], [132, 528], [132, 132], p)
+    assert "".join(map(str, plan.node_assignments)) == gold["assign"]
+    assert plan.phase_node_nums == gold["phase_node_nums"]
+    assert plan.phase_node_offsets == gold["phase_node_offsets"]
+    assert list(p.TSQs) == gold["tsq_after"] and list(p.TSKs) == gold["tsk_after"]
+    names = ["kv_entries", "kv_offs", "kv_lens", "q_entries", "q_offs", "q_lens",
+             "r2v_entries", "r2v_offs", "r2v_lens"]
+    for name, arr in zip(names, plan.tables()):
+        assert arr.dtype == np.int32, name
+        assert arr.size == gold[name]["n"], name
+        assert cases.sha_np(arr) == gold[name]["sha256"], name
+
+
+def check_plan_covers_every_path_once(tree, ptrs, batch, plan):
+    """Every request must see each token of its root->leaf path in exactly one
+    of its partial rows, and nothing else."""
+    kv_entries = plan.vnode_to_kv_entries
+    row_tokens = {}
+    for vn in range(plan.num_vnodes):
+        ko, kl = int(plan.vnode_to_kv_offs[vn]), int(plan.vnode_to_kv_lens[vn])
+        qo, ql = int(plan.vnode_to_q_offs[vn]), int(plan.vnode_to_q_lens[vn])
+        assert kl > 0 and ql > 0
+        toks = kv_entries[ko:ko + kl]
+        assert toks.min() >= 0
+        for row in range(qo, qo + ql):
+            assert row not in row_tokens, "two vnodes write the same partial row"
+            row_tokens[row] = toks
+    assert len(row_tokens) == plan.num_partial_rows
+    paths = {}
+    for nd in tree:
+        if nd.num_children == 0:
+            chain, cur = [], nd.id
+            while cur != -1:
+                chain.append(cur)
+                cur = tree[cur].parent
+            paths[nd.requests[0]] = chain
+    for r in range(batch):
+        off, n = int(plan.req_to_vnode_offs[r]), int(plan.req_to_vnode_lens[r])
+        rows = plan.req_to_vnode_entries[off:off + n]
+        assert all(plan.vnode_to_q_entries[row] == r for row in rows)
+        seen = np.sort(np.concatenate([row_tokens[int(row)] for row in rows]))
+        want = np.sort(np.concatenate([np.arange(ptrs[n_], ptrs[n_ + 1]) for n_ in paths[r]]))
+        np.testing.assert_array_equal(seen, want)
+    # phases: a stable split on the small request tile, contiguous ranges
+    n0, n1 = plan.phase_node_nums
+    assert plan.phase_node_offsets == [0, n0] and n0 + n1 == plan.num_vnodes
+
+
+B200_TREES = {
+    "cfg1": ([1, 4], [512, 64], 8, 2),
+    "cfg2": ([1, 64], [4096, 256], 32, 8),
+    "cfg3": ([1, 16, 256], [2048, 512, 64], 32, 8),
+    "cfg3_one_kv_head": ([1, 16, 256], [2048, 512, 64], 4, 1),
+    "deep_short": ([1, 2, 4, 8, 16, 32, 64], [16, 16, 16, 16, 16, 16, 16], 32, 32),
+    "single_node": ([1], [300], 8, 8),
+    "one_token_nodes": ([1, 3, 9], [1, 1, 1], 16, 4),
+}
+
+
+@pytest.mark.parametrize("name", sorted(B200_TREES))
+def test_b200_plan_is_valid_and_deterministic(name):
+    sizes, lens, hq, hkv = B200_TREES[name]
+    plans = []
+    for _ in range(2):
+        tree, batch, ptrs = product_tree(ref_inputs.layered_tree(sizes, lens))
+        p = make_params(hq, hkv, [16, 4], planner_name="b200")
+        plan = fasttree.build_plan(tree, ptrs, batch, hq, hkv, 128, [1024, 128], [132, 528], [132, 132], p)
+        check_plan_covers_every_path_once(tree, ptrs, batch, plan)
+        plans.append(plan)
+    for a, b in zip(plans[0].tables(), plans[1].tables()):
+        np.testing.assert_array_equal(a, b)
+    assert plans[0].node_assignments == plans[1].node_assignments
+    group = hq // hkv
+    assert int(plans[0].vnode_to_q_lens.max()) * group <= max(64, group)
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_b200_plan_on_random_trees(seed):
+    tree, batch, ptrs = product_tree(ref_inputs.random_tree(4, seed, len_lo=1, len_hi=300))
+    p = make_params(32, 8, [16, 4], planner_name="b200")
+    plan = fasttree.build_plan(tree, ptrs, batch, 32, 8, 128, [1024, 128], [132, 528], [132, 132], p)
+    check_plan_covers_every_path_once(tree, ptrs, batch, plan)
+
+
+def test_b200_plan_splits_long_prefix_and_keeps_leaves_whole():
+    tree, batch, ptrs = product_tree(ref_inputs.layered_tree([1, 64], [4096, 256]))
+    p = make_params(32, 8, [16, 4], planner_name="b200")
+    plan = fasttree.build_plan(tree, ptrs, batch, 32, 8, 128, [1024, 128], [132, 528], [132, 132], p)
+    lens = plan.vnode_to_kv_lens
+    assert (lens[plan.vnode_to_q_lens == 1] == 256).all()          # leaves: one task each
+    assert lens.max() < 4096 and lens.max() % 64 == 0              # the shared prefix is cut on tile boundaries
+    # long tasks first inside each phase
+    n0 = plan.phase_node_nums[0]
+    assert (np.diff(lens[:n0]) <= 0).all() and (np.diff(lens[n0:]) <= 0).all()
+    # far fewer partial rows than the reference plan for the same tree (2176)
+    assert plan.num_partial_rows < 1000
+
+
+def test_reference_mode_covers_every_path_once():
+    tree, batch, ptrs = product_tree(ref_inputs.layered_tree([1, 2, 16], [8, 40, 19]))
+    p = make_params(8, 2, [16, 4])
+    plan = fasttree.build_plan(tree, ptrs, batch, 8, 2, 64, [1024, 128], [132, 528], [132, 132], p)
+    assert sum(plan.node_assignments) > 0          # this tree triggers KV-carrying children
+    check_plan_covers_every_path_once(tree, ptrs, batch, plan)
+
+
+def test_tree_file_tools_match_reference_format(tmp_path):
+    rows = tree_generation.generate_tree([1, 3, 7], [70, 33, 21])
+    path = tmp_path / "tree.txt"
+    tree_generation.save_tree(rows, str(path))
+    onodes = ref_inputs.layered_tree([1, 3, 7], [70, 33, 21])
+    ref_path = tmp_path / "ref.txt"
+    ref_inputs.write_tree_file(onodes, ref_path)
+    assert path.read_text() == ref_path.read_text()
+    nodes = retrive_from_file(str(path))
+    validate_tree(nodes)
+    assert [(n.parent, n.id, n.seqlen, n.num_children) for n in nodes] == [tuple(r) for r in rows]
+    tree_generation.main(["-n", "1,2", "-l", "5,6", "-o", str(tmp_path / "cli.txt")])
+    assert (tmp_path / "cli.txt").read_text() == "3\n-1 0 5 2\n0 1 6 0\n0 2 6 0\n"
+    with pytest.raises(ValueError):
+        tree_generation.generate_tree([1, 2], [3])
+
+
+def test_validate_tree_rejects_bad_trees():
+    nodes = [KVTreeNode(-1, 0, 4, 1), KVTreeNode(0, 1, 4, 0)]
+    validate_tree(nodes)
+    nodes[1].parent = 1
+    with pytest.raises(ValueError):
+        validate_tree(nodes)
+    nodes[1].parent = 0
+    nodes[0].num_children = 2
+    with pytest.raises(ValueError):
+        validate_tree(nodes)
