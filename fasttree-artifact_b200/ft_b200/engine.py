@@ -130,7 +130,7 @@ def _cached_args(tensors, rest, path, o_lse):
     shape, strides), so a steady-state decode loop pays for one dict lookup."""
     q = tensors[0]
     stream = torch.cuda.current_stream(q.device).cuda_stream
-    key = (tuple((t.data_ptr(), tuple(t.shape), t.stride(0)) for t in tensors),
+    key = (q.dtype, tuple((t.data_ptr(), t.shape, t.stride()) for t in tensors),
            tuple(tuple(x) if isinstance(x, (list, tuple)) else x for x in rest), path,
            o_lse.data_ptr() if o_lse is not None else 0, stream)
     a = _ARG_CACHE.get(key)
