@@ -221,6 +221,8 @@ def main():
     ap.add_argument("--path", default="auto", choices=["auto", "generic", "mma", "tcgen05"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--ref-requests", type=int, default=16, help="requests per step of the CPU arm")
+    ap.add_argument("--prewarm-s", type=float, default=0.3, help="seconds of untimed steps before the warm-up (clock ramp)")
+    ap.add_argument("--no-graph", action="store_true", help="launch every timed step from Python instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -299,24 +301,60 @@ def main():
     sampler.start()
 
     # clock ramp-up and first-use costs (argument caches, NCCL channels), then W warm-up steps
-    t_end = time.perf_counter() + 0.3
+    t_end = time.perf_counter() + args.prewarm_s
     i = 0
     while time.perf_counter() < t_end:
         step(i)
         i += 1
         if i % 64 == 0:
             torch.cuda.synchronize()
-    for i in range(args.warmup):
-        step(i)
+    # The decode step is launch-bound from Python (a few microseconds of GPU work per call), so the
+    # timed loop replays a CUDA graph holding `cycle` consecutive steps (one full K/V rotation or more).
+    cycle = copies * max(1, -(-16 // copies))
+    graph, launch_mode = None, "eager"
+    launches_per_step = None
+    if not args.no_graph and args.steps >= cycle:
+        try:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for i in range(cycle):
+                    step(i)
+                side.synchronize()
+                l0 = lib.launch_count()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(cycle):
+                        step(i)
+                launches_per_step = (lib.launch_count() - l0) / cycle
+            torch.cuda.current_stream().wait_stream(side)
+            launch_mode = f"cuda graph of {cycle} steps, replayed"
+        except Exception as exc:                       # capture unsupported (e.g. a collective): launch eagerly
+            graph, launch_mode = None, f"eager (graph capture failed: {type(exc).__name__})"
+            torch.cuda.synchronize()
+
+    def run_steps(n):
+        if graph is None:
+            for i in range(n):
+                step(i)
+            return
+        for _ in range(n // cycle):
+            graph.replay()
+        for i in range(n % cycle):
+            step(i)
+
+    run_steps(max(args.warmup, cycle))
     fence()
     launches0 = lib.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
-    for i in range(args.steps):
-        step(i)
+    run_steps(args.steps)
     ev1.record()
     fence()
-    launches = lib.launch_count() - launches0
+    if graph is None:
+        launches = lib.launch_count() - launches0
+    else:
+        launches = int(round(launches_per_step * (args.steps // cycle) * cycle)) + (lib.launch_count() - launches0)
     elapsed_ms = ev0.elapsed_time(ev1)
     t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
     if world > 1:
@@ -392,7 +430,7 @@ def main():
                 "workload": f"{args.workload}: {desc}, {hq}q/{hkv}kv heads, head_dim {HEAD_DIM}, {dt}, "
                             f"one decode token per leaf",
                 "requests": batch, "tokens": tokens, "planner": args.planner, "stage1_path": s1_path,
-                "vnodes": n_vnodes, "partial_rows": n_rows, "plan_ms_host": plan_ms,
+                "vnodes": n_vnodes, "partial_rows": n_rows, "plan_ms_host": plan_ms, "launch": launch_mode,
                 "parallelism": f"tp{world} (kv heads sharded, {hkv_l} per GPU)" if world > 1 else "single GPU",
                 "l2": f"K/V rotated over {copies} copies = {copies * kv_bytes / 2 ** 20:.0f} MiB per GPU (> 126 MiB L2)",
             },

@@ -10,6 +10,7 @@
 #include "ft_common.cuh"
 #include "ft_stage1_generic.cuh"
 #include "ft_stage1_mma.cuh"
+#include "ft_stage1_narrow.cuh"
 #include "ft_stage2.cuh"
 
 namespace {
@@ -86,9 +87,9 @@ const char* mma_obstacle(const ft_decode_args* a) {
 int pick_path(const ft_decode_args* a) {
   if (a->path == FT_PATH_GENERIC) return FT_PATH_GENERIC;
   const char* why = mma_obstacle(a);
-  if (a->path == FT_PATH_MMA || a->path == FT_PATH_TCGEN05) {
+  if (a->path == FT_PATH_MMA || a->path == FT_PATH_TCGEN05 || a->path == FT_PATH_MMA_WIDE) {
     if (why != nullptr) return fail(FT_ERR_UNSUPPORTED, "tensor-core path unavailable: %s", why);
-    return FT_PATH_MMA;
+    return a->path == FT_PATH_MMA_WIDE ? FT_PATH_MMA_WIDE : FT_PATH_MMA;
   }
   if (a->path != FT_PATH_AUTO) return fail(FT_ERR_INVALID_ARGUMENT, "unknown path %d", a->path);
   return why == nullptr ? FT_PATH_MMA : FT_PATH_GENERIC;
@@ -146,6 +147,30 @@ int launch_mma(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
   return FT_OK;
 }
 
+template <typename T, int D>
+int launch_narrow(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
+  using C = ft::NarrowCfg<D, 2>;
+  static bool configured[64] = {};
+  int dev = 0;
+  FT_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    FT_CUDA_OK(cudaFuncSetAttribute(ft::stage1_narrow_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    C::SMEM_BYTES));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  dim3 grid(p.node_count, hkv);
+  ft::stage1_narrow_kernel<T, D><<<grid, 128, C::SMEM_BYTES, st>>>(p);
+  FT_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FT_OK;
+}
+
+template <typename T, int D>
+int launch_tensor(const ft::Stage1Params& p, int hkv, cudaStream_t st, int max_rows, bool wide_only) {
+  if (!wide_only && max_rows <= 16) return launch_narrow<T, D>(p, hkv, st);
+  return launch_mma<T, D>(p, hkv, st);
+}
+
 template <typename T>
 int launch_generic(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
   dim3 grid(p.node_count, hkv);
@@ -155,17 +180,21 @@ int launch_generic(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
   return FT_OK;
 }
 
-int launch_stage1_range(const ft_decode_args* a, int path, int offset, int count) {
+// max_rows: upper bound on query rows (requests x group) of the tasks in the range
+int launch_stage1_range(const ft_decode_args* a, int path, int offset, int count, int max_rows) {
   if (count <= 0) return FT_OK;
   ft::Stage1Params p = stage1_params(a);
   p.node_offset = offset;
   p.node_count = count;
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
   const int hkv = a->num_kv_heads;
-  if (path == FT_PATH_MMA) {
+  if (path == FT_PATH_MMA || path == FT_PATH_MMA_WIDE) {
+    const bool wide = path == FT_PATH_MMA_WIDE;
     if (a->dtype == FT_F16)
-      return a->head_dim == 128 ? launch_mma<__half, 128>(p, hkv, st) : launch_mma<__half, 64>(p, hkv, st);
-    return a->head_dim == 128 ? launch_mma<__nv_bfloat16, 128>(p, hkv, st) : launch_mma<__nv_bfloat16, 64>(p, hkv, st);
+      return a->head_dim == 128 ? launch_tensor<__half, 128>(p, hkv, st, max_rows, wide)
+                                : launch_tensor<__half, 64>(p, hkv, st, max_rows, wide);
+    return a->head_dim == 128 ? launch_tensor<__nv_bfloat16, 128>(p, hkv, st, max_rows, wide)
+                              : launch_tensor<__nv_bfloat16, 64>(p, hkv, st, max_rows, wide);
   }
   switch (a->dtype) {
     case FT_F16: return launch_generic<__half>(p, hkv, st);
@@ -211,7 +240,7 @@ const char* ft_stage1_path_name(const ft_decode_args* args) {
   if (rc != FT_OK) return nullptr;
   const int path = pick_path(args);
   if (path < 0) return nullptr;
-  return path == FT_PATH_MMA ? "mma" : "generic";
+  return path == FT_PATH_MMA ? "mma" : (path == FT_PATH_MMA_WIDE ? "mma_wide" : "generic");
 }
 
 int ft_stage1(const ft_decode_args* a) {
@@ -223,11 +252,18 @@ int ft_stage1(const ft_decode_args* a) {
   if (path < 0) return path;
   const int n0 = a->phase_node_nums[0], n1 = a->phase_node_nums[1];
   const int o0 = a->phase_node_offsets[0], o1 = a->phase_node_offsets[1];
-  // The kernels size themselves from each vnode's q_len, so two adjacent phases go out as one grid.
-  if (n0 > 0 && n1 > 0 && o1 == o0 + n0) return launch_stage1_range(a, path, o0, n0 + n1);
-  rc = launch_stage1_range(a, path, o0, n0);
+  const int group = a->num_qo_heads / a->num_kv_heads;
+  // A phase's request tile bounds the query rows of its tasks; a non-positive tile size means "unknown".
+  const int64_t r0 = a->phase_q_tile_sizes[0] > 0 ? (int64_t)a->phase_q_tile_sizes[0] * group : 1 << 30;
+  const int64_t r1 = a->phase_q_tile_sizes[1] > 0 ? (int64_t)a->phase_q_tile_sizes[1] * group : 1 << 30;
+  const int rows0 = (int)(r0 < (1 << 30) ? r0 : (1 << 30)), rows1 = (int)(r1 < (1 << 30) ? r1 : (1 << 30));
+  const bool same_kernel = path == FT_PATH_GENERIC || path == FT_PATH_MMA_WIDE || ((rows0 > 16) == (rows1 > 16));
+  // Adjacent phases that want the same kernel go out as one grid.
+  if (n0 > 0 && n1 > 0 && o1 == o0 + n0 && same_kernel)
+    return launch_stage1_range(a, path, o0, n0 + n1, rows0 > rows1 ? rows0 : rows1);
+  rc = launch_stage1_range(a, path, o0, n0, rows0);
   if (rc != FT_OK) return rc;
-  return launch_stage1_range(a, path, o1, n1);
+  return launch_stage1_range(a, path, o1, n1, rows1);
 }
 
 int ft_stage2(const ft_decode_args* a) {

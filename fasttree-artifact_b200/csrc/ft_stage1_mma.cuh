@@ -10,9 +10,9 @@
 // memory-bound shape of leaf and low-fan-out nodes.
 //
 // K/V rows are gathered by row id (vnode_to_kv_entries) with 16-byte cp.async
-// copies into a 3-stage shared-memory ring; every 256-byte row is XOR-swizzled
-// at 16-byte granularity so that ldmatrix reads are bank-conflict free.  Each
-// KV byte is read from global memory once per (vnode, 64-row block).
+// copies into a 3-stage shared-memory ring (KvPipe); every 256-byte row is
+// XOR-swizzled at 16-byte granularity so that ldmatrix reads are bank-conflict
+// free.  Each KV byte is read from global memory once per (vnode, 64-row block).
 //
 // Arithmetic follows kernel_bench/fasttree.py:360-413: scores scaled after the
 // dot product in fp32, online softmax, probabilities rounded to the storage
@@ -100,9 +100,117 @@ struct MmaCfg {
   static constexpr int PIPE_BYTES = STAGES * 2 * STAGE_BYTES;
   static constexpr int OSTRIDE = D + 4;         // floats per staged output row
   static constexpr int EPI_BYTES = 4 * 16 * OSTRIDE * 4 + 2 * 4 * 16 * 4;
-  static constexpr int SMEM_BYTES = Q_BYTES + (PIPE_BYTES > EPI_BYTES ? PIPE_BYTES : EPI_BYTES);
+  static constexpr int WIDE_IDXB = 128;         // row-id block of the wide kernel (2 x 512 B: all the room two CTAs/SM leave)
+  static constexpr int WIDE_IDX_BYTES = 2 * WIDE_IDXB * 4;
+  static constexpr int SMEM_BYTES = Q_BYTES + WIDE_IDX_BYTES + (PIPE_BYTES > EPI_BYTES ? PIPE_BYTES : EPI_BYTES);
   __device__ static __forceinline__ uint32_t swz(int row, int chunk) {
     return static_cast<uint32_t>(row * ROWB + ((chunk ^ (row & 7)) << 4));
+  }
+};
+
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ int lds_s32(uint32_t addr) {
+  int v;
+  asm volatile("ld.shared.s32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+  return v;
+}
+
+// Gathered K/V streaming for one (vnode chunk, kv head): a ring of STAGES K/V
+// tiles filled with 16-byte cp.async copies, fed by a two-block ring of row
+// ids in shared memory.  The row ids are themselves fetched with cp.async, a
+// whole block (IDXB tokens) at a time and one block ahead of use: a plain
+// global load issued next to ~100 KB of outstanding tile copies only returns
+// after those have drained, which stalls the issue of the following tile.
+template <typename T, int D, int IDXB>
+struct KvPipe {
+  using C = MmaCfg<D>;
+  static constexpr int TPB = IDXB / C::TILE;     // tiles per row-id block
+  static constexpr int IDX_BYTES = 2 * IDXB * 4;
+  const Stage1Params& p;
+  const T* kbase;
+  const T* vbase;
+  uint32_t idx_sm, pipe_sm;
+  int kv_off, kv_len, ntiles, tid, ld_c, ld_r;
+
+  __device__ __forceinline__ KvPipe(const Stage1Params& p_, int kvh, int kv_off_, int kv_len_, uint32_t idx_sm_,
+                                    uint32_t pipe_sm_)
+      : p(p_), idx_sm(idx_sm_), pipe_sm(pipe_sm_), kv_off(kv_off_), kv_len(kv_len_) {
+    tid = threadIdx.x;
+    ld_c = tid % C::CPR;
+    ld_r = tid / C::CPR;
+    ntiles = (kv_len + C::TILE - 1) / C::TILE;
+    kbase = reinterpret_cast<const T*>(p.k) + (int64_t)kvh * p.k_s1 + ld_c * 8;
+    vbase = reinterpret_cast<const T*>(p.v) + (int64_t)kvh * p.v_s1 + ld_c * 8;
+  }
+  // row ids of tokens [b*IDXB, (b+1)*IDXB) -> ring slot b&1 (joins the caller's open cp.async group)
+  __device__ __forceinline__ void issue_idx_block(int b) {
+    const uint32_t dst = idx_sm + (b & 1) * IDXB * 4;
+#pragma unroll
+    for (int i = 0; i < IDXB / C::THREADS; ++i) {
+      const int t = i * C::THREADS + tid;
+      const int pos = b * IDXB + t;
+      const int64_t e = (int64_t)kv_off + pos;
+      if (pos < kv_len && e >= 0 && e < p.kv_entries_len) cp_async4(dst + t * 4, p.kv_entries + e);
+    }
+  }
+  // blocks 0 and 1, waited for; call once before the first tile
+  __device__ __forceinline__ void prime_indices() {
+    issue_idx_block(0);
+    if (IDXB < kv_len) issue_idx_block(1);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+  }
+  // K/V rows of tile `tile` -> stage tile % STAGES (joins the open group)
+  __device__ __forceinline__ void issue_tile(int tile) {
+    const uint32_t k_sm = pipe_sm + (tile % C::STAGES) * 2 * C::STAGE_BYTES;
+    const uint32_t v_sm = k_sm + C::STAGE_BYTES;
+    const uint32_t ring = idx_sm + ((tile / TPB) & 1) * IDXB * 4 + (tile % TPB) * C::TILE * 4;
+#pragma unroll
+    for (int ps = 0; ps < C::PASSES; ++ps) {
+      const int r = ps * C::TPP + ld_r;
+      const int pos = tile * C::TILE + r;
+      int64_t row = -1;
+      if (pos < kv_len) {
+        row = lds_s32(ring + r * 4);
+        if (row < 0 || row >= p.kv_rows || (int64_t)kv_off + pos >= p.kv_entries_len) {
+          flag_error(FT_DEV_BAD_KV_INDEX);
+          row = -1;
+        }
+      }
+      const bool ok = row >= 0;
+      if (!ok) row = 0;
+      cp_async16(k_sm + C::swz(r, ld_c), kbase + row * p.k_s0, ok);
+      cp_async16(v_sm + C::swz(r, ld_c), vbase + row * p.v_s0, ok);
+    }
+  }
+  // tiles 0 .. STAGES-2, one group each
+  __device__ __forceinline__ void prologue() {
+#pragma unroll
+    for (int s = 0; s < C::STAGES - 1; ++s) {
+      if (s < ntiles) issue_tile(s);
+      cp_async_commit();
+    }
+  }
+  // top of iteration j: tile j has landed; refill the stage freed by tile j-1
+  __device__ __forceinline__ void advance(int j) {
+    cp_async_wait<C::STAGES - 2>();
+    __syncthreads();
+    const int nt = j + C::STAGES - 1;
+    if (nt < ntiles) {
+      issue_tile(nt);
+      // the first tile of a row-id block is going out: the block before it is dead, refill its slot
+      if (nt % TPB == 0 && nt >= TPB && (nt / TPB + 1) * IDXB < kv_len) issue_idx_block(nt / TPB + 1);
+    }
+    cp_async_commit();
+  }
+  __device__ __forceinline__ uint32_t k_stage(int j) const { return pipe_sm + (j % C::STAGES) * 2 * C::STAGE_BYTES; }
+  __device__ __forceinline__ uint32_t v_stage(int j) const { return k_stage(j) + C::STAGE_BYTES; }
+  __device__ __forceinline__ void drain() {
+    cp_async_wait<0>();
+    __syncthreads();
   }
 };
 
@@ -199,8 +307,9 @@ __global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
   using C = MmaCfg<D>;
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t q_sm = smem_u32(smem);
-  const uint32_t pipe_sm = q_sm + C::Q_BYTES;
-  float* epi_o = reinterpret_cast<float*>(smem + C::Q_BYTES);
+  const uint32_t idx_sm = q_sm + C::Q_BYTES;
+  const uint32_t pipe_sm = idx_sm + C::WIDE_IDX_BYTES;
+  float* epi_o = reinterpret_cast<float*>(smem + C::Q_BYTES + C::WIDE_IDX_BYTES);
   float* epi_m = epi_o + 4 * 16 * C::OSTRIDE;
   float* epi_l = epi_m + 4 * 16;
 
@@ -216,37 +325,7 @@ __global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
   const int ntiles = (kv_len + C::TILE - 1) / C::TILE;
   const int ld_c = tid % C::CPR, ld_r = tid / C::CPR;
 
-  const T* __restrict__ kbase = reinterpret_cast<const T*>(p.k) + (int64_t)kvh * p.k_s1 + ld_c * 8;
-  const T* __restrict__ vbase = reinterpret_cast<const T*>(p.v) + (int64_t)kvh * p.v_s1 + ld_c * 8;
-
-  auto load_idx = [&](int tile, int (&idx)[C::PASSES]) {
-#pragma unroll
-    for (int ps = 0; ps < C::PASSES; ++ps) {
-      const int pos = tile * C::TILE + ps * C::TPP + ld_r;
-      int v = -1;
-      if (pos < kv_len) {
-        const int64_t e = (int64_t)kv_off + pos;
-        if (e >= 0 && e < p.kv_entries_len) v = p.kv_entries[e];
-        if (v < 0 || v >= p.kv_rows) {
-          flag_error(FT_DEV_BAD_KV_INDEX);
-          v = -1;
-        }
-      }
-      idx[ps] = v;
-    }
-  };
-  auto issue_tile = [&](int stage, const int (&idx)[C::PASSES]) {
-    const uint32_t k_sm = pipe_sm + stage * 2 * C::STAGE_BYTES;
-    const uint32_t v_sm = k_sm + C::STAGE_BYTES;
-#pragma unroll
-    for (int ps = 0; ps < C::PASSES; ++ps) {
-      const int r = ps * C::TPP + ld_r;
-      const bool ok = idx[ps] >= 0;
-      const int64_t row = ok ? idx[ps] : 0;
-      cp_async16(k_sm + C::swz(r, ld_c), kbase + row * p.k_s0, ok);
-      cp_async16(v_sm + C::swz(r, ld_c), vbase + row * p.v_s0, ok);
-    }
-  };
+  KvPipe<T, D, C::WIDE_IDXB> pipe(p, kvh, kv_off, kv_len, idx_sm, pipe_sm);
 
   for (int row0 = 0; row0 < rows; row0 += C::QROWS) {
     const int rows_here = min(C::QROWS, rows - row0);
@@ -279,11 +358,6 @@ __global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
         }
       }
     }
-    int idx[C::STAGES][C::PASSES];
-#pragma unroll
-    for (int s = 0; s < C::STAGES; ++s) {
-      if (s < ntiles) load_idx(s, idx[s]);
-    }
 #pragma unroll
     for (int ps = 0; ps < QPASSES; ++ps) {
       if (ps < q_passes) {
@@ -292,12 +366,8 @@ __global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
                    reinterpret_cast<const T*>(p.q) + (ok ? q_src[ps] : 0), ok);
       }
     }
-#pragma unroll
-    for (int s = 0; s < C::STAGES - 1; ++s) {
-      if (s < ntiles) issue_tile(s, idx[s]);
-      cp_async_commit();
-    }
-    // idx[STAGES-1] now holds the row ids of the next tile to be issued
+    pipe.prime_indices();  // also lands Q
+    pipe.prologue();
 
     float o_acc[D / 8][4];
 #pragma unroll
@@ -306,20 +376,14 @@ __global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
     uint32_t qf[D / 16][4];
 
     for (int j = 0; j < ntiles; ++j) {
-      cp_async_wait<C::STAGES - 2>();  // tile j (and Q) have landed for this thread
-      __syncthreads();                 // ... for every thread; and tile j-1's stage is free again
-      const int nt = j + C::STAGES - 1;
-      if (nt < ntiles) issue_tile(nt % C::STAGES, idx[C::STAGES - 1]);
-      cp_async_commit();
-      if (nt + 1 < ntiles) load_idx(nt + 1, idx[C::STAGES - 1]);
+      pipe.advance(j);  // tile j has landed for every thread; tile j-1's stage is being refilled
       if (j == 0 && active) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           ldmatrix_x4(qf[kk], q_sm + C::swz(my_rb * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * kk + (lane >> 4)));
       }
       if (active) {
-        const uint32_t k_sm = pipe_sm + (j % C::STAGES) * 2 * C::STAGE_BYTES;
-        const uint32_t v_sm = k_sm + C::STAGE_BYTES;
+        const uint32_t k_sm = pipe.k_stage(j), v_sm = pipe.v_stage(j);
         const bool masked = (j + 1) * C::TILE > kv_len;
         if (ways == 4) {
           const int tok0 = my_way * 16;
@@ -334,8 +398,7 @@ __global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
         }
       }
     }
-    cp_async_wait<0>();
-    __syncthreads();  // the ring is idle: its memory becomes the output staging area
+    pipe.drain();  // the ring is idle: its memory becomes the output staging area
 
     if (active) {
       float l0 = l_run[0], l1 = l_run[1];

@@ -41,6 +41,7 @@ def build_library(force=False, verbose=False):
            "-I", INCLUDE, "-I", CSRC, "-o", LIB_PATH]
     if verbose:
         cmd += ["-Xptxas", "-v"]
+    cmd += os.environ.get("FT_B200_NVCC_FLAGS", "").split()
     cmd += [os.path.join(CSRC, s) for s in SOURCES]
     cmd += ["-lcuda"]
     res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)

@@ -126,20 +126,26 @@ def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, 
 
 
 def _cached_args(tensors, rest, path, o_lse):
-    """Argument structs are memoised on the identity of the tensors (address,
-    shape, strides), so a steady-state decode loop pays for one dict lookup."""
+    """Argument structs are memoised so that a steady-state decode loop pays for
+    one dict lookup and a pointer check instead of rebuilding ~45 fields.  The key
+    is the identity of the tensor objects (kept alive by the cache entry, so an id
+    cannot be recycled) plus the scalar arguments; on a hit the data pointers are
+    compared with the cached ones, which catches storage that was re-allocated
+    behind the same tensor object.  Shapes and strides of a tensor object are
+    assumed not to change in place."""
     q = tensors[0]
     stream = torch.cuda.current_stream(q.device).cuda_stream
-    key = (q.dtype, tuple((t.data_ptr(), t.shape, t.stride()) for t in tensors),
-           tuple(tuple(x) if isinstance(x, (list, tuple)) else x for x in rest), path,
-           o_lse.data_ptr() if o_lse is not None else 0, stream)
-    a = _ARG_CACHE.get(key)
-    if a is None:
-        (pn, po, pq, pk, sm_scale, logit_cap) = rest
-        a = build_args(*tensors, pn, po, pq, pk, sm_scale, logit_cap, path=path, o_lse=o_lse, stream=stream)
-        if len(_ARG_CACHE) >= _ARG_CACHE_MAX:
-            _ARG_CACHE.clear()
-        _ARG_CACHE[key] = a
+    (pn, po, pq, pk, sm_scale, logit_cap) = rest
+    key = (tuple(map(id, tensors)), pn[0], pn[1], po[0], po[1], pq[0], pq[1], pk[0], pk[1], sm_scale, logit_cap,
+           path, id(o_lse), stream)
+    ptrs = tuple([t.data_ptr() for t in tensors])
+    hit = _ARG_CACHE.get(key)
+    if hit is not None and hit[1] == ptrs:
+        return hit[0]
+    a = build_args(*tensors, pn, po, pq, pk, sm_scale, logit_cap, path=path, o_lse=o_lse, stream=stream)
+    if len(_ARG_CACHE) >= _ARG_CACHE_MAX:
+        _ARG_CACHE.clear()
+    _ARG_CACHE[key] = (a, ptrs, tensors, o_lse)
     return a
 
 

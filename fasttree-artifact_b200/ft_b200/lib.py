@@ -11,8 +11,9 @@ import threading
 from . import build as _build
 
 FT_F16, FT_BF16, FT_F32 = 0, 1, 2
-FT_PATH_AUTO, FT_PATH_GENERIC, FT_PATH_MMA, FT_PATH_TCGEN05 = 0, 1, 2, 3
-PATHS = {"auto": FT_PATH_AUTO, "generic": FT_PATH_GENERIC, "mma": FT_PATH_MMA, "tcgen05": FT_PATH_TCGEN05}
+FT_PATH_AUTO, FT_PATH_GENERIC, FT_PATH_MMA, FT_PATH_TCGEN05, FT_PATH_MMA_WIDE = 0, 1, 2, 3, 4
+PATHS = {"auto": FT_PATH_AUTO, "generic": FT_PATH_GENERIC, "mma": FT_PATH_MMA, "tcgen05": FT_PATH_TCGEN05,
+         "mma_wide": FT_PATH_MMA_WIDE}
 
 FT_DEV_BAD_KV_INDEX, FT_DEV_BAD_Q_INDEX, FT_DEV_BAD_ROW_INDEX, FT_DEV_WAIT_TIMEOUT = 1, 2, 4, 8
 

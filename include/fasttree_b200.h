@@ -33,8 +33,10 @@ enum ft_dtype { FT_F16 = 0, FT_BF16 = 1, FT_F32 = 2 };
 enum ft_path {
   FT_PATH_AUTO = 0,    /* pick per launch from dtype / head_dim / rows per task */
   FT_PATH_GENERIC = 1, /* scalar fp32 kernel: any dtype, head_dim <= 256 */
-  FT_PATH_MMA = 2,     /* mma.sync tensor-core kernel, 16-bit types, head_dim 64/128 */
-  FT_PATH_TCGEN05 = 3  /* tcgen05/TMEM kernel for 128-row tasks, 16-bit types, head_dim 128 */
+  FT_PATH_MMA = 2,     /* mma.sync tensor-core kernels, 16-bit types, head_dim 64/128: per phase the
+                          narrow (swapped-operand) kernel for <= 16 query rows per task, else the wide one */
+  FT_PATH_TCGEN05 = 3, /* tcgen05/TMEM kernel for 128-row tasks, 16-bit types, head_dim 128 */
+  FT_PATH_MMA_WIDE = 4 /* the wide mma.sync kernel for every task (ablation / cross-check) */
 };
 
 /* Status codes. */

@@ -30,7 +30,7 @@ def atol_for(dtype):
 
 def paths_for(c):
     fast = c["dtype"] != torch.float32 and c["d"] in (64, 128)
-    return ["generic", "mma"] if fast else ["generic"]
+    return ["generic", "mma", "mma_wide"] if fast else ["generic"]
 
 
 SMALL = [n for n in cases.DECODE_CASES if n != "cfg2_fp16"]
@@ -65,7 +65,7 @@ def test_bf16_case(planner):
     fp32 up-cast of the same bf16 tensors."""
     c = cases.build_decode_case("mini3_bf16_as_fp32")
     assert c["dtype"] == torch.bfloat16
-    for path in ("generic", "mma"):
+    for path in ("generic", "mma", "mma_wide"):
         _, out = gpu_utils.run_case(c, planner=planner, path=path)
         # the output itself is rounded to bf16 (8 bits of mantissa): allow one bf16 ulp of the largest value
         bound = ATOL16 + float(np.abs(c["gold"]["o"]).max()) * 2 ** -8
@@ -160,7 +160,7 @@ def test_scattered_pool_rows_and_2d_index_table():
     table = torch.cat([remapped, torch.full((pad,), -1, dtype=torch.int32)]).view(-1, width).cuda()
     aux = (table,) + run.aux[1:]
     o = torch.empty_like(run.q)
-    for path in ("mma", "generic"):
+    for path in ("mma", "mma_wide", "generic"):
         o.fill_(float("nan"))
         engine.decode(run.q, k_pool.cuda(), v_pool.cuda(), o, *aux, run.tiles[0], run.tiles[1], run.scale,
                       path=path)
@@ -181,7 +181,7 @@ def test_strided_kv_buffers():
     k_view, v_view = both[:, :, 0], both[:, :, 1]
     assert k_view.stride(1) == 2 * c["d"]
     o = torch.empty_like(run.q)
-    for path in ("mma", "generic"):
+    for path in ("mma", "mma_wide", "generic"):
         engine.decode(run.q, k_view, v_view, o, *run.aux, run.tiles[0], run.tiles[1], run.scale, path=path)
         torch.cuda.synchronize()
         assert (o.float().cpu() - base).abs().max().item() <= (0 if path == "mma" else ATOL16)
@@ -197,7 +197,7 @@ def test_bad_plan_data_is_flagged_not_faulted():
     assert lib.read_device_status() == 0
     entries = run.aux[0]
     saved = entries[3].item()
-    for path in ("mma", "generic"):
+    for path in ("mma", "mma_wide", "generic"):
         entries[3] = 10 ** 8
         run.decode(path=path)
         assert lib.read_device_status() & lib.FT_DEV_BAD_KV_INDEX
