@@ -303,6 +303,44 @@ int ft_decode(const ft_decode_args* a) {
   return ft_stage2(a);
 }
 
+// ---- ft_decode_static_scratch: partial-result scratch in a fixed device array owned by the library ----------
+//
+// The array lives in every CUDA context that loads this library, from load until exit.  In host code its name is
+// only a stand-in for the device symbol, so the device address is looked up once per device with
+// cudaGetSymbolAddress (that device being current) and that address is what the kernels receive.
+#define FT_STATIC_SCRATCH_FLOATS (FT_STATIC_SCRATCH_BYTES / 4u)
+static __device__ __align__(256) float g_static_scratch[FT_STATIC_SCRATCH_FLOATS];
+
+int ft_decode_static_scratch(const ft_decode_args* a) {
+  if (a == nullptr) return fail(FT_ERR_INVALID_ARGUMENT, "args is NULL");
+  if (a->num_partial_rows < 0 || a->num_qo_heads <= 0 || a->head_dim <= 0)
+    return fail(FT_ERR_INVALID_ARGUMENT, "num_partial_rows / num_qo_heads / head_dim must be positive");
+  const int64_t per_row = (int64_t)a->num_qo_heads * (a->head_dim + 1);
+  if (a->num_partial_rows > (int64_t)FT_STATIC_SCRATCH_FLOATS / per_row)
+    return fail(FT_ERR_TOO_LARGE,
+                "plan needs %lld partial rows x %d heads x (%d+1) floats = %lld bytes of scratch; the built-in array "
+                "holds %u bytes - use ft_decode with caller-owned mid_o / mid_lse",
+                (long long)a->num_partial_rows, a->num_qo_heads, a->head_dim,
+                (long long)(a->num_partial_rows * per_row * 4), (unsigned)(4u * FT_STATIC_SCRATCH_FLOATS));
+  static float* scratch_of_device[64] = {};
+  int dev = 0;
+  FT_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(FT_ERR_UNSUPPORTED, "device ordinal %d outside 0..63", dev);
+  if (scratch_of_device[dev] == nullptr) {  // set-up: first call on this device
+    float* ptr = nullptr;
+    FT_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch));
+    if (ptr == nullptr) return fail(FT_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    scratch_of_device[dev] = ptr;
+  }
+  ft_decode_args b = *a;
+  b.mid_o = scratch_of_device[dev];
+  b.mid_o_stride0 = (int64_t)a->num_qo_heads * a->head_dim;
+  b.mid_o_stride1 = a->head_dim;
+  b.mid_lse = b.mid_o + a->num_partial_rows * b.mid_o_stride0;
+  b.mid_lse_stride0 = a->num_qo_heads;
+  return ft_decode(&b);
+}
+
 int ft_bump_kv_lens(int32_t* vnode_to_kv_lens, const int32_t* last_vnodes, int32_t n, void* stream) {
   if (n < 0) return fail(FT_ERR_INVALID_ARGUMENT, "n is negative");
   if (n == 0) return FT_OK;

@@ -15,9 +15,12 @@ FT_PATH_AUTO, FT_PATH_GENERIC, FT_PATH_MMA, FT_PATH_TCGEN05, FT_PATH_MMA_WIDE = 
 PATHS = {"auto": FT_PATH_AUTO, "generic": FT_PATH_GENERIC, "mma": FT_PATH_MMA, "tcgen05": FT_PATH_TCGEN05,
          "mma_wide": FT_PATH_MMA_WIDE}
 
+FT_STATIC_SCRATCH_BYTES = 16 << 20      # capacity of the array behind ft_decode_static_scratch
+
 FT_DEV_BAD_KV_INDEX, FT_DEV_BAD_Q_INDEX, FT_DEV_BAD_ROW_INDEX, FT_DEV_WAIT_TIMEOUT = 1, 2, 4, 8
 
-EXPORTS = ["ft_version", "ft_decode_args_size", "ft_last_error", "ft_decode", "ft_stage1", "ft_stage2", "ft_bump_kv_lens",
+EXPORTS = ["ft_version", "ft_decode_args_size", "ft_last_error", "ft_decode", "ft_stage1", "ft_stage2",
+           "ft_decode_static_scratch", "ft_bump_kv_lens",
            "ft_read_device_status", "ft_launch_count", "ft_stage1_path_name"]
 
 
@@ -91,7 +94,7 @@ def load():
             raise FastTreeError(-1, "struct ft_decode_args of the library (%d bytes) differs from the binding (%d)"
                                 % (lib.ft_decode_args_size(), ctypes.sizeof(DecodeArgs)))
         lib.ft_last_error.restype = ctypes.c_char_p
-        for name in ("ft_decode", "ft_stage1", "ft_stage2"):
+        for name in ("ft_decode", "ft_stage1", "ft_stage2", "ft_decode_static_scratch"):
             fn = getattr(lib, name)
             fn.argtypes = [argp]
             fn.restype = ctypes.c_int

@@ -131,6 +131,27 @@ int ft_stage1(const ft_decode_args* args);
  * Replaces _fasttree_decode_stage2 (kernel_bench/fasttree.py:549-579). */
 int ft_stage2(const ft_decode_args* args);
 
+/* ft_decode for callers that cannot provide (or allocate) the mid_o / mid_lse scratch.  It has no counterpart
+ * in the reference, whose planner and plugin always allocate those buffers with torch
+ * (kernel_bench/fasttree.py:275-280, fasttree_sglang_plugin_v0_2_13/metadata.py:53-58).
+ *
+ * Who needs it: a serving worker that handed all free device memory to its KV pool at start-up cannot rely on a
+ * later cudaMalloc succeeding, and a decode loop cannot afford the device-wide synchronisation cudaMalloc /
+ * cudaFree imply.  Here the partial outputs and their LSE go to a fixed array of FT_STATIC_SCRATCH_BYTES (16 MiB)
+ * compiled into the library; args->mid_o, args->mid_lse and their strides are ignored (they may be NULL),
+ * everything else is as in ft_decode.  The call allocates nothing: no cudaMalloc, no cudaFree, no allocating
+ * library routine.
+ *
+ * Limit: num_partial_rows * num_qo_heads * (head_dim + 1) * 4 bytes must fit in the array (e.g. 1015 partial
+ * rows at 32 heads x 128); larger plans get FT_ERR_TOO_LARGE and must use ft_decode.
+ * Set-up: the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ * device current); make that first call before any stream capture begins.
+ * Sharing: every call on a device uses the same array, which still holds the previous call's partials; stage 1
+ * overwrites every row stage 2 reads, so nothing needs clearing, but two calls that overlap on the GPU
+ * (different streams, or several threads) race on it - serialise them. */
+#define FT_STATIC_SCRATCH_BYTES (16u << 20)
+int ft_decode_static_scratch(const ft_decode_args* args);
+
 /* vnode_to_kv_lens[last_vnodes[i]] += 1 for i < n, on the device: the token
  * just generated joins each request's last private KV chunk.
  * Replaces prepare_for_fasttree_step (fasttree_sglang_plugin_v0_2_13/schedule.py:278-283). */
