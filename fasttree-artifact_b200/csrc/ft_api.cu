@@ -11,6 +11,7 @@
 #include "ft_stage1_generic.cuh"
 #include "ft_stage1_mma.cuh"
 #include "ft_stage1_narrow.cuh"
+#include "ft_stage1_tc.cuh"
 #include "ft_stage2.cuh"
 
 namespace {
@@ -70,6 +71,8 @@ int check_stage1(const ft_decode_args* a) {
     if (a->kv_entries_len <= 0) return fail(FT_ERR_INVALID_ARGUMENT, "kv_entries_len must be positive");
   }
   if (a->num_kv_heads > 65535) return fail(FT_ERR_UNSUPPORTED, "more than 65535 kv heads");
+  if (((int64_t)a->phase_node_nums[0] + a->phase_node_nums[1]) * a->num_kv_heads > 0x7fffffffLL)
+    return fail(FT_ERR_TOO_LARGE, "vnodes x kv heads exceeds the grid limit");
   return FT_OK;
 }
 
@@ -89,10 +92,12 @@ int pick_path(const ft_decode_args* a) {
   const char* why = mma_obstacle(a);
   if (a->path == FT_PATH_MMA || a->path == FT_PATH_TCGEN05 || a->path == FT_PATH_MMA_WIDE) {
     if (why != nullptr) return fail(FT_ERR_UNSUPPORTED, "tensor-core path unavailable: %s", why);
-    return a->path == FT_PATH_MMA_WIDE ? FT_PATH_MMA_WIDE : FT_PATH_MMA;
+    if (a->path == FT_PATH_TCGEN05 && a->head_dim != 128)
+      return fail(FT_ERR_UNSUPPORTED, "the tcgen05 kernel needs head_dim 128, got %d", a->head_dim);
+    return a->path;
   }
   if (a->path != FT_PATH_AUTO) return fail(FT_ERR_INVALID_ARGUMENT, "unknown path %d", a->path);
-  return why == nullptr ? FT_PATH_MMA : FT_PATH_GENERIC;
+  return why == nullptr ? FT_PATH_AUTO : FT_PATH_GENERIC;
 }
 
 ft::Stage1Params stage1_params(const ft_decode_args* a) {
@@ -125,6 +130,8 @@ ft::Stage1Params stage1_params(const ft_decode_args* a) {
   p.head_dim = a->head_dim;
   p.node_offset = 0;
   p.node_count = 0;
+  p.node_split = 0;
+  p.num_kv_heads = a->num_kv_heads;
   p.sm_scale = a->sm_scale;
   return p;
 }
@@ -140,7 +147,7 @@ int launch_mma(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
                                     C::SMEM_BYTES));
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  dim3 grid(p.node_count, hkv);
+  const unsigned grid = (unsigned)p.node_count * (unsigned)hkv;
   ft::stage1_mma_kernel<T, D><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(p);
   FT_CUDA_OK(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -158,16 +165,56 @@ int launch_narrow(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
                                     C::SMEM_BYTES));
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  dim3 grid(p.node_count, hkv);
+  const unsigned grid = (unsigned)p.node_count * (unsigned)hkv;
   ft::stage1_narrow_kernel<T, D><<<grid, 128, C::SMEM_BYTES, st>>>(p);
   FT_CUDA_OK(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return FT_OK;
 }
 
+template <typename T>
+int launch_tc(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
+  using C = ft::TcCfg;
+  static bool configured[64] = {};
+  int dev = 0;
+  FT_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    FT_CUDA_OK(cudaFuncSetAttribute(ft::stage1_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const unsigned grid = (unsigned)p.node_count * (unsigned)hkv;
+  ft::stage1_tc_kernel<T><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(p);
+  FT_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FT_OK;
+}
+
+template <typename T>
+int launch_fused(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
+  constexpr int smem = ft::TcCfg::SMEM_BYTES > ft::NarrowCfg<128, 2>::SMEM_BYTES ? ft::TcCfg::SMEM_BYTES
+                                                                                 : ft::NarrowCfg<128, 2>::SMEM_BYTES;
+  static bool configured[64] = {};
+  int dev = 0;
+  FT_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    FT_CUDA_OK(cudaFuncSetAttribute(ft::stage1_fused_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const unsigned grid = (unsigned)p.node_count * (unsigned)hkv;
+  ft::stage1_fused_kernel<T><<<grid, 128, smem, st>>>(p);
+  FT_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FT_OK;
+}
+
+// path: AUTO (narrow <= 16 rows, tcgen05 above when head_dim is 128, else wide), MMA (narrow / wide),
+// MMA_WIDE (wide for everything), TCGEN05 (tcgen05 for everything)
 template <typename T, int D>
-int launch_tensor(const ft::Stage1Params& p, int hkv, cudaStream_t st, int max_rows, bool wide_only) {
-  if (!wide_only && max_rows <= 16) return launch_narrow<T, D>(p, hkv, st);
+int launch_tensor(const ft::Stage1Params& p, int hkv, cudaStream_t st, int max_rows, int path) {
+  if constexpr (D == 128) {
+    if (path == FT_PATH_TCGEN05 || (path == FT_PATH_AUTO && max_rows > 16)) return launch_tc<T>(p, hkv, st);
+  }
+  if (path != FT_PATH_MMA_WIDE && max_rows <= 16) return launch_narrow<T, D>(p, hkv, st);
   return launch_mma<T, D>(p, hkv, st);
 }
 
@@ -188,13 +235,12 @@ int launch_stage1_range(const ft_decode_args* a, int path, int offset, int count
   p.node_count = count;
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
   const int hkv = a->num_kv_heads;
-  if (path == FT_PATH_MMA || path == FT_PATH_MMA_WIDE) {
-    const bool wide = path == FT_PATH_MMA_WIDE;
+  if (path != FT_PATH_GENERIC) {
     if (a->dtype == FT_F16)
-      return a->head_dim == 128 ? launch_tensor<__half, 128>(p, hkv, st, max_rows, wide)
-                                : launch_tensor<__half, 64>(p, hkv, st, max_rows, wide);
-    return a->head_dim == 128 ? launch_tensor<__nv_bfloat16, 128>(p, hkv, st, max_rows, wide)
-                              : launch_tensor<__nv_bfloat16, 64>(p, hkv, st, max_rows, wide);
+      return a->head_dim == 128 ? launch_tensor<__half, 128>(p, hkv, st, max_rows, path)
+                                : launch_tensor<__half, 64>(p, hkv, st, max_rows, path);
+    return a->head_dim == 128 ? launch_tensor<__nv_bfloat16, 128>(p, hkv, st, max_rows, path)
+                              : launch_tensor<__nv_bfloat16, 64>(p, hkv, st, max_rows, path);
   }
   switch (a->dtype) {
     case FT_F16: return launch_generic<__half>(p, hkv, st);
@@ -240,7 +286,13 @@ const char* ft_stage1_path_name(const ft_decode_args* args) {
   if (rc != FT_OK) return nullptr;
   const int path = pick_path(args);
   if (path < 0) return nullptr;
-  return path == FT_PATH_MMA ? "mma" : (path == FT_PATH_MMA_WIDE ? "mma_wide" : "generic");
+  switch (path) {
+    case FT_PATH_AUTO: return args->head_dim == 128 ? "narrow+tcgen05" : "narrow+mma";
+    case FT_PATH_MMA: return "narrow+mma";
+    case FT_PATH_MMA_WIDE: return "mma_wide";
+    case FT_PATH_TCGEN05: return "tcgen05";
+    default: return "generic";
+  }
 }
 
 int ft_stage1(const ft_decode_args* a) {
@@ -257,7 +309,18 @@ int ft_stage1(const ft_decode_args* a) {
   const int64_t r0 = a->phase_q_tile_sizes[0] > 0 ? (int64_t)a->phase_q_tile_sizes[0] * group : 1 << 30;
   const int64_t r1 = a->phase_q_tile_sizes[1] > 0 ? (int64_t)a->phase_q_tile_sizes[1] * group : 1 << 30;
   const int rows0 = (int)(r0 < (1 << 30) ? r0 : (1 << 30)), rows1 = (int)(r1 < (1 << 30) ? r1 : (1 << 30));
-  const bool same_kernel = path == FT_PATH_GENERIC || path == FT_PATH_MMA_WIDE || ((rows0 > 16) == (rows1 > 16));
+  const bool same_kernel = path == FT_PATH_GENERIC || path == FT_PATH_MMA_WIDE || path == FT_PATH_TCGEN05 ||
+                           ((rows0 > 16) == (rows1 > 16));
+  // head_dim 128, many-row phase followed directly by the few-row phase: one grid with both kernel bodies
+  if (path == FT_PATH_AUTO && a->head_dim == 128 && n0 > 0 && n1 > 0 && o1 == o0 + n0 && rows0 > 16 && rows1 <= 16) {
+    ft::Stage1Params p = stage1_params(a);
+    p.node_offset = o0;
+    p.node_count = n0 + n1;
+    p.node_split = n0;
+    cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+    return a->dtype == FT_F16 ? launch_fused<__half>(p, a->num_kv_heads, st)
+                              : launch_fused<__nv_bfloat16>(p, a->num_kv_heads, st);
+  }
   // Adjacent phases that want the same kernel go out as one grid.
   if (n0 > 0 && n1 > 0 && o1 == o0 + n0 && same_kernel)
     return launch_stage1_range(a, path, o0, n0 + n1, rows0 > rows1 ? rows0 : rows1);

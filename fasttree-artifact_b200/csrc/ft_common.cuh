@@ -37,6 +37,8 @@ struct Stage1Params {
   int32_t head_dim;
   int32_t node_offset;  // first vnode of this launch
   int32_t node_count;   // vnodes in this launch
+  int32_t num_kv_heads;
+  int32_t node_split;   // fused launch: vnodes [0, node_split) of the launch are many-row tasks
   float sm_scale;
 };
 
@@ -54,6 +56,13 @@ struct Stage2Params {
   int32_t heads;
   int32_t head_dim;
 };
+
+// Tensor-core kernels use a 1-D grid with the kv head varying fastest, so that CTAs launched next to
+// each other read the same tokens' rows (adjacent 2*D-byte slices of one pool row).
+__device__ __forceinline__ void task_of_block(const Stage1Params& p, int block, int& vnode, int& kv_head) {
+  vnode = p.node_offset + block / p.num_kv_heads;
+  kv_head = block - (block / p.num_kv_heads) * p.num_kv_heads;
+}
 
 template <typename T>
 __device__ __forceinline__ float to_float(T x);

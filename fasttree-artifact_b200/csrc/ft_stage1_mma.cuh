@@ -305,7 +305,7 @@ __device__ __forceinline__ void mma_tile(const uint32_t k_sm, const uint32_t v_s
 template <typename T, int D>
 __global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
   using C = MmaCfg<D>;
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t q_sm = smem_u32(smem);
   const uint32_t idx_sm = q_sm + C::Q_BYTES;
   const uint32_t pipe_sm = idx_sm + C::WIDE_IDX_BYTES;
@@ -314,8 +314,8 @@ __global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
   float* epi_l = epi_m + 4 * 16;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int vn = blockIdx.x + p.node_offset;
-  const int kvh = blockIdx.y;
+  int vn, kvh;
+  task_of_block(p, blockIdx.x, vn, kvh);
   const int q_off = p.q_offs[vn], q_len = p.q_lens[vn];
   const int kv_off = p.kv_offs[vn], kv_len = max(p.kv_lens[vn], 0);
   const int G = p.group;

@@ -46,7 +46,7 @@ struct NarrowCfg {
 };
 
 template <typename T, int D, int NQ>
-__device__ __forceinline__ void narrow_body(const Stage1Params& p, uint8_t* smem) {
+__device__ __forceinline__ void narrow_body(const Stage1Params& p, uint8_t* smem, const int vn, const int kvh) {
   using C = MmaCfg<D>;
   using N = NarrowCfg<D, NQ>;
   const uint32_t q_sm = smem_u32(smem);
@@ -58,8 +58,6 @@ __device__ __forceinline__ void narrow_body(const Stage1Params& p, uint8_t* smem
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g8 = lane >> 2, t4 = lane & 3;
-  const int vn = blockIdx.x + p.node_offset;
-  const int kvh = blockIdx.y;
   const int q_off = p.q_offs[vn], q_len = p.q_lens[vn];
   const int kv_off = p.kv_offs[vn], kv_len = max(p.kv_lens[vn], 0);
   const int G = p.group;
@@ -275,13 +273,20 @@ __device__ __forceinline__ void narrow_body(const Stage1Params& p, uint8_t* smem
 // Tasks with at most 8 query rows run the one-block body, the others the
 // two-block body (which also loops if a task has more than 16 rows).
 template <typename T, int D>
-__global__ void __launch_bounds__(128, 2) stage1_narrow_kernel(Stage1Params p) {
-  extern __shared__ __align__(128) uint8_t smem[];
-  const int rows = p.q_lens[blockIdx.x + p.node_offset] * p.group;
+__device__ __forceinline__ void narrow_dispatch(const Stage1Params& p, uint8_t* smem, const int vn, const int kvh) {
+  const int rows = p.q_lens[vn] * p.group;
   if (rows <= 8)
-    narrow_body<T, D, 1>(p, smem);
+    narrow_body<T, D, 1>(p, smem, vn, kvh);
   else
-    narrow_body<T, D, 2>(p, smem);
+    narrow_body<T, D, 2>(p, smem, vn, kvh);
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(128, 2) stage1_narrow_kernel(Stage1Params p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  int vn, kvh;
+  task_of_block(p, blockIdx.x, vn, kvh);
+  narrow_dispatch<T, D>(p, smem, vn, kvh);
 }
 
 }  // namespace ft

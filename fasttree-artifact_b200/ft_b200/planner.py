@@ -21,7 +21,7 @@ The emitted table family is the reference's (fasttree.py:282-296):
 ``phase_node_nums/offsets``.
 """
 from collections import deque
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace
 
 import numpy as np
 
@@ -342,6 +342,9 @@ def plan_b200(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, p
     local KV heads), so a head-sharded rank plans finer chunks.  Writes the
     request/KV tile sizes it used back into ``params`` like the reference does."""
     m = model or getattr(params, "b200_model", None) or B200Model()
+    if model is None and head_dim == 128:
+        # the tcgen05 stage-1 kernel holds 128 query rows per CTA (head_dim 128 only)
+        m = replace(m, rows_per_cta=128, ridge_flop_per_byte=4 * m.ridge_flop_per_byte)
     group = max(1, num_qo_heads // num_kv_heads)
     q_tile = max(1, m.rows_per_cta // group)
     small_tile = max(1, min(q_tile, 16 // group if group <= 16 else 1))

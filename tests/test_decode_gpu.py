@@ -30,7 +30,9 @@ def atol_for(dtype):
 
 def paths_for(c):
     fast = c["dtype"] != torch.float32 and c["d"] in (64, 128)
-    return ["generic", "mma", "mma_wide"] if fast else ["generic"]
+    if not fast:
+        return ["generic"]
+    return ["generic", "mma", "mma_wide"] + (["tcgen05", "auto"] if c["d"] == 128 else [])
 
 
 SMALL = [n for n in cases.DECODE_CASES if n != "cfg2_fp16"]
@@ -65,7 +67,7 @@ def test_bf16_case(planner):
     fp32 up-cast of the same bf16 tensors."""
     c = cases.build_decode_case("mini3_bf16_as_fp32")
     assert c["dtype"] == torch.bfloat16
-    for path in ("generic", "mma", "mma_wide"):
+    for path in ("generic", "mma", "mma_wide", "tcgen05", "auto"):
         _, out = gpu_utils.run_case(c, planner=planner, path=path)
         # the output itself is rounded to bf16 (8 bits of mantissa): allow one bf16 ulp of the largest value
         bound = ATOL16 + float(np.abs(c["gold"]["o"]).max()) * 2 ** -8
