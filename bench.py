@@ -222,6 +222,7 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--ref-requests", type=int, default=16, help="requests per step of the CPU arm")
     ap.add_argument("--prewarm-s", type=float, default=0.3, help="seconds of untimed steps before the warm-up (clock ramp)")
+    ap.add_argument("--planner-opt", default="", help="comma-separated B200Model overrides, e.g. waves=3,min_chunk=64")
     ap.add_argument("--no-graph", action="store_true", help="launch every timed step from Python instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -274,6 +275,17 @@ def main():
     params.set_q_tile_sizes([max(1, 64 // (hq // hkv)), max(1, 16 // (hq // hkv))])
     params.set_kv_tile_sizes([32, 32])
     params.set_planner(args.planner)
+    if args.planner_opt:
+        from dataclasses import replace
+        from ft_b200 import planner as ft_planner
+        base = ft_planner.B200Model()
+        if HEAD_DIM == 128:
+            base = replace(base, rows_per_cta=128, ridge_flop_per_byte=4 * base.ridge_flop_per_byte)
+        over = {}
+        for kv in args.planner_opt.split(","):
+            k, v = kv.split("=")
+            over[k] = type(getattr(base, k))(float(v))
+        params.b200_model = replace(base, **over)
     tree = to_product_tree(nodes)
     t0 = time.perf_counter()
     aux, _ = fasttree.fasttree_preparation(tree, ptrs, batch, hq_l, hkv_l, HEAD_DIM, [1024, 128], [132, 528],

@@ -1,0 +1,69 @@
+"""Pre-allocated plan buffers of one TP worker (reference:
+fasttree_sglang_plugin_v0_2_13/metadata.py:5-66): hyper-parameters, fixed-capacity
+int32 plan tables and the fp32 partial-result scratch, allocated once so that the
+decode path never allocates."""
+from typing import List, Tuple
+
+import torch
+
+
+class FastTreeMetadata:
+    def __init__(
+        self,
+        num_qo_heads: int,
+        num_kv_heads: int,
+        head_dim: int,
+        device="cuda",
+        alpha: float = 0.6,
+        beta: float = 0.3,
+        gamma: float = 0.1,
+        TSQs: Tuple[int, int] = None,
+        TSKs: Tuple[int, int] = (32, 32),
+        kv_split_sizes: Tuple[int, int] = (1024, 128),
+        para_threshs1: Tuple[int, int] = (132, 132),
+        para_threshs2: Tuple[int, int] = (132, 528),
+        max_vnodes: int = 16384,
+        max_vnode_to_q_entries: int = 81920,
+        max_batch_size: int = 8192,
+        planner: str = "b200",
+    ):
+        if planner not in ("b200", "reference"):
+            raise ValueError("planner must be 'b200' or 'reference'")
+        self.num_qo_heads = num_qo_heads
+        self.num_kv_heads = num_kv_heads
+        self.head_dim = head_dim
+        self.kv_group_num = num_qo_heads // num_kv_heads
+        self.device = device
+        self.alpha, self.beta, self.gamma = alpha, beta, gamma
+        self.TSQs = TSQs if TSQs is not None else (64 // self.kv_group_num, 16 // self.kv_group_num)
+        self.TSKs = TSKs
+        self.kv_split_sizes = kv_split_sizes
+        self.para_threshs1 = para_threshs1
+        self.para_threshs2 = para_threshs2
+        self.planner = planner
+        self.max_vnodes = max_vnodes
+        self.max_vnode_to_q_entries = max_vnode_to_q_entries
+        self.max_batch_size = max_batch_size
+
+        def i32(n):
+            return torch.empty(n, dtype=torch.int32, device=device)
+
+        self.vnode_to_q_entries = i32(max_vnode_to_q_entries)
+        self.vnode_to_q_offs = i32(max_vnodes)
+        self.vnode_to_q_lens = i32(max_vnodes)
+        self.vnode_to_kv_offs = i32(max_vnodes)
+        self.vnode_to_kv_lens = i32(max_vnodes)
+        self.req_to_vnode_entries = i32(max_vnode_to_q_entries)
+        self.req_to_vnode_offs = i32(max_batch_size)
+        self.req_to_vnode_lens = i32(max_batch_size)
+        self.req_last_vnodes_dev = i32(max_batch_size)      # device copy of req_last_vnodes for the per-step bump
+        self.mid_o = torch.empty((max_vnode_to_q_entries, num_qo_heads, head_dim), dtype=torch.float32, device=device)
+        self.mid_lse = torch.empty((max_vnode_to_q_entries, num_qo_heads), dtype=torch.float32, device=device)
+
+        self.phase_node_nums: Tuple[int, int] = None
+        self.phase_node_offsets: Tuple[int, int] = None
+        self.phase_q_tile_sizes: Tuple[int, int] = None
+        self.phase_kv_tile_sizes: Tuple[int, int] = None
+        self.req_last_vnodes: List[int] = None
+        self.num_vnodes = 0
+        self.num_partial_rows = 0

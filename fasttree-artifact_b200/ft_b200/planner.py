@@ -71,12 +71,16 @@ class Plan:
 
 
 # --------------------------------------------------------------------- emitter
-def emit_tables(vnodes, batch_size, small_tile, order_key=None):
+def emit_tables(vnodes, batch_size, small_tile, order_key=None, order_out=None, direct_offsets=False):
     """Cut every virtual node into (KV chunk x request tile) tasks and build the
     reference-format tables.  Tasks whose request count exceeds ``small_tile``
     form phase 0, the others phase 1 (stable partition, fasttree.py:246-259).
     ``order_key(kv_len, q_len)`` optionally sorts the tasks inside each phase
-    (stable, descending) so that long tasks are scheduled first."""
+    (stable, descending) so that long tasks are scheduled first.
+    ``direct_offsets``: every virtual node has ONE row range and the ranges already
+    are offsets into an existing row-id table (the serving path's flattened
+    ``req_to_token``); no ``vnode_to_kv_entries`` array is built and
+    ``vnode_to_kv_offs`` are those offsets."""
     kv_chunks, kv_offs, kv_lens, q_chunks, q_offs, q_lens = [], [], [], [], [], []
     kv_total = q_total = 0
     for vn in vnodes:
@@ -84,11 +88,19 @@ def emit_tables(vnodes, batch_size, small_tile, order_key=None):
         nreq = int(reqs.size)
         if nreq == 0:
             continue
-        segs = [np.arange(b, e, dtype=np.int32) for (b, e) in vn.kv_ranges]
-        length = int(sum(s.size for s in segs))
-        if length == 0:
-            continue
-        kv_chunks.extend(segs)
+        if direct_offsets:
+            (rb, re_), = vn.kv_ranges
+            length = int(re_ - rb)
+            if length <= 0:
+                continue
+            kv_base = int(rb)
+        else:
+            segs = [np.arange(b, e, dtype=np.int32) for (b, e) in vn.kv_ranges]
+            length = int(sum(s.size for s in segs))
+            if length == 0:
+                continue
+            kv_chunks.extend(segs)
+            kv_base = kv_total
         n_kv = -(-length // vn.kv_split)
         n_q = -(-nreq // vn.q_tile)
         c_off = np.arange(n_kv, dtype=np.int64) * vn.kv_split
@@ -96,7 +108,7 @@ def emit_tables(vnodes, batch_size, small_tile, order_key=None):
         t_off = np.arange(n_q, dtype=np.int64) * vn.q_tile
         t_len = np.minimum(t_off + vn.q_tile, nreq) - t_off
         # chunk-major, request-tile-minor; every chunk repeats the full request list
-        kv_offs.append(np.repeat(kv_total + c_off, n_q))
+        kv_offs.append(np.repeat(kv_base + c_off, n_q))
         kv_lens.append(np.repeat(c_len, n_q))
         q_base = q_total + np.arange(n_kv, dtype=np.int64) * nreq
         q_offs.append((q_base[:, None] + t_off[None, :]).reshape(-1))
@@ -110,7 +122,7 @@ def emit_tables(vnodes, batch_size, small_tile, order_key=None):
 
     kv_offs, kv_lens, q_offs, q_lens = cat(kv_offs), cat(kv_lens), cat(q_offs), cat(q_lens)
     q_entries = cat(q_chunks, np.int32)
-    if kv_total + PAD_ENTRIES >= 2 ** 31 or q_total >= 2 ** 31:
+    if kv_total + PAD_ENTRIES >= 2 ** 31 or q_total >= 2 ** 31 or (kv_offs.size and int(kv_offs.max()) >= 2 ** 31):
         raise ValueError("plan does not fit int32 tables")
 
     # request -> partial rows: rows grouped by request id, original order kept inside a group
@@ -128,8 +140,10 @@ def emit_tables(vnodes, batch_size, small_tile, order_key=None):
         small = small[np.argsort(-order_key(kv_lens[small], q_lens[small]), kind="stable")]
     perm = np.concatenate([big, small])
     pad = np.full(PAD_ENTRIES, -1, dtype=np.int32)
+    if order_out is not None:        # task i of the emitted tables is task order_out[i] of the emission order
+        order_out.append(perm)
     return dict(
-        vnode_to_kv_entries=np.concatenate([cat(kv_chunks, np.int32), pad]),
+        vnode_to_kv_entries=None if direct_offsets else np.concatenate([cat(kv_chunks, np.int32), pad]),
         vnode_to_kv_offs=kv_offs[perm].astype(np.int32), vnode_to_kv_lens=kv_lens[perm].astype(np.int32),
         vnode_to_q_entries=q_entries,
         vnode_to_q_offs=q_offs[perm].astype(np.int32), vnode_to_q_lens=q_lens[perm].astype(np.int32),
@@ -275,7 +289,7 @@ class B200Model:
     warp-MMA stage-1 kernel keeps two 112 KiB CTAs resident per SM)."""
     num_sms: int = 148
     ctas_per_sm: int = 2
-    waves: float = 2.0              # aim for this many rounds of resident CTAs
+    waves: float = 1.0              # aim for this many rounds of resident CTAs (measured: more chunks cost more in partial rows than they gain in balance)
     tile_tokens: int = 64           # KV tile of the stage-1 kernels
     rows_per_cta: int = 64          # query rows (requests x group) one CTA holds
     min_chunk: int = 128            # never cut a node's KV finer than this many tokens
@@ -341,10 +355,38 @@ def plan_b200(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, p
     ``num_kv_heads`` is the LOCAL head count of this GPU (the grid is tasks x
     local KV heads), so a head-sharded rank plans finer chunks.  Writes the
     request/KV tile sizes it used back into ``params`` like the reference does."""
-    m = model or getattr(params, "b200_model", None) or B200Model()
-    if model is None and head_dim == 128:
+    m = b200_model_for(params, head_dim, model)
+    vnodes, assign, q_tile, small_tile, target = b200_virtual_nodes(
+        tree, num_qo_heads, num_kv_heads, head_dim, m, lambda a, i: _chain_ranges(tree, kv_ptrs, a, i))
+    tabs = emit_tables(vnodes, batch_size, small_tile=small_tile, order_key=b200_task_order)
+    params.set_q_tile_sizes([q_tile, small_tile])
+    params.set_kv_tile_sizes([m.tile_tokens, m.tile_tokens])
+    return Plan(node_assignments=assign, phase_q_tile_sizes=[q_tile, small_tile],
+                phase_kv_tile_sizes=[m.tile_tokens, m.tile_tokens], kv_split_sizes=[],
+                info={"planner": "b200", "target_bytes": float(target), "vnodes": len(vnodes)}, **tabs)
+
+
+def b200_model_for(params, head_dim, model=None):
+    explicit = model or getattr(params, "b200_model", None)
+    m = explicit or B200Model()
+    if explicit is None and head_dim == 128:
         # the tcgen05 stage-1 kernel holds 128 query rows per CTA (head_dim 128 only)
         m = replace(m, rows_per_cta=128, ridge_flop_per_byte=4 * m.ridge_flop_per_byte)
+    return m
+
+
+def b200_task_order(kv_len, q_len):
+    """Sort key of the tasks inside a phase: longest KV chunk first, more requests first."""
+    return kv_len * 64 + np.minimum(q_len, 63)
+
+
+def b200_virtual_nodes(tree, num_qo_heads, num_kv_heads, head_dim, m, ranges_of, extra=()):
+    """Steps 1-3 of :func:`plan_b200` on any tree of node records (``parent``,
+    ``seqlen``, ``num_children``, ``requests``).  ``ranges_of(assign, i)`` gives the
+    KV row ranges of node i preceded by the ancestors it carries.  ``extra`` is a
+    list of ``(ranges, requests)`` pairings outside the tree (per-request private
+    tails) that take part in the byte budget and come last in emission order.
+    Returns (virtual nodes, assignments, request tile, small request tile, byte target)."""
     group = max(1, num_qo_heads // num_kv_heads)
     q_tile = max(1, m.rows_per_cta // group)
     small_tile = max(1, min(q_tile, 16 // group if group <= 16 else 1))
@@ -361,12 +403,17 @@ def plan_b200(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, p
         reqs = sorted(set(nd.requests) - carried_away[i])
         if not reqs:
             continue
-        ranges = _chain_ranges(tree, kv_ptrs, assign, i)
+        ranges = ranges_of(assign, i)
         length = sum(e - b for b, e in ranges)
         if length <= 0:
             continue
         specs.append((ranges, reqs, length))
         total_stream += -(-len(reqs) // q_tile) * length * row_bytes
+    for ranges, reqs in extra:
+        length = sum(e - b for b, e in ranges)
+        if length > 0 and len(reqs) > 0:
+            specs.append((ranges, list(reqs), length))
+            total_stream += -(-len(reqs) // q_tile) * length * row_bytes
     slots = m.num_sms * m.ctas_per_sm * m.waves
     target = max(total_stream * num_kv_heads / slots, m.min_chunk * row_bytes)
 
@@ -377,10 +424,4 @@ def plan_b200(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, p
         chunk = -(-length // n_chunks)
         chunk = -(-chunk // m.tile_tokens) * m.tile_tokens
         vnodes.append(VirtualNode(ranges, np.asarray(reqs, dtype=np.int32), q_tile=q_tile, kv_split=chunk))
-    tabs = emit_tables(vnodes, batch_size, small_tile=small_tile,
-                       order_key=lambda kv_len, q_len: kv_len * 64 + np.minimum(q_len, 63))
-    params.set_q_tile_sizes([q_tile, small_tile])
-    params.set_kv_tile_sizes([m.tile_tokens, m.tile_tokens])
-    return Plan(node_assignments=assign, phase_q_tile_sizes=[q_tile, small_tile],
-                phase_kv_tile_sizes=[m.tile_tokens, m.tile_tokens], kv_split_sizes=[],
-                info={"planner": "b200", "target_bytes": float(target), "vnodes": len(vnodes)}, **tabs)
+    return vnodes, assign, q_tile, small_tile, target
