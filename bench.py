@@ -235,7 +235,7 @@ def main():
 
     import torch.distributed as dist
     import fasttree
-    from ft_b200 import engine, lib
+    from ft_b200 import engine, lib, parallel
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -253,7 +253,7 @@ def main():
     esize = 4 if dtype == torch.float32 else 2
     if hkv % world != 0:
         raise SystemExit(f"{hkv} kv heads cannot be sharded over {world} ranks")
-    hkv_l, hq_l = hkv // world, hq // world
+    _q0, hq_l, _k0, hkv_l = parallel.head_shard(rank, world, hq, hkv)
     tokens = ptrs[-1]
 
     # ---- synthetic inputs, this rank's head slice, drawn on the device

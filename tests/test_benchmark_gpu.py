@@ -1,0 +1,30 @@
+"""The micro-benchmark driver with the reference's command line runs end to end
+on a GPU and prints the line the reference's result scraper looks for."""
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+KB = os.path.join(ROOT, "fasttree-artifact_b200", "kernel_bench")
+
+
+@pytest.mark.parametrize("planner", ["b200", "reference"])
+def test_benchmark_cli(tmp_path, planner):
+    tree = tmp_path / "tree.txt"
+    subprocess.run([sys.executable, os.path.join(KB, "tree_generation.py"), "-n", "1,4,16", "-l", "256,64,32",
+                    "-o", str(tree)], check=True)
+    plan_file = tmp_path / "plan.txt"
+    res = subprocess.run(
+        [sys.executable, os.path.join(KB, "benchmark.py"), "--load_file_path", str(tree), "--num_qo_heads", "32",
+         "--num_kv_heads", "8", "--q_tile_size_per_phase", "16,4", "--choice", "fasttree", "--planner", planner,
+         "--fasttree_heuristic_path", str(plan_file)],
+        cwd=KB, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    m = re.search(r"fasttree attn time: ([0-9.eE+-]+)", res.stdout)
+    assert m and 0 < float(m.group(1)) < 100
+    assert plan_file.read_text().startswith("Node 0: parent -1, assignment")
