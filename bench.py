@@ -30,6 +30,9 @@ for _p in (ROOT, PKG, os.path.join(PKG, "kernel_bench")):
     if _p not in sys.path:
         sys.path.insert(0, _p)
 
+_JSON_FD = os.dup(1)      # keep the real stdout for the result line ...
+os.dup2(2, 1)             # ... and send every other write to fd 1 to stderr
+
 import torch  # noqa: E402
 
 WORKLOADS = {
@@ -207,7 +210,13 @@ def run_reference_arm(args):
         "cpu_baseline": {"value": us, "unit": "us/step", "cores": cores, "kind": "port", "sample": what},
         "e2e": {"value": us, "unit": "us/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+def emit(line):
+    """The one JSON line goes to the process's original stdout; everything libraries print to fd 1
+    (NCCL's version banner, for one) was redirected to stderr at start-up."""
+    os.write(_JSON_FD, (json.dumps(line) + "\n").encode())
 
 
 def main():
@@ -245,6 +254,7 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        os.environ["NCCL_DEBUG"] = os.environ.get("FT_BENCH_NCCL_DEBUG", "WARN")   # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
     lib.load()
 
@@ -313,13 +323,20 @@ def main():
     sampler.start()
 
     # clock ramp-up and first-use costs (argument caches, NCCL channels), then W warm-up steps
-    t_end = time.perf_counter() + args.prewarm_s
-    i = 0
-    while time.perf_counter() < t_end:
-        step(i)
-        i += 1
-        if i % 64 == 0:
-            torch.cuda.synchronize()
+    if world > 1:
+        # every rank must issue the same number of collectives: a fixed count, not a time budget
+        for i in range(int(args.prewarm_s * 4000)):
+            step(i)
+            if i % 64 == 63:
+                torch.cuda.synchronize()
+    else:
+        t_end = time.perf_counter() + args.prewarm_s
+        i = 0
+        while time.perf_counter() < t_end:
+            step(i)
+            i += 1
+            if i % 64 == 0:
+                torch.cuda.synchronize()
     # The decode step is launch-bound from Python (a few microseconds of GPU work per call), so the
     # timed loop replays a CUDA graph holding `cycle` consecutive steps (one full K/V rotation or more).
     cycle = copies * max(1, -(-16 // copies))
@@ -450,9 +467,19 @@ def main():
             "gpu_launches": launches * world,
             "hbm_gbs_whole_step": algo_bytes * world / (ms_per_step * 1e-3) / 1e9,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
+        # drop the captured graph (it holds NCCL work) before tearing the group down; never hang on exit
+        graph = None
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
+        watchdog = threading.Timer(30.0, lambda: os._exit(0))
+        watchdog.daemon = True
+        watchdog.start()
+        dist.barrier()
         dist.destroy_process_group()
+        watchdog.cancel()
 
 
 if __name__ == "__main__":
