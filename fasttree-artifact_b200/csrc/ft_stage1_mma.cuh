@@ -131,13 +131,21 @@ struct KvPipe {
   const Stage1Params& p;
   const T* kbase;
   const T* vbase;
-  uint32_t idx_sm, pipe_sm;
-  int kv_off, kv_len, ntiles, tid, ld_c, ld_r;
+  const int* idx_ptr;
+  uint32_t idx_sm, pipe_sm, row_lim;
+  int kv_off, kv_len, id_lim, ntiles, tid, ld_c, ld_r;
 
-  __device__ __forceinline__ KvPipe(const Stage1Params& p_, int kvh, int kv_off_, int kv_len_, uint32_t idx_sm_,
-                                    uint32_t pipe_sm_)
-      : p(p_), idx_sm(idx_sm_), pipe_sm(pipe_sm_), kv_off(kv_off_), kv_len(kv_len_) {
+  // idx_ptr_ / idx_sm_: generic pointer and shared-window address of the same row-id ring
+  __device__ __forceinline__ KvPipe(const Stage1Params& p_, int kvh, int kv_off_, int kv_len_, const void* idx_ptr_,
+                                    uint32_t idx_sm_, uint32_t pipe_sm_)
+      : p(p_), idx_ptr(static_cast<const int*>(idx_ptr_)), idx_sm(idx_sm_), pipe_sm(pipe_sm_), kv_off(kv_off_),
+        kv_len(kv_len_) {
     tid = threadIdx.x;
+    // row ids past the end of the table are a plan error: flagged once, those tokens become padding
+    const int64_t readable = p.kv_entries_len - (int64_t)kv_off;
+    id_lim = kv_off < 0 ? 0 : (int)(readable < (int64_t)kv_len ? (readable < 0 ? 0 : readable) : kv_len);
+    if (id_lim < kv_len && tid == 0) flag_error(FT_DEV_BAD_KV_INDEX);
+    row_lim = (uint32_t)(p.kv_rows < 0x7fffffffLL ? p.kv_rows : 0x7fffffffLL);
     ld_c = tid % C::CPR;
     ld_r = tid / C::CPR;
     ntiles = (kv_len + C::TILE - 1) / C::TILE;
@@ -151,8 +159,7 @@ struct KvPipe {
     for (int i = 0; i < IDXB / C::THREADS; ++i) {
       const int t = i * C::THREADS + tid;
       const int pos = b * IDXB + t;
-      const int64_t e = (int64_t)kv_off + pos;
-      if (pos < kv_len && e >= 0 && e < p.kv_entries_len) cp_async4(dst + t * 4, p.kv_entries + e);
+      if (pos < id_lim) cp_async4(dst + t * 4, p.kv_entries + kv_off + pos);
     }
   }
   // blocks 0 and 1, waited for; call once before the first tile
@@ -167,24 +174,23 @@ struct KvPipe {
   __device__ __forceinline__ void issue_tile(int tile) {
     const uint32_t k_sm = pipe_sm + (tile % C::STAGES) * 2 * C::STAGE_BYTES;
     const uint32_t v_sm = k_sm + C::STAGE_BYTES;
-    const uint32_t ring = idx_sm + ((tile / TPB) & 1) * IDXB * 4 + (tile % TPB) * C::TILE * 4;
+    // all row ids of this thread first (independent shared-memory loads), then the copies
+    const int* ring = idx_ptr + ((tile / TPB) & 1) * IDXB + (tile % TPB) * C::TILE + ld_r;
+    const int pos0 = tile * C::TILE + ld_r;
+    uint32_t row[C::PASSES];
+#pragma unroll
+    for (int ps = 0; ps < C::PASSES; ++ps) row[ps] = pos0 + ps * C::TPP < id_lim ? (uint32_t)ring[ps * C::TPP] : 0xffffffffu;
+    bool bad = false;
 #pragma unroll
     for (int ps = 0; ps < C::PASSES; ++ps) {
       const int r = ps * C::TPP + ld_r;
-      const int pos = tile * C::TILE + r;
-      int64_t row = -1;
-      if (pos < kv_len) {
-        row = lds_s32(ring + r * 4);
-        if (row < 0 || row >= p.kv_rows || (int64_t)kv_off + pos >= p.kv_entries_len) {
-          flag_error(FT_DEV_BAD_KV_INDEX);
-          row = -1;
-        }
-      }
-      const bool ok = row >= 0;
-      if (!ok) row = 0;
-      cp_async16(k_sm + C::swz(r, ld_c), kbase + row * p.k_s0, ok);
-      cp_async16(v_sm + C::swz(r, ld_c), vbase + row * p.v_s0, ok);
+      const bool ok = row[ps] < row_lim;  // padding (0xffffffff), negative and too-large ids all fail this test
+      bad |= !ok && pos0 + ps * C::TPP < id_lim;
+      const int64_t off = (int64_t)(ok ? row[ps] : 0u);
+      cp_async16(k_sm + C::swz(r, ld_c), kbase + off * p.k_s0, ok);
+      cp_async16(v_sm + C::swz(r, ld_c), vbase + off * p.v_s0, ok);
     }
+    if (bad) flag_error(FT_DEV_BAD_KV_INDEX);
   }
   // tiles 0 .. STAGES-2, one group each
   __device__ __forceinline__ void prologue() {
@@ -325,7 +331,7 @@ __global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
   const int ntiles = (kv_len + C::TILE - 1) / C::TILE;
   const int ld_c = tid % C::CPR, ld_r = tid / C::CPR;
 
-  KvPipe<T, D, C::WIDE_IDXB> pipe(p, kvh, kv_off, kv_len, idx_sm, pipe_sm);
+  KvPipe<T, D, C::WIDE_IDXB> pipe(p, kvh, kv_off, kv_len, smem + C::Q_BYTES, idx_sm, pipe_sm);
 
   for (int row0 = 0; row0 < rows; row0 += C::QROWS) {
     const int rows_here = min(C::QROWS, rows - row0);

@@ -68,7 +68,7 @@ __device__ __forceinline__ void narrow_body(const Stage1Params& p, uint8_t* smem
   const int ld_c = tid % C::CPR, ld_r = tid / C::CPR;
   const int tok0 = warp * 16;  // this warp's 16 tokens of every tile
 
-  KvPipe<T, D, N::IDXB> pipe(p, kvh, kv_off, kv_len, idx_sm, pipe_sm);
+  KvPipe<T, D, N::IDXB> pipe(p, kvh, kv_off, kv_len, smem + N::Q_BYTES, idx_sm, pipe_sm);
 
   for (int row0 = 0; row0 < rows; row0 += N::ROWS) {
     // ---- row ids first (independent loads), then the copies

@@ -12,8 +12,10 @@
 // operand layout (64-element blocks, 8-row groups of 1024 bytes); K/V rows are
 // gathered by row id with 16-byte cp.async copies (the KV pool is token
 // granular, so there is no dense box for a tiled TMA copy).  S and O live in
-// TMEM (columns 0..63 and 64..191 of a 256-column allocation; two CTAs fit on
-// an SM).  Thread t owns query row t = TMEM lane t: it reads its row of S with
+// TMEM (two 64-column S buffers and 128 columns of O in a 256-column allocation;
+// two CTAs fit on an SM).  The scores of tile j+1 are issued before the softmax
+// of tile j starts, so the tensor pipe works while the CUDA cores do the
+// exponentials; P.V of tile j follows as soon as P is written.  Thread t owns query row t = TMEM lane t: it reads its row of S with
 // tcgen05.ld, does the online softmax without any cross-lane traffic, writes
 // its row of P, and rescales its row of O in TMEM only when the running
 // maximum has grown by more than 2^8 (the exponent offset may lag the true
@@ -45,11 +47,11 @@ struct TcCfg {
   static constexpr int V_OFF = K_OFF + 2 * 16384;
   static constexpr int P_OFF = V_OFF + 2 * 16384;     // [128 rows][128 B]
   static constexpr int IDX_OFF = P_OFF + 16384;       // 3 slots x 64 row ids
-  static constexpr int BAR_OFF = IDX_OFF + 3 * 64 * 4;
-  static constexpr int TMEM_SLOT_OFF = BAR_OFF + 8;
+  static constexpr int BAR_OFF = IDX_OFF + 3 * 64 * 4;   // two mbarriers: scores ready, P.V done
+  static constexpr int TMEM_SLOT_OFF = BAR_OFF + 16;
   static constexpr int SMEM_BYTES = TMEM_SLOT_OFF + 8;
   static constexpr int TMEM_COLS = 256;
-  static constexpr int S_COL = 0, O_COL = 64;
+  static constexpr int S_COL = 0, O_COL = 128;           // S is double-buffered: columns [0,64) and [64,128)
   static constexpr int WAIT_LIMIT = 1 << 22;
 };
 
@@ -132,7 +134,8 @@ template <typename T>
 __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, const int vn, const int kvh) {
   using C = TcCfg;
   const uint32_t sm = smem_u32(smem);
-  const uint32_t q_sm = sm + C::Q_OFF, p_sm = sm + C::P_OFF, idx_sm = sm + C::IDX_OFF, bar = sm + C::BAR_OFF;
+  const uint32_t q_sm = sm + C::Q_OFF, p_sm = sm + C::P_OFF, idx_sm = sm + C::IDX_OFF;
+  const uint32_t bar_s = sm + C::BAR_OFF, bar_o = bar_s + 8;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::TMEM_SLOT_OFF);
 
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -160,7 +163,8 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
 
   // ---- one-time set-up: barrier, tensor memory
   if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bar) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bar_s) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bar_o) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 0) {
@@ -176,7 +180,7 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
   const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32-lane quadrant
   const uint32_t idesc_s = tc_idesc<T>(128, C::TILE, false);
   const uint32_t idesc_o = tc_idesc<T>(128, C::D, true);
-  uint32_t commits = 0;  // completed-phase counter of the barrier (same value in every thread)
+  uint32_t waits_s = 0, waits_o = 0;  // phases consumed on each barrier (same value in every thread)
   bool dead = false;
 
   // row ids of tile t -> ring slot t % 3 (threads 0..63, one id each; joins the open cp.async group)
@@ -188,22 +192,20 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
   };
   // rows of tile t of K (or V) -> buffer `buf_sm`
   auto issue_rows = [&](int t, uint32_t buf_sm, const T* base, int64_t stride) {
-    const uint32_t ring = idx_sm + ((t % 3) * C::TILE + ld_r) * 4;
+    // all eight row ids first (independent shared-memory loads), then the copies
+    const int* ring = reinterpret_cast<const int*>(smem + C::IDX_OFF) + (t % 3) * C::TILE + ld_r;
     const int pos0 = t * C::TILE + ld_r;
+    uint32_t row[8];
+#pragma unroll
+    for (int ps = 0; ps < 8; ++ps) row[ps] = pos0 + ps * 8 < id_lim ? (uint32_t)ring[ps * 8] : 0xffffffffu;
+    bool bad = false;
 #pragma unroll
     for (int ps = 0; ps < 8; ++ps) {  // rows ld_r, ld_r + 8, ...: same swizzle phase, 1024 bytes apart
-      uint32_t row = 0;
-      bool ok = pos0 + ps * 8 < id_lim;
-      if (ok) {
-        row = (uint32_t)lds_s32(ring + ps * 32);
-        if (row >= row_lim) {  // also catches negative ids
-          flag_error(FT_DEV_BAD_KV_INDEX);
-          ok = false;
-          row = 0;
-        }
-      }
-      cp_async16(buf_sm + tile_pos + ps * 1024, base + (int64_t)row * stride, ok);
+      const bool ok = row[ps] < row_lim;  // padding (0xffffffff), negative and too-large ids all fail this test
+      bad |= !ok && pos0 + ps * 8 < id_lim;
+      cp_async16(buf_sm + tile_pos + ps * 1024, base + (int64_t)(ok ? row[ps] : 0u) * stride, ok);
     }
+    if (bad) flag_error(FT_DEV_BAD_KV_INDEX);
   };
   auto k_buf = [&](int t) { return sm + C::K_OFF + (t & 1) * 16384; };
   auto v_buf = [&](int t) { return sm + C::V_OFF + (t & 1) * 16384; };
@@ -247,13 +249,13 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
     tc_fence_before();
     __syncthreads();
 
-    auto issue_s = [&](int t) {  // S = Q K_t^T : 8 k-steps of 16 along head_dim
+    auto issue_s = [&](int t) {  // S[t & 1] = Q K_t^T : 8 k-steps of 16 along head_dim
       const uint32_t kb = k_buf(t);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         const uint64_t a = tc_desc(q_sm + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
         const uint64_t b = tc_desc(kb + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024);
-        tc_mma(tmem + C::S_COL, a, b, idesc_s, ks > 0);
+        tc_mma(tmem + C::S_COL + (t & 1) * C::TILE, a, b, idesc_s, ks > 0);
       }
     };
     auto issue_pv = [&](int t) {  // O += P V_t : 4 k-steps of 16 tokens
@@ -269,34 +271,46 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
     if (tid == 0 && ntiles > 0) {
       tc_fence_after();
       issue_s(0);
-      tc_commit(bar);
+      tc_commit(bar_s);
     }
     float m_used = -INFINITY, l_run = 0.f;
 
+#ifdef FT_TC_PROFILE
+    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long t_prev = clock64();
+#define FT_MARK(i) { const long long t_now = clock64(); prof[i] += t_now - t_prev; t_prev = t_now; }
+#else
+#define FT_MARK(i)
+#endif
     for (int j = 0; j < ntiles; ++j) {
-      // S_j (and P.V of tile j-1) finished?
-      const bool ok = tc_wait(bar, commits & 1);
-      ++commits;
-      if (__syncthreads_or(!ok)) {
+      // K_{j+1} (copied during the previous iteration) must be visible before S_{j+1} is issued
+      cp_async_wait<1>();
+      proxy_fence();
+      FT_MARK(0)
+      const bool ok_s = tc_wait(bar_s, waits_s & 1);  // S_j ready
+      ++waits_s;
+      FT_MARK(1)
+      if (__syncthreads_or(!ok_s)) {
         if (tid == 0) flag_error(FT_DEV_WAIT_TIMEOUT);
         dead = true;
         break;
       }
       tc_fence_after();
-      // copies issued one iteration ago (K_{j+1}, V_j, ids) have had a full tile time to land
-      cp_async_wait<0>();
-      proxy_fence();
-      __syncthreads();
-      // refill: K buffer of tile j is free (S_j done), V buffer of tile j-1 is free (its P.V done)
+      if (tid == 0 && j + 1 < ntiles) {  // the tensor pipe computes the next scores during this softmax
+        issue_s(j + 1);
+        tc_commit(bar_s);
+      }
+      // K buffer of tile j is free again (S_j done)
       if (j + 2 < ntiles) issue_rows(j + 2, k_buf(j + 2), kbase, p.k_s0);
-      if (j + 1 < ntiles) issue_rows(j + 1, v_buf(j + 1), vbase, p.v_s0);
       if (j + 3 < ntiles) issue_ids(j + 3);
       cp_async_commit();
+      FT_MARK(2)
 
       // ---- softmax of this thread's row (scores stay unscaled until the exponent: one FMA per element)
       float s[64];
-      tmem_ld32(t_lane + C::S_COL, *reinterpret_cast<float(*)[32]>(&s[0]));
-      tmem_ld32(t_lane + C::S_COL + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+      const uint32_t s_col = t_lane + C::S_COL + (j & 1) * C::TILE;
+      tmem_ld32(s_col, *reinterpret_cast<float(*)[32]>(&s[0]));
+      tmem_ld32(s_col + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
       const int valid = kv_len - j * C::TILE;  // columns >= valid are padding (last tile only)
       if (valid < C::TILE) {
 #pragma unroll
@@ -317,55 +331,80 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
         }
       }
       l_run *= corr;
-      if (j > 0 && __any_sync(0xffffffffu, grow)) {  // rescale this warp's rows of O in tensor memory
-#pragma unroll
-        for (int cb = 0; cb < 4; ++cb) {
-          float o[32];
-          tmem_ld32(t_lane + C::O_COL + cb * 32, o);
-#pragma unroll
-          for (int c = 0; c < 32; ++c) o[c] *= corr;
-          tmem_st32(t_lane + C::O_COL + cb * 32, o);
-        }
-        tmem_wait_st();
-      }
       const float neg_off = m_used == -INFINITY ? 0.f : -m_used;
       const float2 sc2 = make_float2(scale2, scale2), no2 = make_float2(neg_off, neg_off);
       float2 sum2 = make_float2(0.f, 0.f);
+      uint32_t w[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float2 x = __ffma2_rn(make_float2(s[2 * i], s[2 * i + 1]), sc2, no2);
+        x.x = fast_exp2(x.x);
+        x.y = fast_exp2(x.y);
+        sum2 = __fadd2_rn(sum2, x);
+        w[i] = pack2<T>(x.x, x.y);
+      }
+      l_run += sum2.x + sum2.y;
+      FT_MARK(3)
+
+      // P.V of the previous tile must be done before P and O are touched
+      bool ok_o = true;
+      if (j > 0) {
+        ok_o = tc_wait(bar_o, waits_o & 1);
+        ++waits_o;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, grow)) {  // rescale this warp's rows of O in tensor memory
+#pragma unroll
+          for (int cb = 0; cb < 4; ++cb) {
+            float o[32];
+            tmem_ld32(t_lane + C::O_COL + cb * 32, o);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] *= corr;
+            tmem_st32(t_lane + C::O_COL + cb * 32, o);
+          }
+          tmem_wait_st();
+        }
+      }
+      FT_MARK(4)
+      // V buffer of tile j-1 is free (its P.V is done)
+      if (j + 1 < ntiles) issue_rows(j + 1, v_buf(j + 1), vbase, p.v_s0);
+      cp_async_commit();
       const uint32_t p_row = p_sm + (tid >> 3) * 1024 + (tid & 7) * 128;
 #pragma unroll
-      for (int c8 = 0; c8 < 8; ++c8) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float2 x = __ffma2_rn(make_float2(s[c8 * 8 + 2 * i], s[c8 * 8 + 2 * i + 1]), sc2, no2);
-          x.x = fast_exp2(x.x);
-          x.y = fast_exp2(x.y);
-          sum2 = __fadd2_rn(sum2, x);
-          w[i] = pack2<T>(x.x, x.y);
-        }
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + ((c8 ^ (tid & 7)) << 4)), "r"(w[0]),
-                     "r"(w[1]), "r"(w[2]), "r"(w[3])
+      for (int c8 = 0; c8 < 8; ++c8)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + ((c8 ^ (tid & 7)) << 4)),
+                     "r"(w[4 * c8]), "r"(w[4 * c8 + 1]), "r"(w[4 * c8 + 2]), "r"(w[4 * c8 + 3])
                      : "memory");
+      FT_MARK(5)
+      cp_async_wait<2>();  // V_j (copied during the previous iteration) has landed
+      proxy_fence();       // P (generic stores) and V_j (cp.async) become visible to the tensor core
+      tc_fence_before();   // orders this thread's tcgen05.ld/st before the barrier
+      if (__syncthreads_or(!ok_o)) {
+        if (tid == 0) flag_error(FT_DEV_WAIT_TIMEOUT);
+        dead = true;
+        break;
       }
-      const float sum = sum2.x + sum2.y;
-      l_run += sum;
-      proxy_fence();      // P (generic stores) and V_j (cp.async) become visible to the tensor core
-      tc_fence_before();  // orders this thread's tcgen05.ld/st before the barrier
-      __syncthreads();
+      FT_MARK(6)
       if (tid == 0) {
         tc_fence_after();
         issue_pv(j);
-        if (j + 1 < ntiles) issue_s(j + 1);
-        tc_commit(bar);
+        tc_commit(bar_o);
       }
+      FT_MARK(7)
     }
+#ifdef FT_TC_PROFILE
+    if (blockIdx.x == 0 && (tid == 0 || tid == 37))
+      printf("tc profile tid %d tiles %d: cpwait+top %lld | barS %lld | sync+issueS+loadK %lld | tmem ld+softmax %lld | "
+             "barO+rescale %lld | loadV+Pstore %lld | wait2+fence+sync %lld | issuePV %lld  (cycles per tile)\n",
+             tid, ntiles, prof[0] / ntiles, prof[1] / ntiles, prof[2] / ntiles, prof[3] / ntiles, prof[4] / ntiles,
+             prof[5] / ntiles, prof[6] / ntiles, prof[7] / ntiles);
+#endif
     if (dead) break;
 
     // ---- epilogue: wait for the last P.V, normalise, write this thread's partial row
     bool ok = true;
     if (ntiles > 0) {
-      ok = tc_wait(bar, commits & 1);
-      ++commits;
+      ok = tc_wait(bar_o, waits_o & 1);  // the last P.V
+      ++waits_o;
     }
     if (__syncthreads_or(!ok)) {
       if (tid == 0) flag_error(FT_DEV_WAIT_TIMEOUT);
