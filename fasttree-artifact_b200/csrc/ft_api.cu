@@ -201,7 +201,7 @@ int launch_fused(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const unsigned grid = (unsigned)p.node_count * (unsigned)hkv;
-  ft::stage1_fused_kernel<T><<<grid, 128, smem, st>>>(p);
+  ft::stage1_fused_kernel<T><<<grid, ft::TcCfg::THREADS, smem, st>>>(p);
   FT_CUDA_OK(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return FT_OK;

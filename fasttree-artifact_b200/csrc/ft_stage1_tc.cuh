@@ -20,8 +20,10 @@
 // its row of P, and rescales its row of O in TMEM only when the running
 // maximum has grown by more than 2^8 (the exponent offset may lag the true
 // maximum; sum and output use the same offset, so the result is unchanged).
-// One elected thread issues the MMAs; completion comes back through an
-// mbarrier (tcgen05.commit) that every thread polls with a bounded wait.
+// A fifth warp does nothing but issue the MMAs (one elected lane), so that the
+// descriptor arithmetic and the issue latency stay off the softmax warps'
+// critical path; completion comes back through mbarriers (tcgen05.commit)
+// that every thread polls with a bounded wait.
 //
 // Arithmetic conventions as in the other stage-1 kernels
 // (kernel_bench/fasttree.py:360-413): fp32 scores scaled after the dot product,
@@ -38,7 +40,7 @@
 namespace ft {
 
 struct TcCfg {
-  static constexpr int THREADS = 128;
+  static constexpr int THREADS = 160;  // warps 0-3: one query row per thread (loads, softmax); warp 4: issues the MMAs
   static constexpr int ROWS = 128;    // query rows per pass (UMMA M)
   static constexpr int TILE = 64;     // tokens per tile (UMMA N of S, K of P.V)
   static constexpr int D = 128;
@@ -52,7 +54,7 @@ struct TcCfg {
   static constexpr int SMEM_BYTES = TMEM_SLOT_OFF + 8;
   static constexpr int TMEM_COLS = 256;
   static constexpr int S_COL = 0, O_COL = 128;           // S is double-buffered: columns [0,64) and [64,128)
-  static constexpr int WAIT_LIMIT = 1 << 22;
+  static constexpr int WAIT_LIMIT = 1 << 16;   // probes of mbarrier.try_wait (each suspends for a while) before giving up
 };
 
 // canonical K-major / MN-major 128B-swizzled position of 16-byte chunk `c16` (0..15 over 256 B)
@@ -139,6 +141,8 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::TMEM_SLOT_OFF);
 
   const int tid = threadIdx.x, warp = tid >> 5;
+  const bool mma_warp = warp == 4;   // this warp only issues MMAs and takes part in the barriers
+  const bool mma_lane = tid == 128;
   const int q_off = p.q_offs[vn], q_len = p.q_lens[vn];
   const int kv_off = p.kv_offs[vn], kv_len = max(p.kv_lens[vn], 0);
   const int G = p.group;
@@ -177,7 +181,7 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32-lane quadrant
+  const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's 32-lane quadrant
   const uint32_t idesc_s = tc_idesc<T>(128, C::TILE, false);
   const uint32_t idesc_o = tc_idesc<T>(128, C::D, true);
   uint32_t waits_s = 0, waits_o = 0;  // phases consumed on each barrier (same value in every thread)
@@ -185,13 +189,14 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
 
   // row ids of tile t -> ring slot t % 3 (threads 0..63, one id each; joins the open cp.async group)
   auto issue_ids = [&](int t) {
-    if (tid < C::TILE) {
+    if (tid < C::TILE) {  // (warps 0 and 1)
       const int pos = t * C::TILE + tid;
       if (pos < id_lim) cp_async4(idx_sm + ((t % 3) * C::TILE + tid) * 4, p.kv_entries + kv_off + pos);
     }
   };
   // rows of tile t of K (or V) -> buffer `buf_sm`
   auto issue_rows = [&](int t, uint32_t buf_sm, const T* base, int64_t stride) {
+    if (mma_warp) return;
     // all eight row ids first (independent shared-memory loads), then the copies
     const int* ring = reinterpret_cast<const int*>(smem + C::IDX_OFF) + (t % 3) * C::TILE + ld_r;
     const int pos0 = t * C::TILE + ld_r;
@@ -213,7 +218,7 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
   for (int row0 = 0; row0 < rows && !dead; row0 += C::ROWS) {
     // ---- Q tile (gathered by request id), row ids of the first tiles
 #pragma unroll 4
-    for (int ps = 0; ps < 16; ++ps) {
+    for (int ps = 0; ps < (mma_warp ? 0 : 16); ++ps) {
       const int r = ps * 8 + ld_r;
       const int prow = row0 + r;
       int64_t src = -1;
@@ -268,7 +273,7 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
       }
     };
 
-    if (tid == 0 && ntiles > 0) {
+    if (mma_lane && ntiles > 0) {
       tc_fence_after();
       issue_s(0);
       tc_commit(bar_s);
@@ -276,7 +281,7 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
     float m_used = -INFINITY, l_run = 0.f;
 
 #ifdef FT_TC_PROFILE
-    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long prof[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
     long long t_prev = clock64();
 #define FT_MARK(i) { const long long t_now = clock64(); prof[i] += t_now - t_prev; t_prev = t_now; }
 #else
@@ -296,12 +301,16 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
         break;
       }
       tc_fence_after();
-      if (tid == 0 && j + 1 < ntiles) {  // the tensor pipe computes the next scores during this softmax
+      FT_MARK(8)
+      if (mma_lane && j + 1 < ntiles) {  // the tensor pipe computes the next scores during this softmax
         issue_s(j + 1);
         tc_commit(bar_s);
       }
+      bool ok_o = true;
+      if (!mma_warp) {
       // K buffer of tile j is free again (S_j done)
       if (j + 2 < ntiles) issue_rows(j + 2, k_buf(j + 2), kbase, p.k_s0);
+      FT_MARK(9)
       if (j + 3 < ntiles) issue_ids(j + 3);
       cp_async_commit();
       FT_MARK(2)
@@ -347,7 +356,6 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
       FT_MARK(3)
 
       // P.V of the previous tile must be done before P and O are touched
-      bool ok_o = true;
       if (j > 0) {
         ok_o = tc_wait(bar_o, waits_o & 1);
         ++waits_o;
@@ -378,13 +386,16 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
       cp_async_wait<2>();  // V_j (copied during the previous iteration) has landed
       proxy_fence();       // P (generic stores) and V_j (cp.async) become visible to the tensor core
       tc_fence_before();   // orders this thread's tcgen05.ld/st before the barrier
+      } else if (j > 0) {
+        ++waits_o;  // the MMA warp does not wait for P.V here but must keep the phase count of the barrier
+      }
       if (__syncthreads_or(!ok_o)) {
         if (tid == 0) flag_error(FT_DEV_WAIT_TIMEOUT);
         dead = true;
         break;
       }
       FT_MARK(6)
-      if (tid == 0) {
+      if (mma_lane) {
         tc_fence_after();
         issue_pv(j);
         tc_commit(bar_o);
@@ -394,9 +405,9 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
 #ifdef FT_TC_PROFILE
     if (blockIdx.x == 0 && (tid == 0 || tid == 37))
       printf("tc profile tid %d tiles %d: cpwait+top %lld | barS %lld | sync+issueS+loadK %lld | tmem ld+softmax %lld | "
-             "barO+rescale %lld | loadV+Pstore %lld | wait2+fence+sync %lld | issuePV %lld  (cycles per tile)\n",
+             "barO+rescale %lld | loadV+Pstore %lld | wait2+fence+sync %lld | issuePV %lld | syncA %lld | issueK %lld (cycles per tile)\n",
              tid, ntiles, prof[0] / ntiles, prof[1] / ntiles, prof[2] / ntiles, prof[3] / ntiles, prof[4] / ntiles,
-             prof[5] / ntiles, prof[6] / ntiles, prof[7] / ntiles);
+             prof[5] / ntiles, prof[6] / ntiles, prof[7] / ntiles, prof[8] / ntiles, prof[9] / ntiles);
 #endif
     if (dead) break;
 
@@ -413,7 +424,7 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
     }
     tc_fence_after();
     const int prow = row0 + tid;
-    const bool live = prow < rows;
+    const bool live = !mma_warp && prow < rows;
     int slot = 0, gg = 0;
     if (live) {
       slot = prow / G;
@@ -427,8 +438,8 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
 #pragma unroll
     for (int cb = 0; cb < 4; ++cb) {
       float o[32];
-      if (ntiles > 0) {
-        tmem_ld32(t_lane + C::O_COL + cb * 32, o);  // warp-collective: every lane takes part
+      if (ntiles > 0 && !mma_warp) {
+        tmem_ld32(t_lane + C::O_COL + cb * 32, o);  // warp-collective: every lane of the warp takes part
       } else {
 #pragma unroll
         for (int c = 0; c < 32; ++c) o[c] = 0.f;
@@ -456,7 +467,7 @@ __device__ __forceinline__ void tc_body(const Stage1Params& p, uint8_t* smem, co
 }
 
 template <typename T>
-__global__ void __launch_bounds__(128, 2) stage1_tc_kernel(Stage1Params p) {
+__global__ void __launch_bounds__(TcCfg::THREADS, 2) stage1_tc_kernel(Stage1Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   int vn, kvh;
   task_of_block(p, blockIdx.x, vn, kvh);
@@ -467,14 +478,16 @@ __global__ void __launch_bounds__(128, 2) stage1_tc_kernel(Stage1Params p) {
 // many-row tasks for the tcgen05 body, the rest few-row tasks for the swapped-operand body.  The
 // tensor-bound and the memory-bound CTAs then share the SMs instead of running back to back.
 template <typename T>
-__global__ void __launch_bounds__(128, 2) stage1_fused_kernel(Stage1Params p) {
+__global__ void __launch_bounds__(TcCfg::THREADS, 2) stage1_fused_kernel(Stage1Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   int vn, kvh;
   task_of_block(p, blockIdx.x, vn, kvh);  // blocks [0, node_split * heads) are the many-row tasks: they start first
-  if (vn - p.node_offset < p.node_split)
+  if (vn - p.node_offset < p.node_split) {
     tc_body<T>(p, smem, vn, kvh);
-  else
+  } else {
+    if (threadIdx.x >= 128) return;  // the few-row body is written for four warps
     narrow_dispatch<T, 128>(p, smem, vn, kvh);
+  }
 }
 
 }  // namespace ft
