@@ -1,8 +1,11 @@
 // C ABI of the tree-attention decode engine: argument validation, kernel
 // selection and launches.  Declarations and the mapping to the reference's
 // Python entry points are in include/fasttree_b200.h.
+#include <cuda.h>
+
 #include <atomic>
 #include <cstdarg>
+#include <mutex>
 #include <cstdio>
 #include <cstring>
 
@@ -11,6 +14,7 @@
 #include "ft_stage1_generic.cuh"
 #include "ft_stage1_mma.cuh"
 #include "ft_stage1_narrow.cuh"
+#include "ft_stage1_stream.cuh"
 #include "ft_stage1_tc.cuh"
 #include "ft_stage2.cuh"
 
@@ -90,7 +94,7 @@ const char* mma_obstacle(const ft_decode_args* a) {
 int pick_path(const ft_decode_args* a) {
   if (a->path == FT_PATH_GENERIC) return FT_PATH_GENERIC;
   const char* why = mma_obstacle(a);
-  if (a->path == FT_PATH_MMA || a->path == FT_PATH_TCGEN05 || a->path == FT_PATH_MMA_WIDE) {
+  if (a->path == FT_PATH_MMA || a->path == FT_PATH_TCGEN05 || a->path == FT_PATH_MMA_WIDE || a->path == FT_PATH_STREAM) {
     if (why != nullptr) return fail(FT_ERR_UNSUPPORTED, "tensor-core path unavailable: %s", why);
     if (a->path == FT_PATH_TCGEN05 && a->head_dim != 128)
       return fail(FT_ERR_UNSUPPORTED, "the tcgen05 kernel needs head_dim 128, got %d", a->head_dim);
@@ -172,8 +176,103 @@ int launch_narrow(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
   return FT_OK;
 }
 
+// Persistent few-row kernel: two CTAs per SM, each walking its share of the tasks.
+template <typename T, int D>
+int launch_stream(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
+  using C = ft::StreamCfg<D>;
+  static bool configured[64] = {};
+  static int sms[64] = {};
+  int dev = 0;
+  FT_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    FT_CUDA_OK(cudaFuncSetAttribute(ft::stage1_stream_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    C::SMEM_BYTES));
+    int n = 0;
+    FT_CUDA_OK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    if (dev >= 0 && dev < 64) {
+      sms[dev] = n;
+      configured[dev] = true;
+    }
+  }
+  const int64_t tasks = (int64_t)p.node_count * hkv;
+  const int64_t slots = 2LL * (dev >= 0 && dev < 64 && sms[dev] > 0 ? sms[dev] : 148);
+  const unsigned grid = (unsigned)(tasks < slots ? tasks : slots);
+  ft::stage1_stream_kernel<T, D><<<grid, 128, C::SMEM_BYTES, st>>>(p);
+  FT_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FT_OK;
+}
+
+// ---- TMA descriptors of the K / V buffers for the tcgen05 kernel -------------------------------------------
+// The driver entry point is looked up through the runtime, so the library has no link-time dependency on libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+struct KvMapKey {
+  const void* base;
+  int64_t rows, s0, s1;
+  int hkv, dtype;
+  bool operator==(const KvMapKey& o) const {
+    return base == o.base && rows == o.rows && s0 == o.s0 && s1 == o.s1 && hkv == o.hkv && dtype == o.dtype;
+  }
+};
+
+// [rows, kv heads, 128] 16-bit tensor, box 64 (head_dim) x 1 (head) x 64 (rows), 128-byte swizzle.
+bool kv_tensor_map(CUtensorMap* out, const void* base, int dtype, int64_t rows, int hkv, int64_t s0, int64_t s1) {
+  static std::mutex mu;
+  static KvMapKey keys[16];
+  static CUtensorMap maps[16];
+  static int used = 0, next = 0;
+  const KvMapKey key{base, rows, s0, s1, hkv, dtype};
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < used; ++i)
+    if (keys[i] == key) {
+      *out = maps[i];
+      return true;
+    }
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr || rows <= 0 || rows > 0x7fffffffLL) return false;
+  const cuuint64_t dims[3] = {128, (cuuint64_t)hkv, (cuuint64_t)rows};
+  const cuuint64_t strides[2] = {(cuuint64_t)s1 * 2, (cuuint64_t)s0 * 2};  // bytes, for dimensions 1 and 2
+  const cuuint32_t box[3] = {64, 1, 64};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMap m;
+  const CUresult rc = enc(&m, dtype == FT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                          const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return false;
+  const int slot = used < 16 ? used++ : (next++ & 15);
+  keys[slot] = key;
+  maps[slot] = m;
+  *out = m;
+  return true;
+}
+
+ft::TcParams tc_params(const ft::Stage1Params& p, const ft_decode_args* a) {
+  ft::TcParams tp;
+  memset(&tp, 0, sizeof(tp));
+  tp.p = p;
+  tp.has_tma = kv_tensor_map(&tp.k_map, a->k_buffer, a->dtype, a->kv_rows, a->num_kv_heads, a->k_stride0, a->k_stride1) &&
+               kv_tensor_map(&tp.v_map, a->v_buffer, a->dtype, a->kv_rows, a->num_kv_heads, a->v_stride0, a->v_stride1);
+  return tp;
+}
+
 template <typename T>
-int launch_tc(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
+int launch_tc(const ft::TcParams& p, int hkv, cudaStream_t st) {
   using C = ft::TcCfg;
   static bool configured[64] = {};
   int dev = 0;
@@ -182,7 +281,7 @@ int launch_tc(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
     FT_CUDA_OK(cudaFuncSetAttribute(ft::stage1_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  const unsigned grid = (unsigned)p.node_count * (unsigned)hkv;
+  const unsigned grid = (unsigned)p.p.node_count * (unsigned)hkv;
   ft::stage1_tc_kernel<T><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(p);
   FT_CUDA_OK(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -190,7 +289,7 @@ int launch_tc(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
 }
 
 template <typename T>
-int launch_fused(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
+int launch_fused(const ft::TcParams& p, int hkv, cudaStream_t st) {
   constexpr int smem = ft::TcCfg::SMEM_BYTES > ft::NarrowCfg<128, 2>::SMEM_BYTES ? ft::TcCfg::SMEM_BYTES
                                                                                  : ft::NarrowCfg<128, 2>::SMEM_BYTES;
   static bool configured[64] = {};
@@ -200,7 +299,7 @@ int launch_fused(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
     FT_CUDA_OK(cudaFuncSetAttribute(ft::stage1_fused_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  const unsigned grid = (unsigned)p.node_count * (unsigned)hkv;
+  const unsigned grid = (unsigned)p.p.node_count * (unsigned)hkv;
   ft::stage1_fused_kernel<T><<<grid, ft::TcCfg::THREADS, smem, st>>>(p);
   FT_CUDA_OK(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -210,10 +309,12 @@ int launch_fused(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
 // path: AUTO (narrow <= 16 rows, tcgen05 above when head_dim is 128, else wide), MMA (narrow / wide),
 // MMA_WIDE (wide for everything), TCGEN05 (tcgen05 for everything)
 template <typename T, int D>
-int launch_tensor(const ft::Stage1Params& p, int hkv, cudaStream_t st, int max_rows, int path) {
+int launch_tensor(const ft::Stage1Params& p, const ft_decode_args* a, int hkv, cudaStream_t st, int max_rows, int path) {
   if constexpr (D == 128) {
-    if (path == FT_PATH_TCGEN05 || (path == FT_PATH_AUTO && max_rows > 16)) return launch_tc<T>(p, hkv, st);
+    if (path == FT_PATH_TCGEN05 || ((path == FT_PATH_AUTO || path == FT_PATH_STREAM) && max_rows > 16))
+      return launch_tc<T>(tc_params(p, a), hkv, st);
   }
+  if (path == FT_PATH_STREAM && max_rows <= 16) return launch_stream<T, D>(p, hkv, st);
   if (path != FT_PATH_MMA_WIDE && max_rows <= 16) return launch_narrow<T, D>(p, hkv, st);
   return launch_mma<T, D>(p, hkv, st);
 }
@@ -237,10 +338,10 @@ int launch_stage1_range(const ft_decode_args* a, int path, int offset, int count
   const int hkv = a->num_kv_heads;
   if (path != FT_PATH_GENERIC) {
     if (a->dtype == FT_F16)
-      return a->head_dim == 128 ? launch_tensor<__half, 128>(p, hkv, st, max_rows, path)
-                                : launch_tensor<__half, 64>(p, hkv, st, max_rows, path);
-    return a->head_dim == 128 ? launch_tensor<__nv_bfloat16, 128>(p, hkv, st, max_rows, path)
-                              : launch_tensor<__nv_bfloat16, 64>(p, hkv, st, max_rows, path);
+      return a->head_dim == 128 ? launch_tensor<__half, 128>(p, a, hkv, st, max_rows, path)
+                                : launch_tensor<__half, 64>(p, a, hkv, st, max_rows, path);
+    return a->head_dim == 128 ? launch_tensor<__nv_bfloat16, 128>(p, a, hkv, st, max_rows, path)
+                              : launch_tensor<__nv_bfloat16, 64>(p, a, hkv, st, max_rows, path);
   }
   switch (a->dtype) {
     case FT_F16: return launch_generic<__half>(p, hkv, st);
@@ -291,6 +392,7 @@ const char* ft_stage1_path_name(const ft_decode_args* args) {
     case FT_PATH_MMA: return "narrow+mma";
     case FT_PATH_MMA_WIDE: return "mma_wide";
     case FT_PATH_TCGEN05: return "tcgen05";
+    case FT_PATH_STREAM: return args->head_dim == 128 ? "stream+tcgen05" : "stream+mma";
     default: return "generic";
   }
 }
@@ -318,8 +420,9 @@ int ft_stage1(const ft_decode_args* a) {
     p.node_count = n0 + n1;
     p.node_split = n0;
     cudaStream_t st = static_cast<cudaStream_t>(a->stream);
-    return a->dtype == FT_F16 ? launch_fused<__half>(p, a->num_kv_heads, st)
-                              : launch_fused<__nv_bfloat16>(p, a->num_kv_heads, st);
+    const ft::TcParams tp = tc_params(p, a);
+    return a->dtype == FT_F16 ? launch_fused<__half>(tp, a->num_kv_heads, st)
+                              : launch_fused<__nv_bfloat16>(tp, a->num_kv_heads, st);
   }
   // Adjacent phases that want the same kernel go out as one grid.
   if (n0 > 0 && n1 > 0 && o1 == o0 + n0 && same_kernel)

@@ -1,0 +1,395 @@
+// Stage 1 for few-row tasks as a PERSISTENT kernel: each CTA walks a list of
+// (vnode, kv head) tasks and keeps ONE software pipeline running across task
+// boundaries, so the start-up latency of a task (metadata -> row ids -> first
+// K/V tile) is hidden behind the tiles of the tasks before it.  This is what
+// short leaves need: a 64-token leaf is a single tile, and with one CTA per
+// task its whole life is start-up latency.
+//
+// The per-tile arithmetic is that of the swapped-operand kernel
+// (ft_stage1_narrow.cuh): S^T = K.Q^T and O^T += V^T.P^T with m16n8k16, four
+// warps splitting every 64-token tile by tokens, merged through shared memory at
+// the end of the task.
+//
+// Task list of CTA c: tasks c, c + gridDim.x, c + 2*gridDim.x, ... of the launch
+// (task = vnode * kv_heads + kv_head, so the planner's longest-first order is
+// dealt round-robin).  Three cursors walk the same (task, tile) sequence:
+//   ids cursor   5 tiles ahead   row ids of a tile (and the task's request ids)
+//                                -> shared-memory rings, by cp.async
+//   kv cursor    2 tiles ahead   the tile's K/V rows (and the task's Q rows)
+//                                -> 3-stage ring / 3 Q buffers, by cp.async
+//   consumer                     MMA + online softmax; epilogue at a task's last
+//                                tile, staged through the ring stage just freed
+// One cp.async group per tile; metadata of up to MAXT tasks per round sits in
+// shared memory.
+#pragma once
+
+#include "ft_common.cuh"
+#include "ft_stage1_mma.cuh"
+#include "ft_stage1_narrow.cuh"
+
+namespace ft {
+
+template <int D>
+struct StreamCfg {
+  using M = MmaCfg<D>;
+  static constexpr int QBUFS = 3;
+  static constexpr int Q_BYTES = QBUFS * 16 * M::ROWB;
+  static constexpr int IDS_SLOTS = 8;
+  static constexpr int IDS_OFF = Q_BYTES;
+  static constexpr int IDS_BYTES = IDS_SLOTS * 64 * 4;
+  static constexpr int QID_SLOTS = 8;  // more than IDS_AHEAD: while priming, the ids cursor is that many tasks ahead
+  static constexpr int QID_OFF = IDS_OFF + IDS_BYTES;
+  static constexpr int QID_BYTES = QID_SLOTS * 16 * 4;
+  static constexpr int MAXT = 48;                      // tasks per CTA per round
+  static constexpr int META_OFF = QID_OFF + QID_BYTES;  // 8 ints per task: q_off, q_len, kv_off, kv_len, kv head
+  static constexpr int META_BYTES = MAXT * 32;
+  static constexpr int ML_OFF = META_OFF + META_BYTES;  // staged (max, sum) of the four warps
+  static constexpr int ML_BYTES = 2 * 4 * 16 * 4;
+  static constexpr int PIPE_OFF = ML_OFF + ML_BYTES;
+  static constexpr int SMEM_BYTES = PIPE_OFF + M::PIPE_BYTES;
+  static constexpr int IDS_AHEAD = 5, KV_AHEAD = 2;
+};
+static_assert(StreamCfg<128>::SMEM_BYTES <= 115712, "two CTAs must fit in one SM's shared memory");
+static_assert(StreamCfg<128>::PIPE_OFF % 128 == 0, "ring must stay 128-byte aligned");
+
+struct StreamCursor {
+  int i, t, n;  // task (index inside the round), tile inside the task, tile number inside the round
+};
+
+// one 64-token tile for one warp (its 16 tokens); NQ = 8-row blocks of the task (1 or 2)
+template <typename T, int D, int NQ>
+__device__ __forceinline__ void stream_tile(uint32_t k_sm, uint32_t v_sm, int tok0, int pos0, int kv_len, float scale2,
+                                            const uint32_t (&qb)[2][D / 16][2], float (&o_acc)[D / 16][2][4],
+                                            float (&m_run)[2][2], float (&l_run)[2][2], int lane) {
+  using C = MmaCfg<D>;
+  const int g8 = lane >> 2;
+  float s[2][NQ][4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+#pragma unroll
+    for (int nq = 0; nq < NQ; ++nq) s[h][nq][0] = s[h][nq][1] = s[h][nq][2] = s[h][nq][3] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    uint32_t ka[4];
+    ldmatrix_x4(ka, k_sm + C::swz(tok0 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * kk + (lane >> 4)));
+#pragma unroll
+    for (int nq = 0; nq < NQ; ++nq) mma16816<T>(s[kk & 1][nq], ka, qb[nq][kk][0], qb[nq][kk][1]);
+  }
+  const int pos_lo = pos0 + tok0 + g8;  // token of c0,c1; c2,c3 are 8 further
+  const bool lo_ok = pos_lo < kv_len, hi_ok = pos_lo + 8 < kv_len;
+  uint32_t pb[NQ][2];
+  bool rescale = false;
+  float corr[NQ][2];
+#pragma unroll
+  for (int nq = 0; nq < NQ; ++nq) {
+    float x0 = (s[0][nq][0] + s[1][nq][0]) * scale2, x1 = (s[0][nq][1] + s[1][nq][1]) * scale2;
+    float x2 = (s[0][nq][2] + s[1][nq][2]) * scale2, x3 = (s[0][nq][3] + s[1][nq][3]) * scale2;
+    if (!lo_ok) x0 = x1 = -INFINITY;
+    if (!hi_ok) x2 = x3 = -INFINITY;
+    float ma = fmaxf(x0, x2), mb_ = fmaxf(x1, x3);
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+      ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, o));
+      mb_ = fmaxf(mb_, __shfl_xor_sync(0xffffffffu, mb_, o));
+    }
+    const float na = fmaxf(m_run[nq][0], ma), nb = fmaxf(m_run[nq][1], mb_);
+    const float sa = na == -INFINITY ? 0.f : na, sb = nb == -INFINITY ? 0.f : nb;
+    corr[nq][0] = fast_exp2(m_run[nq][0] - sa);
+    corr[nq][1] = fast_exp2(m_run[nq][1] - sb);
+    rescale |= (na != m_run[nq][0]) | (nb != m_run[nq][1]);
+    m_run[nq][0] = na;
+    m_run[nq][1] = nb;
+    const float p0 = fast_exp2(x0 - sa), p1 = fast_exp2(x1 - sb);
+    const float p2 = fast_exp2(x2 - sa), p3 = fast_exp2(x3 - sb);
+    l_run[nq][0] = l_run[nq][0] * corr[nq][0] + p0 + p2;
+    l_run[nq][1] = l_run[nq][1] * corr[nq][1] + p1 + p3;
+    pb[nq][0] = movmatrix_trans(pack2<T>(p0, p1));
+    pb[nq][1] = movmatrix_trans(pack2<T>(p2, p3));
+  }
+  if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+    for (int mb = 0; mb < D / 16; ++mb)
+#pragma unroll
+      for (int nq = 0; nq < NQ; ++nq) {
+        o_acc[mb][nq][0] *= corr[nq][0];
+        o_acc[mb][nq][1] *= corr[nq][1];
+        o_acc[mb][nq][2] *= corr[nq][0];
+        o_acc[mb][nq][3] *= corr[nq][1];
+      }
+  }
+#pragma unroll
+  for (int mb = 0; mb < D / 16; ++mb) {
+    uint32_t va[4];
+    ldmatrix_x4_trans(va, v_sm + C::swz(tok0 + (lane & 7) + 8 * (lane >> 4), 2 * mb + ((lane >> 3) & 1)));
+#pragma unroll
+    for (int nq = 0; nq < NQ; ++nq) mma16816<T>(o_acc[mb][nq], va, pb[nq][0], pb[nq][1]);
+  }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(128, 2) stage1_stream_kernel(Stage1Params p) {
+  using C = MmaCfg<D>;
+  using S = StreamCfg<D>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t sm = smem_u32(smem);
+  const uint32_t ids_sm = sm + S::IDS_OFF, qid_sm = sm + S::QID_OFF, meta_sm = sm + S::META_OFF, pipe_sm = sm + S::PIPE_OFF;
+  const int* ids_ptr = reinterpret_cast<const int*>(smem + S::IDS_OFF);
+  const int* qid_ptr = reinterpret_cast<const int*>(smem + S::QID_OFF);
+  int* meta_ptr = reinterpret_cast<int*>(smem + S::META_OFF);
+  float* epi_m = reinterpret_cast<float*>(smem + S::ML_OFF);
+  float* epi_l = epi_m + 4 * 16;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int ld_c = tid % C::CPR, ld_r = tid / C::CPR;
+  const int G = p.group, H = p.num_kv_heads;
+  const int ntasks = p.node_count * H;
+  const int my_total = (int)blockIdx.x < ntasks ? (ntasks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const float scale2 = p.sm_scale * 1.4426950408889634f;
+  const uint32_t row_lim = (uint32_t)(p.kv_rows < 0x7fffffffLL ? p.kv_rows : 0x7fffffffLL);
+  const int tok0 = warp * 16;
+
+  for (int round0 = 0; round0 < my_total; round0 += S::MAXT) {
+    const int nround = min(S::MAXT, my_total - round0);
+    // ---- metadata of this round's tasks -> shared memory
+    if (tid < nround) {
+      const int b = blockIdx.x + (round0 + tid) * gridDim.x;
+      const int vn = p.node_offset + b / H;
+      cp_async4(meta_sm + tid * 32 + 0, p.q_offs + vn);
+      cp_async4(meta_sm + tid * 32 + 4, p.q_lens + vn);
+      cp_async4(meta_sm + tid * 32 + 8, p.kv_offs + vn);
+      cp_async4(meta_sm + tid * 32 + 12, p.kv_lens + vn);
+      meta_ptr[tid * 8 + 4] = b - (b / H) * H;
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+
+    auto tiles_of = [&](int i) {
+      const int kv_len = max(meta_ptr[i * 8 + 3], 0);
+      return max(1, (kv_len + C::TILE - 1) / C::TILE);  // an empty chunk still gets one (fully masked) tile
+    };
+    auto advance = [&](StreamCursor& c) {
+      if (c.t + 1 >= tiles_of(c.i)) {
+        ++c.i;
+        c.t = 0;
+      } else {
+        ++c.t;
+      }
+      ++c.n;
+    };
+    // readable row ids of a task (a table that ends early is a plan error: flagged, the tokens become padding)
+    auto id_limit = [&](int kv_off, int kv_len) {
+      const int64_t readable = p.kv_entries_len - (int64_t)kv_off;
+      return kv_off < 0 ? 0 : (int)(readable < (int64_t)kv_len ? (readable < 0 ? 0 : readable) : kv_len);
+    };
+    auto issue_ids = [&](const StreamCursor& c) {
+      const int q_off = meta_ptr[c.i * 8 + 0], q_len = meta_ptr[c.i * 8 + 1];
+      const int kv_off = meta_ptr[c.i * 8 + 2], kv_len = max(meta_ptr[c.i * 8 + 3], 0);
+      const int lim = id_limit(kv_off, kv_len);
+      if (tid < C::TILE) {
+        const int pos = c.t * C::TILE + tid;
+        if (pos < lim) cp_async4(ids_sm + ((c.n % S::IDS_SLOTS) * C::TILE + tid) * 4, p.kv_entries + kv_off + pos);
+        if (tid == 0 && c.t == 0 && lim < kv_len) flag_error(FT_DEV_BAD_KV_INDEX);
+      } else if (c.t == 0 && tid - C::TILE < min(q_len, 16)) {  // request ids of the task's (at most 16) slots
+        const int64_t part = (int64_t)q_off + (tid - C::TILE);
+        if (part >= 0 && part < p.num_partial_rows)
+          cp_async4(qid_sm + ((c.i % S::QID_SLOTS) * 16 + (tid - C::TILE)) * 4, p.q_entries + part);
+        else
+          flag_error(FT_DEV_BAD_ROW_INDEX);
+      }
+    };
+    auto issue_kv = [&](const StreamCursor& c) {
+      const int q_off = meta_ptr[c.i * 8 + 0], q_len = meta_ptr[c.i * 8 + 1];
+      const int kv_off = meta_ptr[c.i * 8 + 2], kv_len = max(meta_ptr[c.i * 8 + 3], 0);
+      const int kvh = meta_ptr[c.i * 8 + 4];
+      const int lim = id_limit(kv_off, kv_len);
+      const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)kvh * p.k_s1 + ld_c * 8;
+      const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)kvh * p.v_s1 + ld_c * 8;
+      const uint32_t k_sm = pipe_sm + (c.n % C::STAGES) * 2 * C::STAGE_BYTES, v_sm = k_sm + C::STAGE_BYTES;
+      const int* ring = ids_ptr + (c.n % S::IDS_SLOTS) * C::TILE + ld_r;
+      const int pos0 = c.t * C::TILE + ld_r;
+      uint32_t row[C::PASSES];
+#pragma unroll
+      for (int ps = 0; ps < C::PASSES; ++ps) row[ps] = pos0 + ps * C::TPP < lim ? (uint32_t)ring[ps * C::TPP] : 0xffffffffu;
+      bool bad = false;
+#pragma unroll
+      for (int ps = 0; ps < C::PASSES; ++ps) {
+        const int r = ps * C::TPP + ld_r;
+        const bool ok = row[ps] < row_lim;
+        bad |= !ok && pos0 + ps * C::TPP < lim;
+        const int64_t off = (int64_t)(ok ? row[ps] : 0u);
+        cp_async16(k_sm + C::swz(r, ld_c), kbase + off * p.k_s0, ok);
+        cp_async16(v_sm + C::swz(r, ld_c), vbase + off * p.v_s0, ok);
+      }
+      if (bad) flag_error(FT_DEV_BAD_KV_INDEX);
+      if (c.t == 0) {  // the task's query rows -> Q buffer i % 3
+        const int rows = min(q_len * G, 16);
+        if (tid == 0 && q_len * G > 16) flag_error(FT_DEV_BAD_ROW_INDEX);  // not a few-row task: rows beyond 16 are dropped
+        const uint32_t q_sm = sm + (c.i % S::QBUFS) * 16 * C::ROWB;
+        constexpr int QPASSES = (16 + C::TPP - 1) / C::TPP;
+#pragma unroll
+        for (int ps = 0; ps < QPASSES; ++ps) {
+          const int r = ps * C::TPP + ld_r;
+          if (r < 16) {
+            int64_t src = -1;
+            if (r < rows) {
+              const int slot = r / G, gg = r - slot * G;
+              const int req = qid_ptr[(c.i % S::QID_SLOTS) * 16 + slot];
+              const int64_t part = (int64_t)q_off + slot;
+              if (part >= 0 && part < p.num_partial_rows) {
+                if (req >= 0 && req < p.batch)
+                  src = (int64_t)req * p.q_s0 + (int64_t)(kvh * G + gg) * p.q_s1 + ld_c * 8;
+                else
+                  flag_error(FT_DEV_BAD_Q_INDEX);
+              }
+            }
+            cp_async16(q_sm + C::swz(r, ld_c), reinterpret_cast<const T*>(p.q) + (src >= 0 ? src : 0), src >= 0);
+          }
+        }
+      }
+    };
+
+    StreamCursor ic{0, 0, 0}, kc{0, 0, 0}, cc{0, 0, 0};
+    for (int k = 0; k < S::IDS_AHEAD; ++k)
+      if (ic.i < nround) {
+        issue_ids(ic);
+        advance(ic);
+      }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    for (int k = 0; k < S::KV_AHEAD; ++k) {
+      if (kc.i < nround) {
+        issue_kv(kc);
+        advance(kc);
+      }
+      cp_async_commit();
+    }
+
+    float o_acc[D / 16][2][4];
+    float m_run[2][2], l_run[2][2];
+    uint32_t qb[2][D / 16][2];
+    int c_rows = 0, c_qoff = 0, c_kvlen = 0, c_kvh = 0, c_tiles = 1;
+
+    while (cc.i < nround) {
+      cp_async_wait<S::KV_AHEAD - 1>();  // tile cc.n has landed (this thread's copies)
+      __syncthreads();                   // ... everyone's; and the stage of tile cc.n - 1 is free
+      if (kc.i < nround) {
+        issue_kv(kc);
+        advance(kc);
+      }
+      if (ic.i < nround) {
+        issue_ids(ic);
+        advance(ic);
+      }
+      cp_async_commit();
+
+      if (cc.t == 0) {  // a new task: its Q rows arrived together with this tile
+        c_qoff = meta_ptr[cc.i * 8 + 0];
+        c_rows = min(meta_ptr[cc.i * 8 + 1] * G, 16);
+        c_kvlen = max(meta_ptr[cc.i * 8 + 3], 0);
+        c_kvh = meta_ptr[cc.i * 8 + 4];
+        c_tiles = max(1, (c_kvlen + C::TILE - 1) / C::TILE);
+        const uint32_t q_sm = sm + (cc.i % S::QBUFS) * 16 * C::ROWB;
+#pragma unroll
+        for (int nq = 0; nq < 2; ++nq) {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            qb[nq][kk][0] = lds32(q_sm + C::swz(nq * 8 + g8, 2 * kk) + 4 * t4);
+            qb[nq][kk][1] = lds32(q_sm + C::swz(nq * 8 + g8, 2 * kk + 1) + 4 * t4);
+          }
+          m_run[nq][0] = m_run[nq][1] = -INFINITY;
+          l_run[nq][0] = l_run[nq][1] = 0.f;
+#pragma unroll
+          for (int mb = 0; mb < D / 16; ++mb) o_acc[mb][nq][0] = o_acc[mb][nq][1] = o_acc[mb][nq][2] = o_acc[mb][nq][3] = 0.f;
+        }
+      }
+      const uint32_t k_sm = pipe_sm + (cc.n % C::STAGES) * 2 * C::STAGE_BYTES, v_sm = k_sm + C::STAGE_BYTES;
+      if (c_rows <= 8)
+        stream_tile<T, D, 1>(k_sm, v_sm, tok0, cc.t * C::TILE, c_kvlen, scale2, qb, o_acc, m_run, l_run, lane);
+      else
+        stream_tile<T, D, 2>(k_sm, v_sm, tok0, cc.t * C::TILE, c_kvlen, scale2, qb, o_acc, m_run, l_run, lane);
+
+      if (cc.t == c_tiles - 1) {
+        // ---- end of the task: merge the four warps through the stage just consumed, write the partial rows
+        __syncthreads();  // every warp is done reading this stage
+        float* epi_o = reinterpret_cast<float*>(smem + S::PIPE_OFF + (cc.n % C::STAGES) * 2 * C::STAGE_BYTES);
+        const int nq_used = c_rows <= 8 ? 1 : 2;
+#pragma unroll
+        for (int nq = 0; nq < 2; ++nq) {
+          if (nq < nq_used) {
+            float la = l_run[nq][0], lb = l_run[nq][1];
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) {
+              la += __shfl_xor_sync(0xffffffffu, la, o);
+              lb += __shfl_xor_sync(0xffffffffu, lb, o);
+            }
+            const int r = nq * 8 + 2 * t4;
+            float* dst = epi_o + (warp * 16 + r) * D;
+            const int sw = t4 << 3;  // rows are D floats apart: rotate the columns by the row pair to spread the banks
+#pragma unroll
+            for (int mb = 0; mb < D / 16; ++mb) {
+              dst[(mb * 16 + g8) ^ sw] = o_acc[mb][nq][0];
+              dst[D + ((mb * 16 + g8) ^ sw)] = o_acc[mb][nq][1];
+              dst[(mb * 16 + 8 + g8) ^ sw] = o_acc[mb][nq][2];
+              dst[D + ((mb * 16 + 8 + g8) ^ sw)] = o_acc[mb][nq][3];
+            }
+            if (g8 == 0) {
+              epi_m[warp * 16 + r] = m_run[nq][0];
+              epi_m[warp * 16 + r + 1] = m_run[nq][1];
+              epi_l[warp * 16 + r] = la;
+              epi_l[warp * 16 + r + 1] = lb;
+            }
+          }
+        }
+        __syncthreads();
+        {
+          const int r = tid >> 3, seg = tid & 7;
+          if (r < c_rows) {
+            const int slot = r / G, gg = r - slot * G;
+            const int64_t part = (int64_t)c_qoff + slot;
+            if (part >= 0 && part < p.num_partial_rows) {
+              float M = -INFINITY;
+#pragma unroll
+              for (int w = 0; w < 4; ++w) M = fmaxf(M, epi_m[w * 16 + r]);
+              float L = 0.f;
+              float4 out[D / 32];
+#pragma unroll
+              for (int i = 0; i < D / 32; ++i) out[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+              for (int w = 0; w < 4; ++w) {
+                const float mw = epi_m[w * 16 + r];
+                const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - M);
+                L = fmaf(epi_l[w * 16 + r], f, L);
+                const float4* src = reinterpret_cast<const float4*>(epi_o + (w * 16 + r) * D);
+#pragma unroll
+                for (int i = 0; i < D / 32; ++i) {
+                  const float4 x = src[(seg + 8 * i) ^ (((r >> 1) & 3) << 1)];
+                  out[i].x = fmaf(f, x.x, out[i].x);
+                  out[i].y = fmaf(f, x.y, out[i].y);
+                  out[i].z = fmaf(f, x.z, out[i].z);
+                  out[i].w = fmaf(f, x.w, out[i].w);
+                }
+              }
+              const float inv = L > 0.f ? 1.f / L : 0.f;
+              const int head = c_kvh * G + gg;
+              float4* dst = reinterpret_cast<float4*>(p.mid_o + part * p.mo_s0 + (int64_t)head * p.mo_s1);
+#pragma unroll
+              for (int i = 0; i < D / 32; ++i)
+                dst[seg + 8 * i] = make_float4(out[i].x * inv, out[i].y * inv, out[i].z * inv, out[i].w * inv);
+              if (seg == 0)
+                p.mid_lse[part * p.ml_s0 + head] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
+            }
+          }
+        }
+        // the stage is refilled only after the barrier at the top of the next iteration
+      }
+      advance(cc);
+    }
+    cp_async_wait<0>();
+    __syncthreads();  // the rings and the metadata table are rewritten by the next round
+  }
+}
+
+}  // namespace ft

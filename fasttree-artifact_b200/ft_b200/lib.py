@@ -11,9 +11,9 @@ import threading
 from . import build as _build
 
 FT_F16, FT_BF16, FT_F32 = 0, 1, 2
-FT_PATH_AUTO, FT_PATH_GENERIC, FT_PATH_MMA, FT_PATH_TCGEN05, FT_PATH_MMA_WIDE = 0, 1, 2, 3, 4
+FT_PATH_AUTO, FT_PATH_GENERIC, FT_PATH_MMA, FT_PATH_TCGEN05, FT_PATH_MMA_WIDE, FT_PATH_STREAM = 0, 1, 2, 3, 4, 5
 PATHS = {"auto": FT_PATH_AUTO, "generic": FT_PATH_GENERIC, "mma": FT_PATH_MMA, "tcgen05": FT_PATH_TCGEN05,
-         "mma_wide": FT_PATH_MMA_WIDE}
+         "mma_wide": FT_PATH_MMA_WIDE, "stream": FT_PATH_STREAM}
 
 FT_STATIC_SCRATCH_BYTES = 16 << 20      # capacity of the array behind ft_decode_static_scratch
 

@@ -36,7 +36,8 @@ enum ft_path {
   FT_PATH_MMA = 2,     /* mma.sync tensor-core kernels, 16-bit types, head_dim 64/128: per phase the
                           narrow (swapped-operand) kernel for <= 16 query rows per task, else the wide one */
   FT_PATH_TCGEN05 = 3, /* tcgen05/TMEM kernel for 128-row tasks, 16-bit types, head_dim 128 */
-  FT_PATH_MMA_WIDE = 4 /* the wide mma.sync kernel for every task (ablation / cross-check) */
+  FT_PATH_MMA_WIDE = 4, /* the wide mma.sync kernel for every task (ablation / cross-check) */
+  FT_PATH_STREAM = 5    /* like AUTO, but few-row phases run the persistent kernel that pipelines across tasks */
 };
 
 /* Status codes. */

@@ -32,7 +32,7 @@ def paths_for(c):
     fast = c["dtype"] != torch.float32 and c["d"] in (64, 128)
     if not fast:
         return ["generic"]
-    return ["generic", "mma", "mma_wide"] + (["tcgen05", "auto"] if c["d"] == 128 else [])
+    return ["generic", "mma", "mma_wide", "stream"] + (["tcgen05", "auto"] if c["d"] == 128 else [])
 
 
 SMALL = [n for n in cases.DECODE_CASES if n != "cfg2_fp16"]
@@ -67,7 +67,7 @@ def test_bf16_case(planner):
     fp32 up-cast of the same bf16 tensors."""
     c = cases.build_decode_case("mini3_bf16_as_fp32")
     assert c["dtype"] == torch.bfloat16
-    for path in ("generic", "mma", "mma_wide", "tcgen05", "auto"):
+    for path in ("generic", "mma", "mma_wide", "stream", "tcgen05", "auto"):
         _, out = gpu_utils.run_case(c, planner=planner, path=path)
         # the output itself is rounded to bf16 (8 bits of mantissa): allow one bf16 ulp of the largest value
         bound = ATOL16 + float(np.abs(c["gold"]["o"]).max()) * 2 ** -8
@@ -113,6 +113,7 @@ EDGE_TREES = [
     ([1, 9], [150, 33], 24, 8, 128),                  # G=3: rows do not align with 16-row blocks
     ([1, 2, 4], [40, 30, 20], 16, 16, 64),            # MHA, head_dim 64
     ([1, 2], [700, 20], 128, 1, 128),                 # G=128: one request spans two 64-row blocks
+    ([1, 600], [10, 33], 32, 32, 128),                # 19200 one-tile tasks: the persistent kernel walks > 48 per CTA
 ]
 
 
