@@ -390,17 +390,48 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_per_step = t.item() / args.steps
 
-    # ---- dominant kernel (stage 1) timed alone, same rotation, events around every launch
+    # ---- dominant kernel (stage 1) timed alone, same rotation.  Launched back to back from a CUDA graph (events
+    # around the replay, divided by the launches in it) so that Python's per-call time is not counted as kernel
+    # time; eager launches with events around each one if capture is unavailable.
     n_rf = min(args.steps, 500)
-    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_rf)]
-    for i in range(n_rf):
-        c = i % copies
-        pairs[i][0].record()
-        engine.stage1(q, ks[c], vs[c], o, *aux, tsq, tsk, scale, path=args.path)
-        pairs[i][1].record()
-        engine.stage2(q, ks[c], vs[c], o, *aux, tsq, tsk, scale)
-    fence()
-    s1_ms = statistics.mean(a.elapsed_time(b) for a, b in pairs)
+    s1_ms, s1_timing = None, None
+    if graph is not None:
+        try:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                g1 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g1, stream=side):
+                    for i in range(cycle):
+                        engine.stage1(q, ks[i % copies], vs[i % copies], o, *aux, tsq, tsk, scale, path=args.path)
+            torch.cuda.current_stream().wait_stream(side)
+            reps = max(3, n_rf // cycle)
+            g1.replay()
+            fence()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                g1.replay()
+            e1.record()
+            fence()
+            s1_ms = e0.elapsed_time(e1) / (reps * cycle)
+            s1_timing = (f"mean over {reps * cycle} launches replayed from a CUDA graph of {cycle}, CUDA events around "
+                         f"the replays, same KV rotation")
+            del g1
+        except Exception:
+            s1_ms = None
+            torch.cuda.synchronize()
+    if s1_ms is None:
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_rf)]
+        for i in range(n_rf):
+            c = i % copies
+            pairs[i][0].record()
+            engine.stage1(q, ks[c], vs[c], o, *aux, tsq, tsk, scale, path=args.path)
+            pairs[i][1].record()
+            engine.stage2(q, ks[c], vs[c], o, *aux, tsq, tsk, scale)
+        fence()
+        s1_ms = statistics.mean(a.elapsed_time(b) for a, b in pairs)
+        s1_timing = f"mean over {n_rf} launches, CUDA events around each stage-1 launch, same KV rotation"
     s1_path = engine.stage1_path_name(q, ks[0], vs[0], o, *aux, tsq, tsk, scale, path=args.path)
     algo_bytes = 2 * tokens * hkv_l * HEAD_DIM * esize + 2 * batch * hq_l * HEAD_DIM * esize
     peak, peak_kind = measured_peak()
@@ -408,7 +439,7 @@ def main():
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": recorded_traffic(args.workload, world), "peak_source": f"of {peak_kind}",
                 "kernel": f"stage1_{s1_path}", "kernel_us": s1_ms * 1e3, "algorithmic_bytes": algo_bytes,
-                "timing": f"mean over {n_rf} launches, CUDA events around each stage-1 launch, same KV rotation"}
+                "timing": s1_timing}
 
     # ---- end to end: query from pinned host memory in, output to pinned host memory out, every step
     e2e = None

@@ -88,6 +88,8 @@ const char* mma_obstacle(const ft_decode_args* a) {
   if (a->q_stride0 % 8 || a->q_stride1 % 8 || a->k_stride0 % 8 || a->k_stride1 % 8 || a->v_stride0 % 8 ||
       a->v_stride1 % 8)
     return "a q/k/v stride is not a multiple of 8 elements";
+  // partial rows are written 16 bytes at a time
+  if (!aligned16(a->mid_o) || a->mid_o_stride0 % 4 || a->mid_o_stride1 % 4) return "mid_o rows not 16-byte aligned";
   return nullptr;
 }
 
@@ -221,22 +223,26 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-struct KvMapKey {
+struct MapKey {
   const void* base;
   int64_t rows, s0, s1;
-  int hkv, dtype;
-  bool operator==(const KvMapKey& o) const {
-    return base == o.base && rows == o.rows && s0 == o.s0 && s1 == o.s1 && hkv == o.hkv && dtype == o.dtype;
+  int heads, dtype, box_heads;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && s0 == o.s0 && s1 == o.s1 && heads == o.heads && dtype == o.dtype &&
+           box_heads == o.box_heads;
   }
 };
 
-// [rows, kv heads, 128] 16-bit tensor, box 64 (head_dim) x 1 (head) x 64 (rows), 128-byte swizzle.
-bool kv_tensor_map(CUtensorMap* out, const void* base, int dtype, int64_t rows, int hkv, int64_t s0, int64_t s1) {
+// Descriptor of a [rows, heads, 128] 16-bit tensor (element strides s0, s1), box 64 (head_dim) x box_heads x
+// box_rows, 128-byte swizzle.  Descriptors are cached by buffer identity; encoding one costs about a microsecond.
+bool tensor_map_3d(CUtensorMap* out, const void* base, int dtype, int64_t rows, int heads, int64_t s0, int64_t s1,
+                   int box_heads, int box_rows) {
+  constexpr int SLOTS = 128;
   static std::mutex mu;
-  static KvMapKey keys[16];
-  static CUtensorMap maps[16];
+  static MapKey keys[SLOTS];
+  static CUtensorMap maps[SLOTS];
   static int used = 0, next = 0;
-  const KvMapKey key{base, rows, s0, s1, hkv, dtype};
+  const MapKey key{base, rows, s0, s1, heads, dtype, box_heads * 1024 + box_rows};
   std::lock_guard<std::mutex> lock(mu);
   for (int i = 0; i < used; ++i)
     if (keys[i] == key) {
@@ -244,10 +250,10 @@ bool kv_tensor_map(CUtensorMap* out, const void* base, int dtype, int64_t rows, 
       return true;
     }
   EncodeTiledFn enc = encode_tiled_fn();
-  if (enc == nullptr || rows <= 0 || rows > 0x7fffffffLL) return false;
-  const cuuint64_t dims[3] = {128, (cuuint64_t)hkv, (cuuint64_t)rows};
+  if (enc == nullptr || rows <= 0 || rows > 0x7fffffffLL || heads <= 0) return false;
+  const cuuint64_t dims[3] = {128, (cuuint64_t)heads, (cuuint64_t)rows};
   const cuuint64_t strides[2] = {(cuuint64_t)s1 * 2, (cuuint64_t)s0 * 2};  // bytes, for dimensions 1 and 2
-  const cuuint32_t box[3] = {64, 1, 64};
+  const cuuint32_t box[3] = {64, (cuuint32_t)box_heads, (cuuint32_t)box_rows};
   const cuuint32_t estr[3] = {1, 1, 1};
   CUtensorMap m;
   const CUresult rc = enc(&m, dtype == FT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
@@ -255,7 +261,7 @@ bool kv_tensor_map(CUtensorMap* out, const void* base, int dtype, int64_t rows, 
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) return false;
-  const int slot = used < 16 ? used++ : (next++ & 15);
+  const int slot = used < SLOTS ? used++ : (next++ % SLOTS);
   keys[slot] = key;
   maps[slot] = m;
   *out = m;
@@ -266,8 +272,16 @@ ft::TcParams tc_params(const ft::Stage1Params& p, const ft_decode_args* a) {
   ft::TcParams tp;
   memset(&tp, 0, sizeof(tp));
   tp.p = p;
-  tp.has_tma = kv_tensor_map(&tp.k_map, a->k_buffer, a->dtype, a->kv_rows, a->num_kv_heads, a->k_stride0, a->k_stride1) &&
-               kv_tensor_map(&tp.v_map, a->v_buffer, a->dtype, a->kv_rows, a->num_kv_heads, a->v_stride0, a->v_stride1);
+  tp.has_tma =
+      tensor_map_3d(&tp.k_map, a->k_buffer, a->dtype, a->kv_rows, a->num_kv_heads, a->k_stride0, a->k_stride1, 1, 64) &&
+      tensor_map_3d(&tp.v_map, a->v_buffer, a->dtype, a->kv_rows, a->num_kv_heads, a->v_stride0, a->v_stride1, 1, 64);
+  // Q by TMA: one box per request covering its G heads (at most 8 per box), when G is a power of two up to 128
+  const int g = p.group;
+  if (tp.has_tma && g >= 1 && g <= 128 && (g & (g - 1)) == 0) {
+    const int box_heads = g < 8 ? g : 8;
+    if (tensor_map_3d(&tp.q_map, a->q, a->dtype, a->batch, a->num_qo_heads, a->q_stride0, a->q_stride1, box_heads, 1))
+      tp.q_box_rows = box_heads;
+  }
   return tp;
 }
 
@@ -517,6 +531,16 @@ int ft_bump_kv_lens(int32_t* vnode_to_kv_lens, const int32_t* last_vnodes, int32
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return FT_OK;
 }
+
+#ifdef FT_TIMELINE
+// Developer builds only: copies the first n per-CTA records {start ns, end ns, SM id, kind, 12 marks} of the last stage-1 launch.
+int ft_debug_timeline(unsigned long long* out, int n) {
+  if (out == nullptr || n < 0 || n > ft::FT_TIMELINE_CTAS) return fail(FT_ERR_INVALID_ARGUMENT, "bad timeline request");
+  FT_CUDA_OK(cudaDeviceSynchronize());
+  FT_CUDA_OK(cudaMemcpyFromSymbol(out, ft::g_timeline, sizeof(unsigned long long) * 16 * (size_t)n));
+  return FT_OK;
+}
+#endif
 
 int ft_read_device_status(void* stream, int32_t* flags) {
   if (flags == nullptr) return fail(FT_ERR_INVALID_ARGUMENT, "flags is NULL");

@@ -15,6 +15,38 @@ __device__ int g_device_status = 0;
 
 __device__ __forceinline__ void flag_error(int bit) { atomicOr(&g_device_status, bit); }
 
+// Developer builds with -DFT_TIMELINE record, per CTA of a stage-1 launch, {start ns, end ns, SM id, kind, twelve marks} so that
+// the placement and overlap of the task families can be read back (ft_debug_timeline); normal builds compile none of it.
+#ifdef FT_TIMELINE
+constexpr int FT_TIMELINE_CTAS = 1 << 16;
+__device__ unsigned long long g_timeline[16 * FT_TIMELINE_CTAS];
+__device__ __forceinline__ unsigned long long timeline_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define FT_TL_BEGIN() const unsigned long long tl_begin = ft::timeline_now()
+#define FT_TL_END(kind)                                                        \
+  do {                                                                         \
+    if (threadIdx.x == 0 && blockIdx.x < ft::FT_TIMELINE_CTAS) {               \
+      unsigned sm_id;                                                          \
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_id));                       \
+      ft::g_timeline[16 * blockIdx.x + 0] = tl_begin;                           \
+      ft::g_timeline[16 * blockIdx.x + 1] = ft::timeline_now();                 \
+      ft::g_timeline[16 * blockIdx.x + 2] = sm_id;                              \
+      ft::g_timeline[16 * blockIdx.x + 3] = (kind);                             \
+    }                                                                          \
+  } while (0)
+#define FT_TL_MARK(i)                                                          \
+  do {                                                                         \
+    if (blockIdx.x < ft::FT_TIMELINE_CTAS) ft::g_timeline[16 * blockIdx.x + 4 + (i)] = ft::timeline_now(); \
+  } while (0)
+#else
+#define FT_TL_MARK(i) do { } while (0)
+#define FT_TL_BEGIN() do { } while (0)
+#define FT_TL_END(kind) do { } while (0)
+#endif
+
 // Everything a stage-1 kernel needs, passed by value.
 struct Stage1Params {
   const void* q;

@@ -286,7 +286,9 @@ __global__ void __launch_bounds__(128, 2) stage1_narrow_kernel(Stage1Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   int vn, kvh;
   task_of_block(p, blockIdx.x, vn, kvh);
+  FT_TL_BEGIN();
   narrow_dispatch<T, D>(p, smem, vn, kvh);
+  FT_TL_END(2);
 }
 
 }  // namespace ft

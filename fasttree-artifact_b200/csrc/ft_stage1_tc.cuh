@@ -2,7 +2,7 @@
 // tensor cores (tcgen05.mma) with accumulators in tensor memory, K/V tiles
 // staged by TMA, warp-specialised.
 //
-// One CTA (192 threads) per (vnode, kv head) handles up to 128 packed query
+// One CTA (256 threads) per (vnode, kv head) handles up to 128 packed query
 // rows (requests x GQA group) per pass against the vnode's KV chunk, 64 tokens
 // per tile:
 //
@@ -16,15 +16,27 @@
 //              rescales its row of O in TMEM only when the running maximum grew
 //              by more than 2^8 (the exponent offset may lag the true maximum;
 //              sum and output use the same offset, so the result is unchanged).
+//              At the end it stages its normalised row in shared memory and
+//              each warp writes its 32 rows to the partial buffer with full-row
+//              (512-byte) store instructions.
 //   warp 4     MMA issue (one elected lane): S_t is issued before the softmax of
 //              tile t-1 has finished (two S buffers in TMEM), P.V of tile t-1
 //              as soon as its P is written.
-//   warp 5     loads.  A tile whose 64 row ids are consecutive is fetched with
-//              four tiled TMA copies (cp.async.bulk.tensor, 128-byte swizzle,
-//              no multicast) straight into the operand layout; any other tile
-//              (scattered pool slots, the ragged last tile) is gathered with
-//              16-byte cp.async copies.  Row ids reach a small shared ring with
+//   warp 5     K/V loads.  A tile whose 64 row ids are consecutive is fetched
+//              with four tiled TMA copies (cp.async.bulk.tensor, 128-byte
+//              swizzle, no multicast) straight into the operand layout; any
+//              other tile (scattered pool slots, the ragged last tile) is
+//              gathered with 16-byte cp.async copies.  K loads run one tile
+//              ahead of V loads; row ids reach a small shared ring with
 //              cp.async two tiles ahead.
+//   warps 6-7  Q gather (by request id), concurrent with the first K/V loads:
+//              one TMA box per request (its G adjacent heads) when G is a power
+//              of two, 16-byte cp.async copies otherwise.
+// The two warpgroups trade registers at start-up (setmaxnreg): the kernel
+// launches at 128 registers per thread, so that a CTA takes exactly two
+// equal-sized warps per scheduler partition and two CTAs always fit on an SM
+// whatever mix of roles they run; the softmax warps then grow to 184 and the
+// others shrink to 72.
 // Hand-offs are mbarriers (full/empty per K, V and S buffer, P written, P.V
 // done), each with exactly one waiting role; every wait is bounded and unwinds
 // the CTA through an abort flag.
@@ -50,7 +62,7 @@
 namespace ft {
 
 struct TcCfg {
-  static constexpr int THREADS = 192;
+  static constexpr int THREADS = 256;
   static constexpr int ROWS = 128;    // query rows per pass (UMMA M)
   static constexpr int TILE = 64;     // tokens per tile (UMMA N of S, K of P.V)
   static constexpr int D = 128;
@@ -61,7 +73,7 @@ struct TcCfg {
   static constexpr int IDX_SLOTS = 3;
   static constexpr int IDX_OFF = P_OFF + 16384;       // IDX_SLOTS x 64 row ids
   static constexpr int BAR_OFF = IDX_OFF + IDX_SLOTS * 64 * 4;
-  static constexpr int NBARS = 14;
+  static constexpr int NBARS = 15;
   static constexpr int ABORT_OFF = BAR_OFF + NBARS * 8;
   static constexpr int TMEM_SLOT_OFF = ABORT_OFF + 4;
   static constexpr int SMEM_BYTES = TMEM_SLOT_OFF + 4;
@@ -70,17 +82,28 @@ struct TcCfg {
   static constexpr int WAIT_LIMIT = 1 << 16;          // probes of mbarrier.try_wait before a wait gives up
   // barrier indices
   static constexpr int K_FULL = 0, K_EMPTY = 2, V_FULL = 4, V_EMPTY = 6, S_FULL = 8, S_EMPTY = 10, P_FULL = 12,
-                       PV_DONE = 13;
+                       PV_DONE = 13, Q_FULL = 14;
+  static constexpr int OUT_STRIDE = 528;              // bytes between staged output rows (512 + 16: conflict-free 16-byte stores)
+  static constexpr int REGS_SOFTMAX = 184, REGS_OTHER = 72;
 };
 static_assert(TcCfg::SMEM_BYTES <= 115712, "two CTAs must fit in one SM's shared memory");
+static_assert(128 * TcCfg::OUT_STRIDE <= TcCfg::P_OFF, "the staged output rows reuse the Q, K and V buffers");
+static_assert((TcCfg::REGS_SOFTMAX + TcCfg::REGS_OTHER) * 128 <= 2 * 128 * 128, "register trade must balance");
+
+template <int N>
+__device__ __forceinline__ void reg_grow() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_shrink() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(N)); }
 
 // Kernel parameters of the tcgen05 path: the common ones plus the TMA descriptors of the K and V buffers
 // ([rows, kv heads, head_dim], box 64 x 1 x 64 elements, 128-byte swizzle).  has_tma == 0: gather only.
 struct alignas(64) TcParams {
   CUtensorMap k_map;
   CUtensorMap v_map;
+  CUtensorMap q_map;  // [batch, heads, head_dim], box 64 x q_box_rows x 1
   Stage1Params p;
   int has_tma;
+  int q_box_rows;     // 0: gather Q with cp.async (group size not a power of two <= 128, or no descriptor)
 };
 
 // canonical K-major / MN-major 128B-swizzled position of 16-byte chunk `c16` (0..15 over 256 B)
@@ -210,6 +233,12 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
   const uint32_t row_lim = (uint32_t)(p.kv_rows < 0x7fffffffLL ? p.kv_rows : 0x7fffffffLL);
 
   // ---- one-time set-up: barriers, tensor memory
+  if (tid == 32 && tp.has_tma) {  // the first TMA copy would otherwise pay for fetching its descriptor
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tp.k_map)) : "memory");
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tp.v_map)) : "memory");
+    if (tp.q_box_rows > 0)
+      asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tp.q_map)) : "memory");
+  }
   if (tid == 0) {
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(C::K_FULL + b), 32);   // the loader's lanes
@@ -221,6 +250,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
     }
     mbar_init(bar(C::P_FULL), 128);
     mbar_init(bar(C::PV_DONE), 1);
+    mbar_init(bar(C::Q_FULL), 64);  // the Q-gather threads
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -234,13 +264,13 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  if (tid == 0) FT_TL_MARK(0);
   auto k_buf = [&](int t) { return sm + C::K_OFF + (t & 1) * 16384; };
   auto v_buf = [&](int t) { return sm + C::V_OFF + (t & 1) * 16384; };
 
-  // Waits issued so far on each barrier by this thread's role; every barrier has exactly one waiting role, so
-  // the count gives the parity to wait for and stays valid across passes.
-  uint32_t n_kfull[2] = {0, 0}, n_vfull[2] = {0, 0}, n_kempty[2] = {0, 0}, n_vempty[2] = {0, 0};
-  uint32_t n_sfull[2] = {0, 0}, n_sempty[2] = {0, 0}, n_pfull = 0, n_pvdone = 0;
+  // Tiles are numbered g = 0, 1, 2, ... across passes; tile g uses K/V/S buffer g & 1 for the (g >> 1)-th time,
+  // and is the g-th use of the P buffer, which gives every wait its barrier phase without per-barrier counters.
+  int g0 = 0, pass = 0;
   bool dead = false;
   auto give_up = [&]() {
     *abort_flag = 1;
@@ -248,277 +278,363 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
     dead = true;
   };
 
-  for (int row0 = 0; row0 < rows; row0 += C::ROWS) {
-    // ---- Q tile (gathered by request id) by the four softmax warps
-    if (warp < 4) {
-      const int ld_c = tid & 15, ld_r = tid >> 4;
-#pragma unroll 4
-      for (int ps = 0; ps < 16; ++ps) {
-        const int r = ps * 8 + ld_r;
-        const int prow = row0 + r;
-        int64_t src = -1;
-        if (prow < rows) {
-          const int slot = prow / G, gg = prow - slot * G;
-          const int64_t part = (int64_t)q_off + slot;
-          if (part >= 0 && part < p.num_partial_rows) {
-            const int req = p.q_entries[part];
-            if (req >= 0 && req < p.batch)
-              src = (int64_t)req * p.q_s0 + (int64_t)(kvh * G + gg) * p.q_s1 + ld_c * 8;
-            else
-              flag_error(FT_DEV_BAD_Q_INDEX);
-          } else {
-            flag_error(FT_DEV_BAD_ROW_INDEX);
-          }
-        }
-        cp_async16(q_sm + tc_swz(r, ld_c, 16384), reinterpret_cast<const T*>(p.q) + (src >= 0 ? src : 0), src >= 0);
-      }
-      cp_async_commit();
-      cp_async_wait<0>();
-      proxy_fence();
-    }
-    tc_fence_before();
-    __syncthreads();  // Q is in place; S/O columns and P are free (the previous pass has fully drained)
-    tc_fence_after();
-
-    if (warp == 5) {
-      // ================================================================ loader
-      const int* ring = reinterpret_cast<const int*>(smem + C::IDX_OFF);
-      auto issue_ids = [&](int t) {  // 64 row ids of tile t -> slot t % 3, two per lane
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int i = lane + 32 * h, pos = t * C::TILE + i;
-          if (pos < id_lim) cp_async4(idx_sm + ((t % C::IDX_SLOTS) * C::TILE + i) * 4, p.kv_entries + kv_off + pos);
-        }
-      };
-      // one operand tile (K or V of tile t) into `buf`, signalling `full`
-      auto load_tile = [&](int t, uint32_t buf, uint32_t full, const CUtensorMap* map, const T* base, int64_t stride,
-                           bool dense, int first_row) {
-        if (dense) {
-          if (lane == 0) {
-            mbar_arrive_expect_tx(full, 16384);
-            tma_load_3d(buf, map, 0, kvh, first_row, full);
-            tma_load_3d(buf + 8192, map, 64, kvh, first_row, full);
-          } else {
-            mbar_arrive(full);
-          }
-          return;
-        }
-        const int* ids = ring + (t % C::IDX_SLOTS) * C::TILE;
-        const int c = lane & 15;
-        bool bad = false, stored = false;
-#pragma unroll 8
-        for (int i = 0; i < 32; ++i) {
-          const int r = (lane >> 4) + 2 * i, pos = t * C::TILE + r;
-          const uint32_t row = pos < id_lim ? (uint32_t)ids[r] : 0xffffffffu;
-          const bool ok = row < row_lim;  // padding (0xffffffff), negative and too-large ids all fail this test
-          bad |= !ok && pos < id_lim;
-          stored |= !ok;
-          cp_async16(buf + tc_swz(r, c, 8192), base + (int64_t)(ok ? row : 0u) * stride + c * 8, ok);
-        }
-        if (bad) flag_error(FT_DEV_BAD_KV_INDEX);
-        if (stored) proxy_fence();  // the zero rows were plain shared stores
-        mbar_arrive_on_cp_async(full);
-      };
-      const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)kvh * p.k_s1;
-      const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)kvh * p.v_s1;
-      if (ntiles > 0) issue_ids(0);
-      cp_async_commit();
-      if (ntiles > 1) issue_ids(1);
-      cp_async_commit();
-      for (int t = 0; t < ntiles && !dead; ++t) {
-        if (t + 2 < ntiles) issue_ids(t + 2);  // slot of tile t-1, whose ids are no longer needed
-        cp_async_commit();
-        cp_async_wait<2>();                     // ids of tile t have landed (this lane's copies)
-        __syncwarp();
-        // dense tile: 64 valid, consecutive row ids inside the buffer -> TMA
-        const int* ids = ring + (t % C::IDX_SLOTS) * C::TILE;
-        bool dense = false;
-        int first_row = 0;
-        if (tp.has_tma && (t + 1) * C::TILE <= id_lim) {
-          first_row = ids[0];
-          const bool mine = ids[lane] == first_row + lane && ids[lane + 32] == first_row + lane + 32;
-          dense = __all_sync(0xffffffffu, mine) && first_row >= 0 && (uint32_t)(first_row + C::TILE) <= row_lim;
-        }
-        const int b = t & 1;
-        if (!tc_wait(bar(C::K_EMPTY + b), (n_kempty[b]++ & 1) ^ 1, abort_flag)) {
-          give_up();
-          break;
-        }
-        load_tile(t, k_buf(t), bar(C::K_FULL + b), &tp.k_map, kbase, p.k_s0, dense, first_row);
-        if (!tc_wait(bar(C::V_EMPTY + b), (n_vempty[b]++ & 1) ^ 1, abort_flag)) {
-          give_up();
-          break;
-        }
-        load_tile(t, v_buf(t), bar(C::V_FULL + b), &tp.v_map, vbase, p.v_s0, dense, first_row);
-      }
-      cp_async_wait<0>();
-    } else if (warp == 4) {
-      // ================================================================ MMA issue
-      if (lane == 0) {
-        const uint32_t idesc_s = tc_idesc<T>(128, C::TILE, false);
-        const uint32_t idesc_o = tc_idesc<T>(128, C::D, true);
-        const uint64_t q_desc = tc_desc(q_sm, 16, 1024), p_desc = tc_desc(p_sm, 16, 1024);
-        auto issue_pv = [&](int t) {  // O += P_t V_t : 4 k-steps of 16 tokens
-          const int b = t & 1;
-          if (!tc_wait(bar(C::P_FULL), n_pfull++ & 1, abort_flag)) return false;
-          if (!tc_wait(bar(C::V_FULL + b), n_vfull[b]++ & 1, abort_flag)) return false;
-          proxy_fence();
-          tc_fence_after();
-          const uint64_t v_desc = tc_desc(v_buf(t), 8192, 1024);
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            tc_mma(tmem + C::O_COL, p_desc + (uint64_t)(ks * 2), v_desc + (uint64_t)(ks * 128), idesc_o,
-                   (t > 0 || ks > 0) ? 1u : 0u);
-          tc_commit(bar(C::V_EMPTY + b));
-          tc_commit(bar(C::PV_DONE));
-          return true;
-        };
-        for (int t = 0; t < ntiles && !dead; ++t) {
-          const int b = t & 1;
-          // S_t = Q K_t^T into S buffer b (free once the softmax of tile t-2 has read it)
-          if (!tc_wait(bar(C::K_FULL + b), n_kfull[b]++ & 1, abort_flag) ||
-              !tc_wait(bar(C::S_EMPTY + b), (n_sempty[b]++ & 1) ^ 1, abort_flag)) {
-            give_up();
-            break;
-          }
-          proxy_fence();
-          tc_fence_after();
-          const uint64_t k_desc = tc_desc(k_buf(t), 16, 1024);
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {  // 8 k-steps of 16 along head_dim: +32 B inside a block, +1 block after 4
-            const uint64_t a = q_desc + (uint64_t)((ks >> 2) * (16384 >> 4) + (ks & 3) * 2);
-            const uint64_t bb = k_desc + (uint64_t)((ks >> 2) * (8192 >> 4) + (ks & 3) * 2);
-            tc_mma(tmem + C::S_COL + b * C::TILE, a, bb, idesc_s, ks > 0);
-          }
-          tc_commit(bar(C::K_EMPTY + b));
-          tc_commit(bar(C::S_FULL + b));
-          if (t > 0 && !issue_pv(t - 1)) {
-            give_up();
-            break;
-          }
-        }
-        if (!dead && ntiles > 0 && !issue_pv(ntiles - 1)) give_up();
-      }
-      __syncwarp();
-    } else {
-      // ================================================================ softmax (one query row per thread)
-      const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32-lane quadrant
-      float m_used = -INFINITY, l_run = 0.f;
-      for (int j = 0; j < ntiles && !dead; ++j) {
-        const int b = j & 1;
-        if (!tc_wait(bar(C::S_FULL + b), n_sfull[b]++ & 1, abort_flag)) {
-          give_up();
-          break;
-        }
-        tc_fence_after();
-        float s[64];
-        const uint32_t s_col = t_lane + C::S_COL + b * C::TILE;
-        tmem_ld32(s_col, *reinterpret_cast<float(*)[32]>(&s[0]));
-        tmem_ld32(s_col + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
-        tc_fence_before();
-        mbar_arrive(bar(C::S_EMPTY + b));  // the scores are in registers: the buffer may take tile j+2
-        const int valid = kv_len - j * C::TILE;  // columns >= valid are padding (last tile only)
-        if (valid < C::TILE) {
-#pragma unroll
-          for (int c = 0; c < 64; ++c)
-            if (c >= valid) s[c] = -INFINITY;
-        }
-        float mx = fmaxf(s[0], s[1]);
-#pragma unroll
-        for (int c = 2; c < 64; c += 2) asm("max.f32 %0, %0, %1, %2;" : "+f"(mx) : "f"(s[c]), "f"(s[c + 1]));
-        mx *= scale2;  // scale2 > 0
-        float corr = 1.f;
-        bool grow = false;
-        if (mx > m_used + 8.f || m_used == -INFINITY) {  // the offset may lag the true maximum by up to 2^8
-          grow = mx > -INFINITY;
-          if (grow) {
-            corr = fast_exp2(m_used - mx);  // 0 on the first tile
-            m_used = mx;
-          }
-        }
-        l_run *= corr;
-        const float neg_off = m_used == -INFINITY ? 0.f : -m_used;
-        const float2 sc2 = make_float2(scale2, scale2), no2 = make_float2(neg_off, neg_off);
-        float2 sum2 = make_float2(0.f, 0.f);
-        uint32_t w[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {  // scores stay unscaled until the exponent: one packed FMA per pair
-          float2 x = __ffma2_rn(make_float2(s[2 * i], s[2 * i + 1]), sc2, no2);
-          x.x = fast_exp2(x.x);
-          x.y = fast_exp2(x.y);
-          sum2 = __fadd2_rn(sum2, x);
-          w[i] = pack2<T>(x.x, x.y);
-        }
-        l_run += sum2.x + sum2.y;
-        // P.V of the previous tile must be done before P and O are touched
-        if (j > 0) {
-          if (!tc_wait(bar(C::PV_DONE), n_pvdone++ & 1, abort_flag)) {
-            give_up();
-            break;
-          }
-          tc_fence_after();
-          if (__any_sync(0xffffffffu, grow)) {  // rescale this warp's rows of O in tensor memory
-#pragma unroll
-            for (int cb = 0; cb < 4; ++cb) {
-              float o[32];
-              tmem_ld32(t_lane + C::O_COL + cb * 32, o);
-#pragma unroll
-              for (int c = 0; c < 32; ++c) o[c] *= corr;
-              tmem_st32(t_lane + C::O_COL + cb * 32, o);
-            }
-            tmem_wait_st();
-          }
-        }
-        const uint32_t p_row = p_sm + (tid >> 3) * 1024 + (tid & 7) * 128;
-#pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8)
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + ((c8 ^ (tid & 7)) << 4)),
-                       "r"(w[4 * c8]), "r"(w[4 * c8 + 1]), "r"(w[4 * c8 + 2]), "r"(w[4 * c8 + 3])
-                       : "memory");
-        proxy_fence();      // P (generic stores) becomes visible to the tensor core
-        tc_fence_before();  // orders this thread's tcgen05.ld/st before the hand-off
-        mbar_arrive(bar(C::P_FULL));
-      }
-      // ---- epilogue: wait for the last P.V, normalise, write this thread's partial row
-      if (!dead && ntiles > 0 && !tc_wait(bar(C::PV_DONE), n_pvdone++ & 1, abort_flag)) give_up();
-      if (!dead) {
-        tc_fence_after();
-        const int prow = row0 + tid;
-        const bool live = prow < rows;
-        int slot = 0, gg = 0;
-        if (live) {
-          slot = prow / G;
-          gg = prow - slot * G;
-        }
-        const int64_t part = (int64_t)q_off + slot;
-        const bool store = live && part >= 0 && part < p.num_partial_rows;
-        const int head = kvh * G + gg;
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        float4* dst = reinterpret_cast<float4*>(p.mid_o + part * p.mo_s0 + (int64_t)head * p.mo_s1);
-#pragma unroll
-        for (int cb = 0; cb < 4; ++cb) {
-          float o[32];
-          if (ntiles > 0) {
-            tmem_ld32(t_lane + C::O_COL + cb * 32, o);  // warp-collective: every lane of the warp takes part
-          } else {
-#pragma unroll
-            for (int c = 0; c < 32; ++c) o[c] = 0.f;
-          }
-          if (store) {
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-              dst[cb * 8 + c] = make_float4(o[4 * c] * inv, o[4 * c + 1] * inv, o[4 * c + 2] * inv, o[4 * c + 3] * inv);
-          }
-        }
-        if (store)
-          p.mid_lse[part * p.ml_s0 + head] = l_run > 0.f ? (m_used + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
-      }
-    }
-    // ---- end of the pass: every role is done with the buffers and the TMEM columns
+  // end of a pass: every role is done with the buffers and the TMEM columns
+  auto pass_end = [&]() {
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (*abort_flag != 0) break;
+    if (*abort_flag != 0) return false;
+    g0 += ntiles;  // buffers and barrier phases carry on from where this pass stopped
+    ++pass;
+    return true;
+  };
+
+  // Each warpgroup sets its register budget on entry to its own code, so that the budget holds for all of it.
+  if (warp < 4) {
+    reg_grow<C::REGS_SOFTMAX>();
+    for (int row0 = 0; row0 < rows; row0 += C::ROWS) {
+      {
+        // ================================================================ softmax (one query row per thread)
+        const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32-lane quadrant
+        float m_used = -INFINITY, l_run = 0.f;
+        for (int j = 0; j < ntiles && !dead; ++j) {
+          const int g = g0 + j, b = g & 1;
+          if (!tc_wait(bar(C::S_FULL + b), (uint32_t)(g >> 1) & 1u, abort_flag)) {
+            give_up();
+            break;
+          }
+          tc_fence_after();
+          if (j == 0 && tid == 0) FT_TL_MARK(2);
+          if (j == 5 && tid == 0) FT_TL_MARK(10);
+          float s[64];
+          const uint32_t s_col = t_lane + C::S_COL + b * C::TILE;
+          tmem_ld32(s_col, *reinterpret_cast<float(*)[32]>(&s[0]));
+          tmem_ld32(s_col + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+          tc_fence_before();
+          mbar_arrive(bar(C::S_EMPTY + b));  // the scores are in registers: the buffer may take tile j+2
+          const int valid = kv_len - j * C::TILE;  // columns >= valid are padding (last tile only)
+          if (valid < C::TILE) {
+#pragma unroll
+            for (int c = 0; c < 64; ++c)
+              if (c >= valid) s[c] = -INFINITY;
+          }
+          float mx = fmaxf(s[0], s[1]);
+#pragma unroll
+          for (int c = 2; c < 64; c += 2) asm("max.f32 %0, %0, %1, %2;" : "+f"(mx) : "f"(s[c]), "f"(s[c + 1]));
+          mx *= scale2;  // scale2 > 0
+          float corr = 1.f;
+          bool grow = false;
+          if (mx > m_used + 8.f || m_used == -INFINITY) {  // the offset may lag the true maximum by up to 2^8
+            grow = mx > -INFINITY;
+            if (grow) {
+              corr = fast_exp2(m_used - mx);  // 0 on the first tile
+              m_used = mx;
+            }
+          }
+          l_run *= corr;
+          const float neg_off = m_used == -INFINITY ? 0.f : -m_used;
+          const float2 sc2 = make_float2(scale2, scale2), no2 = make_float2(neg_off, neg_off);
+          float2 sum2 = make_float2(0.f, 0.f);
+          uint32_t w[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {  // scores stay unscaled until the exponent: one packed FMA per pair
+            float2 x = __ffma2_rn(make_float2(s[2 * i], s[2 * i + 1]), sc2, no2);
+            x.x = fast_exp2(x.x);
+            x.y = fast_exp2(x.y);
+            sum2 = __fadd2_rn(sum2, x);
+            w[i] = pack2<T>(x.x, x.y);
+          }
+          l_run += sum2.x + sum2.y;
+          // P.V of the previous tile must be done before P and O are touched
+          if (j == 5 && tid == 0) FT_TL_MARK(11);
+          if (j > 0) {
+            if (!tc_wait(bar(C::PV_DONE), (uint32_t)(g - 1) & 1u, abort_flag)) {
+              give_up();
+              break;
+            }
+            tc_fence_after();
+            if (__any_sync(0xffffffffu, grow)) {  // rescale this warp's rows of O in tensor memory
+#pragma unroll
+              for (int cb = 0; cb < 4; ++cb) {
+                float o[32];
+                tmem_ld32(t_lane + C::O_COL + cb * 32, o);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) o[c] *= corr;
+                tmem_st32(t_lane + C::O_COL + cb * 32, o);
+              }
+              tmem_wait_st();
+            }
+          }
+          if (j == 5 && tid == 0) FT_TL_MARK(1);
+          const uint32_t p_row = p_sm + (tid >> 3) * 1024 + (tid & 7) * 128;
+#pragma unroll
+          for (int c8 = 0; c8 < 8; ++c8)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + ((c8 ^ (tid & 7)) << 4)),
+                         "r"(w[4 * c8]), "r"(w[4 * c8 + 1]), "r"(w[4 * c8 + 2]), "r"(w[4 * c8 + 3])
+                         : "memory");
+          proxy_fence();      // P (generic stores) becomes visible to the tensor core
+          tc_fence_before();  // orders this thread's tcgen05.ld/st before the hand-off
+          mbar_arrive(bar(C::P_FULL));
+          if (j == 5 && tid == 0) FT_TL_MARK(4);
+        }
+        // ---- epilogue: wait for the last P.V, normalise, write this thread's partial row
+        if (!dead && ntiles > 0 && !tc_wait(bar(C::PV_DONE), (uint32_t)(g0 + ntiles - 1) & 1u, abort_flag)) give_up();
+        if (!dead) {
+          tc_fence_after();
+          if (tid == 0) FT_TL_MARK(3);
+          const int prow = row0 + tid;
+          const bool live = prow < rows;
+          int slot = 0, gg = 0;
+          if (live) {
+            slot = prow / G;
+            gg = prow - slot * G;
+          }
+          const int64_t part = (int64_t)q_off + slot;
+          const bool store = live && part >= 0 && part < p.num_partial_rows;
+          const int head = kvh * G + gg;
+          const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+          // stage the normalised row in shared memory (every operand buffer is idle by now)
+          const uint32_t out_row = sm + (uint32_t)tid * C::OUT_STRIDE;
+#pragma unroll
+          for (int cb = 0; cb < 4; ++cb) {
+            float o[32];
+            if (ntiles > 0) {
+              tmem_ld32(t_lane + C::O_COL + cb * 32, o);  // warp-collective: every lane of the warp takes part
+            } else {
+#pragma unroll
+              for (int c = 0; c < 32; ++c) o[c] = 0.f;
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(out_row + (cb * 8 + c) * 16),
+                           "f"(o[4 * c] * inv), "f"(o[4 * c + 1] * inv), "f"(o[4 * c + 2] * inv), "f"(o[4 * c + 3] * inv)
+                           : "memory");
+          }
+          if (tid == 0) FT_TL_MARK(8);
+          if (store)
+            p.mid_lse[part * p.ml_s0 + head] = l_run > 0.f ? (m_used + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+          // each warp staged its own 32 rows: write them out one row per instruction (32 lanes x 16 bytes)
+          __syncwarp();
+          float* my_dst = store ? p.mid_o + part * p.mo_s0 + (int64_t)head * p.mo_s1 : nullptr;
+          const uint32_t warp_rows = sm + (uint32_t)(warp * 32) * C::OUT_STRIDE + lane * 16;
+#pragma unroll 8
+          for (int i = 0; i < 32; ++i) {
+            float* dst = reinterpret_cast<float*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_dst), i));
+            float4 x;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n"
+                         : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
+                         : "r"(warp_rows + i * C::OUT_STRIDE));
+            if (dst != nullptr) reinterpret_cast<float4*>(dst)[lane] = x;
+          }
+          if (tid == 0) FT_TL_MARK(9);
+        }
+      }
+      if (!pass_end()) break;
+    }
+  } else {
+    reg_shrink<C::REGS_OTHER>();
+    for (int row0 = 0; row0 < rows; row0 += C::ROWS) {
+      if (warp >= 6) {
+        // ================================================================ Q gather (64 threads)
+        // request ids of this pass's slots -> the (still unused) P buffer, then the rows themselves
+        const int qt = tid - 192, ld_c = qt & 15, ld_r = qt >> 4;
+        const int row_end = min(rows, row0 + C::ROWS);
+        const int first_slot = row0 / G, nslots = (row_end - 1) / G - first_slot + 1;  // <= 128
+        for (int i = qt; i < nslots; i += 64) {
+          const int64_t part = (int64_t)q_off + first_slot + i;
+          if (part >= 0 && part < p.num_partial_rows) {
+            cp_async4(p_sm + i * 4, p.q_entries + part);
+          } else {
+            flag_error(FT_DEV_BAD_ROW_INDEX);
+            asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(p_sm + i * 4), "r"(-1) : "memory");
+          }
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        asm volatile("bar.sync 1, 64;\n" ::: "memory");
+        const int* req_of = reinterpret_cast<const int*>(smem + C::P_OFF);
+        if (tp.q_box_rows > 0) {
+          // The G rows of a request are adjacent heads of one Q row: one box of up to 8 rows x 64 elements per
+          // half.  G divides 128 here, so passes start on a request and a box never straddles an 8-row group.
+          const int br = tp.q_box_rows;
+          uint32_t bytes = 0;
+          for (int i = qt; i < nslots; i += 64) {
+            const int req = req_of[i];
+            if (req >= 0 && req < p.batch)
+              bytes += (uint32_t)G * 256u;
+            else if ((int64_t)q_off + first_slot + i >= 0 && (int64_t)q_off + first_slot + i < p.num_partial_rows)
+              flag_error(FT_DEV_BAD_Q_INDEX);
+          }
+          mbar_arrive_expect_tx(bar(C::Q_FULL), bytes);
+          for (int i = qt; i < nslots; i += 64) {
+            const int req = req_of[i];
+            if (req >= 0 && req < p.batch) {
+              for (int sub = 0; sub < G; sub += br) {
+                const int r = i * G + sub;
+                const uint32_t dst = q_sm + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+                tma_load_3d(dst, &tp.q_map, 0, kvh * G + sub, req, bar(C::Q_FULL));
+                tma_load_3d(dst + 16384, &tp.q_map, 64, kvh * G + sub, req, bar(C::Q_FULL));
+              }
+            }
+          }
+        } else {
+#pragma unroll 4
+          for (int ps = 0; ps < 32; ++ps) {
+            const int r = ps * 4 + ld_r;
+            const int prow = row0 + r;
+            int64_t src = -1;
+            if (prow < rows) {
+              const int slot = prow / G, gg = prow - slot * G;
+              const int req = req_of[slot - first_slot];
+              if (req >= 0 && req < p.batch)
+                src = (int64_t)req * p.q_s0 + (int64_t)(kvh * G + gg) * p.q_s1 + ld_c * 8;
+              else if ((int64_t)q_off + slot >= 0 && (int64_t)q_off + slot < p.num_partial_rows)
+                flag_error(FT_DEV_BAD_Q_INDEX);
+            }
+            cp_async16(q_sm + tc_swz(r, ld_c, 16384), reinterpret_cast<const T*>(p.q) + (src >= 0 ? src : 0), src >= 0);
+          }
+          proxy_fence();                            // rows past the end were zero-filled with plain shared stores
+          mbar_arrive_on_cp_async(bar(C::Q_FULL));  // one arrival per thread once its copies have landed
+          cp_async_wait<0>();
+        }
+      } else if (warp == 5) {
+        // ================================================================ loader
+        const int* ring = reinterpret_cast<const int*>(smem + C::IDX_OFF);
+        auto issue_ids = [&](int t) {  // 64 row ids of tile t -> slot t % 3, two per lane
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int i = lane + 32 * h, pos = t * C::TILE + i;
+            if (pos < id_lim) cp_async4(idx_sm + ((t % C::IDX_SLOTS) * C::TILE + i) * 4, p.kv_entries + kv_off + pos);
+          }
+        };
+        // one operand tile (K or V of tile t) into `buf`, signalling `full`
+        auto load_tile = [&](int t, uint32_t buf, uint32_t full, const CUtensorMap* map, const T* base, int64_t stride,
+                             bool dense, int first_row) {
+          if (dense) {
+            if (lane == 0) {
+              mbar_arrive_expect_tx(full, 16384);
+              tma_load_3d(buf, map, 0, kvh, first_row, full);
+              tma_load_3d(buf + 8192, map, 64, kvh, first_row, full);
+            } else {
+              mbar_arrive(full);
+            }
+            return;
+          }
+          const int* ids = ring + (t % C::IDX_SLOTS) * C::TILE;
+          const int c = lane & 15;
+          bool bad = false, stored = false;
+#pragma unroll 4
+          for (int i = 0; i < 32; ++i) {
+            const int r = (lane >> 4) + 2 * i, pos = t * C::TILE + r;
+            const uint32_t row = pos < id_lim ? (uint32_t)ids[r] : 0xffffffffu;
+            const bool ok = row < row_lim;  // padding (0xffffffff), negative and too-large ids all fail this test
+            bad |= !ok && pos < id_lim;
+            stored |= !ok;
+            cp_async16(buf + tc_swz(r, c, 8192), base + (int64_t)(ok ? row : 0u) * stride + c * 8, ok);
+          }
+          if (bad) flag_error(FT_DEV_BAD_KV_INDEX);
+          if (stored) proxy_fence();  // the zero rows were plain shared stores
+          mbar_arrive_on_cp_async(full);
+        };
+        const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)kvh * p.k_s1;
+        const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)kvh * p.v_s1;
+        if (ntiles > 0) issue_ids(0);
+        cp_async_commit();
+        if (ntiles > 1) issue_ids(1);
+        cp_async_commit();
+        // Step s loads K of tile s and V of tile s-1: K runs one tile ahead, so that a V buffer still held by
+        // the P.V of two tiles back never keeps the next K load (and with it the next S) waiting.
+        bool dense_prev = false;
+        int first_prev = 0;
+        for (int s = 0; s <= ntiles && !dead; ++s) {
+          bool dense = false;
+          int first_row = 0;
+          if (s < ntiles) {
+            const int g = g0 + s, b = g & 1;
+            cp_async_wait<1>();  // ids of tile s have landed (this lane's copies)
+            __syncwarp();
+            if (s == 0 && lane == 0) FT_TL_MARK(5);
+            // dense tile: 64 valid, consecutive row ids inside the buffer -> TMA
+            const int* ids = ring + (s % C::IDX_SLOTS) * C::TILE;
+            if (tp.has_tma && (s + 1) * C::TILE <= id_lim) {
+              first_row = ids[0];
+              const bool mine = ids[lane] == first_row + lane && ids[lane + 32] == first_row + lane + 32;
+              dense = __all_sync(0xffffffffu, mine) && first_row >= 0 && (uint32_t)(first_row + C::TILE) <= row_lim;
+            }
+            if (!tc_wait(bar(C::K_EMPTY + b), ((uint32_t)(g >> 1) & 1u) ^ 1u, abort_flag)) {
+              give_up();
+              break;
+            }
+            load_tile(s, k_buf(g), bar(C::K_FULL + b), &tp.k_map, kbase, p.k_s0, dense, first_row);
+          }
+          if (s > 0) {
+            const int g = g0 + s - 1, b = g & 1;
+            if (!tc_wait(bar(C::V_EMPTY + b), ((uint32_t)(g >> 1) & 1u) ^ 1u, abort_flag)) {
+              give_up();
+              break;
+            }
+            load_tile(s - 1, v_buf(g), bar(C::V_FULL + b), &tp.v_map, vbase, p.v_s0, dense_prev, first_prev);
+          }
+          if (s + 2 < ntiles) issue_ids(s + 2);  // into the slot of tile s-1, whose ids were last used just above
+          cp_async_commit();
+          dense_prev = dense;
+          first_prev = first_row;
+        }
+        cp_async_wait<0>();
+      } else {
+        // ================================================================ MMA issue
+        if (lane == 0) {
+          const uint32_t idesc_s = tc_idesc<T>(128, C::TILE, false);
+          const uint32_t idesc_o = tc_idesc<T>(128, C::D, true);
+          const uint64_t q_desc = tc_desc(q_sm, 16, 1024), p_desc = tc_desc(p_sm, 16, 1024);
+          auto issue_pv = [&](int t) {  // O += P_t V_t : 4 k-steps of 16 tokens
+            const int g = g0 + t, b = g & 1;
+            if (!tc_wait(bar(C::P_FULL), (uint32_t)g & 1u, abort_flag)) return false;
+            if (!tc_wait(bar(C::V_FULL + b), (uint32_t)(g >> 1) & 1u, abort_flag)) return false;
+            proxy_fence();
+            tc_fence_after();
+            const uint64_t v_desc = tc_desc(v_buf(g), 8192, 1024);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              tc_mma(tmem + C::O_COL, p_desc + (uint64_t)(ks * 2), v_desc + (uint64_t)(ks * 128), idesc_o,
+                     (t > 0 || ks > 0) ? 1u : 0u);
+            tc_commit(bar(C::V_EMPTY + b));
+            tc_commit(bar(C::PV_DONE));
+            return true;
+          };
+          if (ntiles > 0 && !tc_wait(bar(C::Q_FULL), (uint32_t)pass & 1u, abort_flag)) give_up();
+          FT_TL_MARK(7);
+          for (int t = 0; t < ntiles && !dead; ++t) {
+            const int g = g0 + t, b = g & 1;
+            const uint32_t use = (uint32_t)(g >> 1) & 1u;
+            // S_t = Q K_t^T into S buffer b (free once the softmax of the tile two before has read it)
+            if (!tc_wait(bar(C::K_FULL + b), use, abort_flag) || !tc_wait(bar(C::S_EMPTY + b), use ^ 1u, abort_flag)) {
+              give_up();
+              break;
+            }
+            if (t == 0) FT_TL_MARK(6);
+            proxy_fence();
+            tc_fence_after();
+            const uint64_t k_desc = tc_desc(k_buf(g), 16, 1024);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {  // 8 k-steps of 16 along head_dim: +32 B inside a block, +1 block after 4
+              const uint64_t a = q_desc + (uint64_t)((ks >> 2) * (16384 >> 4) + (ks & 3) * 2);
+              const uint64_t bb = k_desc + (uint64_t)((ks >> 2) * (8192 >> 4) + (ks & 3) * 2);
+              tc_mma(tmem + C::S_COL + b * C::TILE, a, bb, idesc_s, ks > 0);
+            }
+            tc_commit(bar(C::K_EMPTY + b));
+            tc_commit(bar(C::S_FULL + b));
+            if (t > 0 && !issue_pv(t - 1)) {
+              give_up();
+              break;
+            }
+          }
+          if (!dead && ntiles > 0 && !issue_pv(ntiles - 1)) give_up();
+        }
+        __syncwarp();
+      }
+      if (!pass_end()) break;
+    }
   }
 
   // ---- release tensor memory
@@ -535,7 +651,9 @@ __global__ void __launch_bounds__(TcCfg::THREADS, 2) stage1_tc_kernel(const __gr
   extern __shared__ __align__(1024) uint8_t smem[];
   int vn, kvh;
   task_of_block(tp.p, blockIdx.x, vn, kvh);
+  FT_TL_BEGIN();
   tc_body<T>(tp, smem, vn, kvh);
+  FT_TL_END(1);
 }
 
 // Both task families in one grid (head_dim 128): the first `p.node_split` vnodes of the launch are
@@ -546,11 +664,21 @@ __global__ void __launch_bounds__(TcCfg::THREADS, 2) stage1_fused_kernel(const _
   extern __shared__ __align__(1024) uint8_t smem[];
   int vn, kvh;
   task_of_block(tp.p, blockIdx.x, vn, kvh);  // blocks [0, node_split * heads) are the many-row tasks: they start first
+  FT_TL_BEGIN();
   if (vn - tp.p.node_offset < tp.p.node_split) {
     tc_body<T>(tp, smem, vn, kvh);
+    FT_TL_END(1);
   } else {
-    if (threadIdx.x >= 128) return;  // the few-row body is written for four warps
+    // This CTA will not allocate tensor memory.  Saying so at once matters: the SM admits no second CTA of a
+    // kernel that uses tensor memory while a resident one still holds the right to allocate.
+    if (threadIdx.x < 32) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    if (threadIdx.x >= 128) {  // the few-row body is written for four warps: the others hand over their registers
+      reg_shrink<24>();
+      return;
+    }
+    reg_grow<TcCfg::REGS_SOFTMAX>();
     narrow_dispatch<T, 128>(tp.p, smem, vn, kvh);
+    FT_TL_END(2);
   }
 }
 
