@@ -137,6 +137,8 @@ ft::Stage1Params stage1_params(const ft_decode_args* a) {
   p.node_offset = 0;
   p.node_count = 0;
   p.node_split = 0;
+  p.lead_wide = 0;
+  p.workers = 0;
   p.num_kv_heads = a->num_kv_heads;
   p.sm_scale = a->sm_scale;
   return p;
@@ -178,28 +180,33 @@ int launch_narrow(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
   return FT_OK;
 }
 
+int sm_count(int dev) {
+  static int sms[64] = {};
+  if (dev < 0 || dev >= 64) return 148;
+  if (sms[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    sms[dev] = n;
+  }
+  return sms[dev];
+}
+
 // Persistent few-row kernel: two CTAs per SM, each walking its share of the tasks.
 template <typename T, int D>
-int launch_stream(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
+int launch_stream(const ft::TcParams& tp, int hkv, cudaStream_t st) {
   using C = ft::StreamCfg<D>;
   static bool configured[64] = {};
-  static int sms[64] = {};
   int dev = 0;
   FT_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64 || !configured[dev]) {
     FT_CUDA_OK(cudaFuncSetAttribute(ft::stage1_stream_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     C::SMEM_BYTES));
-    int n = 0;
-    FT_CUDA_OK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
-    if (dev >= 0 && dev < 64) {
-      sms[dev] = n;
-      configured[dev] = true;
-    }
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  const int64_t tasks = (int64_t)p.node_count * hkv;
-  const int64_t slots = 2LL * (dev >= 0 && dev < 64 && sms[dev] > 0 ? sms[dev] : 148);
+  const int64_t tasks = (int64_t)tp.p.node_count * hkv;
+  const int64_t slots = 2LL * sm_count(dev);
   const unsigned grid = (unsigned)(tasks < slots ? tasks : slots);
-  ft::stage1_stream_kernel<T, D><<<grid, 128, C::SMEM_BYTES, st>>>(p);
+  ft::stage1_stream_kernel<T, D><<<grid, 128, C::SMEM_BYTES, st>>>(tp);
   FT_CUDA_OK(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return FT_OK;
@@ -233,16 +240,16 @@ struct MapKey {
   }
 };
 
-// Descriptor of a [rows, heads, 128] 16-bit tensor (element strides s0, s1), box 64 (head_dim) x box_heads x
+// Descriptor of a [rows, heads, head_dim] 16-bit tensor (element strides s0, s1), box 64 (head_dim) x box_heads x
 // box_rows, 128-byte swizzle.  Descriptors are cached by buffer identity; encoding one costs about a microsecond.
-bool tensor_map_3d(CUtensorMap* out, const void* base, int dtype, int64_t rows, int heads, int64_t s0, int64_t s1,
-                   int box_heads, int box_rows) {
+bool tensor_map_3d(CUtensorMap* out, const void* base, int dtype, int head_dim, int64_t rows, int heads, int64_t s0,
+                   int64_t s1, int box_heads, int box_rows) {
   constexpr int SLOTS = 128;
   static std::mutex mu;
   static MapKey keys[SLOTS];
   static CUtensorMap maps[SLOTS];
   static int used = 0, next = 0;
-  const MapKey key{base, rows, s0, s1, heads, dtype, box_heads * 1024 + box_rows};
+  const MapKey key{base, rows, s0, s1, heads, dtype + 16 * head_dim, box_heads * 1024 + box_rows};
   std::lock_guard<std::mutex> lock(mu);
   for (int i = 0; i < used; ++i)
     if (keys[i] == key) {
@@ -251,7 +258,7 @@ bool tensor_map_3d(CUtensorMap* out, const void* base, int dtype, int64_t rows, 
     }
   EncodeTiledFn enc = encode_tiled_fn();
   if (enc == nullptr || rows <= 0 || rows > 0x7fffffffLL || heads <= 0) return false;
-  const cuuint64_t dims[3] = {128, (cuuint64_t)heads, (cuuint64_t)rows};
+  const cuuint64_t dims[3] = {(cuuint64_t)head_dim, (cuuint64_t)heads, (cuuint64_t)rows};
   const cuuint64_t strides[2] = {(cuuint64_t)s1 * 2, (cuuint64_t)s0 * 2};  // bytes, for dimensions 1 and 2
   const cuuint32_t box[3] = {64, (cuuint32_t)box_heads, (cuuint32_t)box_rows};
   const cuuint32_t estr[3] = {1, 1, 1};
@@ -272,14 +279,18 @@ ft::TcParams tc_params(const ft::Stage1Params& p, const ft_decode_args* a) {
   ft::TcParams tp;
   memset(&tp, 0, sizeof(tp));
   tp.p = p;
-  tp.has_tma =
-      tensor_map_3d(&tp.k_map, a->k_buffer, a->dtype, a->kv_rows, a->num_kv_heads, a->k_stride0, a->k_stride1, 1, 64) &&
-      tensor_map_3d(&tp.v_map, a->v_buffer, a->dtype, a->kv_rows, a->num_kv_heads, a->v_stride0, a->v_stride1, 1, 64);
-  // Q by TMA: one box per request covering its G heads (at most 8 per box), when G is a power of two up to 128
+  const int d = a->head_dim;
+  tp.has_tma = tensor_map_3d(&tp.k_map, a->k_buffer, a->dtype, d, a->kv_rows, a->num_kv_heads, a->k_stride0,
+                             a->k_stride1, 1, 64) &&
+               tensor_map_3d(&tp.v_map, a->v_buffer, a->dtype, d, a->kv_rows, a->num_kv_heads, a->v_stride0,
+                             a->v_stride1, 1, 64);
+  // Q by TMA (tcgen05 kernel, head_dim 128): one box per request covering its G heads (at most 8 per box), or one
+  // box for a whole tile of consecutive requests, when G is a power of two up to 128
   const int g = p.group;
-  if (tp.has_tma && g >= 1 && g <= 128 && (g & (g - 1)) == 0) {
+  if (tp.has_tma && d == 128 && g >= 1 && g <= 128 && (g & (g - 1)) == 0) {
     const int box_heads = g < 8 ? g : 8;
-    if (tensor_map_3d(&tp.q_map, a->q, a->dtype, a->batch, a->num_qo_heads, a->q_stride0, a->q_stride1, box_heads, 1))
+    if (tensor_map_3d(&tp.q_map, a->q, a->dtype, d, a->batch, a->num_qo_heads, a->q_stride0, a->q_stride1, box_heads, 1) &&
+        tensor_map_3d(&tp.q_map_tile, a->q, a->dtype, d, a->batch, a->num_qo_heads, a->q_stride0, a->q_stride1, g, 128 / g))
       tp.q_box_rows = box_heads;
   }
   return tp;
@@ -303,9 +314,11 @@ int launch_tc(const ft::TcParams& p, int hkv, cudaStream_t st) {
 }
 
 template <typename T>
-int launch_fused(const ft::TcParams& p, int hkv, cudaStream_t st) {
-  constexpr int smem = ft::TcCfg::SMEM_BYTES > ft::NarrowCfg<128, 2>::SMEM_BYTES ? ft::TcCfg::SMEM_BYTES
-                                                                                 : ft::NarrowCfg<128, 2>::SMEM_BYTES;
+int launch_fused(ft::TcParams p, int hkv, cudaStream_t st) {
+  constexpr int smem_a = ft::TcCfg::SMEM_BYTES > ft::StreamCfg<128>::SMEM_BYTES ? ft::TcCfg::SMEM_BYTES
+                                                                                : ft::StreamCfg<128>::SMEM_BYTES;
+  constexpr int smem = smem_a > ft::NarrowCfg<128, 2>::SMEM_BYTES ? smem_a : ft::NarrowCfg<128, 2>::SMEM_BYTES;
+  static_assert(smem <= 115712, "two CTAs must fit in one SM's shared memory");
   static bool configured[64] = {};
   int dev = 0;
   FT_CUDA_OK(cudaGetDevice(&dev));
@@ -313,8 +326,20 @@ int launch_fused(const ft::TcParams& p, int hkv, cudaStream_t st) {
     FT_CUDA_OK(cudaFuncSetAttribute(ft::stage1_fused_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  const unsigned grid = (unsigned)p.p.node_count * (unsigned)hkv;
-  ft::stage1_fused_kernel<T><<<grid, ft::TcCfg::THREADS, smem, st>>>(p);
+  // Few-row tasks: a full set of persistent workers when each would get several tasks and the many-row CTAs
+  // do not fill the device more than once (the task pipeline then hides the per-task start-up; the workers
+  // take the slots the many-row CTAs leave and, as those finish, theirs too); one CTA per task otherwise (the
+  // hardware then slots the small CTAs in wherever a many-row CTA finishes).  Many-row CTAs go first.
+  const int64_t wide = (int64_t)p.p.node_split * hkv;
+  const int64_t few = (int64_t)(p.p.node_count - p.p.node_split) * hkv;
+  const int64_t slots = 2LL * sm_count(dev);
+  const int64_t workers = few >= 4 * slots && wide <= slots ? slots : 0;
+  const int64_t few_ctas = workers > 0 ? workers : few;
+  const int64_t lead = wide;
+  if (wide + few_ctas > 0x7fffffffLL) return fail(FT_ERR_TOO_LARGE, "vnodes x kv heads exceeds the grid limit");
+  p.p.workers = (int)workers;
+  p.p.lead_wide = (int)lead;
+  ft::stage1_fused_kernel<T><<<(unsigned)(wide + few_ctas), ft::TcCfg::THREADS, smem, st>>>(p);
   FT_CUDA_OK(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return FT_OK;
@@ -328,7 +353,7 @@ int launch_tensor(const ft::Stage1Params& p, const ft_decode_args* a, int hkv, c
     if (path == FT_PATH_TCGEN05 || ((path == FT_PATH_AUTO || path == FT_PATH_STREAM) && max_rows > 16))
       return launch_tc<T>(tc_params(p, a), hkv, st);
   }
-  if (path == FT_PATH_STREAM && max_rows <= 16) return launch_stream<T, D>(p, hkv, st);
+  if (path == FT_PATH_STREAM && max_rows <= 16) return launch_stream<T, D>(tc_params(p, a), hkv, st);
   if (path != FT_PATH_MMA_WIDE && max_rows <= 16) return launch_narrow<T, D>(p, hkv, st);
   return launch_mma<T, D>(p, hkv, st);
 }
@@ -370,8 +395,19 @@ int launch_stage2(const ft::Stage2Params& p, cudaStream_t st) {
   if (pairs == 0) return FT_OK;
   const int64_t blocks = (pairs + 3) / 4;
   if (blocks > 0x7fffffffLL) return fail(FT_ERR_TOO_LARGE, "batch x heads too large for one launch");
-  ft::stage2_merge_kernel<T><<<(unsigned)blocks, 128, 0, st>>>(p);
-  FT_CUDA_OK(cudaGetLastError());
+  // launched with permission to be scheduled before the preceding kernel (stage 1) has drained; the kernel itself
+  // waits for that kernel's completion before it touches the partial buffers
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  FT_CUDA_OK(cudaLaunchKernelEx(&cfg, ft::stage2_merge_kernel<T>, p));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return FT_OK;
 }

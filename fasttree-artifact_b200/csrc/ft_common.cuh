@@ -71,6 +71,8 @@ struct Stage1Params {
   int32_t node_count;   // vnodes in this launch
   int32_t num_kv_heads;
   int32_t node_split;   // fused launch: vnodes [0, node_split) of the launch are many-row tasks
+  int32_t lead_wide;    // fused launch: many-row CTAs placed before the few-row CTAs in block order
+  int32_t workers;      // fused launch: persistent few-row workers (0: one CTA per few-row task)
   float sm_scale;
 };
 
@@ -88,6 +90,12 @@ struct Stage2Params {
   int32_t heads;
   int32_t head_dim;
 };
+
+// Programmatic dependent launch: stage 1 lets the next kernel of the stream be scheduled while its own CTAs are
+// still running; stage 2 is launched with that permission and waits here until stage 1 has completed and its
+// writes are visible, so only its launch latency and its reads of the plan tables overlap stage 1's tail.
+__device__ __forceinline__ void allow_dependent_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void wait_for_prior_grid() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
 // Tensor-core kernels use a 1-D grid with the kv head varying fastest, so that CTAs launched next to
 // each other read the same tokens' rows (adjacent 2*D-byte slices of one pool row).

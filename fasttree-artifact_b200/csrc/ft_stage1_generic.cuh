@@ -14,6 +14,7 @@ namespace ft {
 
 template <typename T>
 __global__ void __launch_bounds__(128) stage1_generic_kernel(Stage1Params p) {
+  allow_dependent_launch();
   constexpr int MAXJ = 8;  // 8 x 32 lanes = head_dim up to 256
   constexpr int TB = 4;    // tokens per step
   const int vn = blockIdx.x + p.node_offset;

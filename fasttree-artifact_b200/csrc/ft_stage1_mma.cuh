@@ -108,8 +108,16 @@ struct MmaCfg {
   static constexpr int WIDE_IDXB = 128;         // row-id block of the wide kernel (2 x 512 B: all the room two CTAs/SM leave)
   static constexpr int WIDE_IDX_BYTES = 2 * WIDE_IDXB * 4;
   static constexpr int SMEM_BYTES = Q_BYTES + WIDE_IDX_BYTES + (PIPE_BYTES > EPI_BYTES ? PIPE_BYTES : EPI_BYTES);
-  __device__ static __forceinline__ uint32_t swz(int row, int chunk) {
+  // Q rows: one row after the other, the 16-byte chunks of a row XOR-swizzled by the row
+  __device__ static __forceinline__ uint32_t swzq(int row, int chunk) {
     return static_cast<uint32_t>(row * ROWB + ((chunk ^ (row & 7)) << 4));
+  }
+  // K/V tiles: 64-element (128-byte) column blocks one after the other, each [TILE rows][128 bytes] with the
+  // chunks of a row XOR-swizzled by the row: the layout a tiled TMA copy with the 128-byte swizzle writes, and
+  // conflict-free for ldmatrix and 16-byte cp.async alike
+  static constexpr int BLOCK_BYTES = TILE * 128;
+  __device__ static __forceinline__ uint32_t swz(int row, int chunk) {
+    return static_cast<uint32_t>((chunk >> 3) * BLOCK_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
   }
 };
 
@@ -315,6 +323,7 @@ __device__ __forceinline__ void mma_tile(const uint32_t k_sm, const uint32_t v_s
 
 template <typename T, int D>
 __global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
+  allow_dependent_launch();
   using C = MmaCfg<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t q_sm = smem_u32(smem);
@@ -373,7 +382,7 @@ __global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
     for (int ps = 0; ps < QPASSES; ++ps) {
       if (ps < q_passes) {
         const bool ok = q_src[ps] >= 0;
-        cp_async16(q_sm + C::swz(ps * C::TPP + ld_r, ld_c),
+        cp_async16(q_sm + C::swzq(ps * C::TPP + ld_r, ld_c),
                    reinterpret_cast<const T*>(p.q) + (ok ? q_src[ps] : 0), ok);
       }
     }
@@ -391,7 +400,7 @@ __global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
       if (j == 0 && active) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          ldmatrix_x4(qf[kk], q_sm + C::swz(my_rb * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * kk + (lane >> 4)));
+          ldmatrix_x4(qf[kk], q_sm + C::swzq(my_rb * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * kk + (lane >> 4)));
       }
       if (active) {
         const uint32_t k_sm = pipe.k_stage(j), v_sm = pipe.v_stage(j);

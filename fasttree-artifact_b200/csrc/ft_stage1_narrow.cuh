@@ -98,7 +98,7 @@ __device__ __forceinline__ void narrow_body(const Stage1Params& p, uint8_t* smem
       const int r = ps * C::TPP + ld_r;
       if (r < N::ROWS) {
         const bool ok = q_src[ps] >= 0;
-        cp_async16(q_sm + C::swz(r, ld_c), reinterpret_cast<const T*>(p.q) + (ok ? q_src[ps] : 0), ok);
+        cp_async16(q_sm + C::swzq(r, ld_c), reinterpret_cast<const T*>(p.q) + (ok ? q_src[ps] : 0), ok);
       }
     }
     pipe.prime_indices();  // also lands Q
@@ -124,8 +124,8 @@ __device__ __forceinline__ void narrow_body(const Stage1Params& p, uint8_t* smem
         for (int nq = 0; nq < NQ; ++nq)
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
-            qb[nq][kk][0] = lds32(q_sm + C::swz(nq * 8 + g8, 2 * kk) + 4 * t4);
-            qb[nq][kk][1] = lds32(q_sm + C::swz(nq * 8 + g8, 2 * kk + 1) + 4 * t4);
+            qb[nq][kk][0] = lds32(q_sm + C::swzq(nq * 8 + g8, 2 * kk) + 4 * t4);
+            qb[nq][kk][1] = lds32(q_sm + C::swzq(nq * 8 + g8, 2 * kk + 1) + 4 * t4);
           }
       }
       const uint32_t k_sm = pipe.k_stage(j), v_sm = pipe.v_stage(j);
@@ -283,6 +283,7 @@ __device__ __forceinline__ void narrow_dispatch(const Stage1Params& p, uint8_t* 
 
 template <typename T, int D>
 __global__ void __launch_bounds__(128, 2) stage1_narrow_kernel(Stage1Params p) {
+  allow_dependent_launch();
   extern __shared__ __align__(1024) uint8_t smem[];
   int vn, kvh;
   task_of_block(p, blockIdx.x, vn, kvh);

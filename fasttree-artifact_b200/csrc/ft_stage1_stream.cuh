@@ -1,28 +1,43 @@
-// Stage 1 for few-row tasks as a PERSISTENT kernel: each CTA walks a list of
+// Stage 1 for few-row tasks as PERSISTENT workers: each CTA walks a list of
 // (vnode, kv head) tasks and keeps ONE software pipeline running across task
 // boundaries, so the start-up latency of a task (metadata -> row ids -> first
-// K/V tile) is hidden behind the tiles of the tasks before it.  This is what
-// short leaves need: a 64-token leaf is a single tile, and with one CTA per
-// task its whole life is start-up latency.
+// K/V tile) is hidden behind the tiles of the tasks before it.  This
+// is what short leaves need: a 64-token leaf is a single tile, and with one
+// CTA per task its whole life is start-up latency.
 //
 // The per-tile arithmetic is that of the swapped-operand kernel
 // (ft_stage1_narrow.cuh): S^T = K.Q^T and O^T += V^T.P^T with m16n8k16, four
 // warps splitting every 64-token tile by tokens, merged through shared memory at
 // the end of the task.
 //
-// Task list of CTA c: tasks c, c + gridDim.x, c + 2*gridDim.x, ... of the launch
-// (task = vnode * kv_heads + kv_head, so the planner's longest-first order is
-// dealt round-robin).  Three cursors walk the same (task, tile) sequence:
-//   ids cursor   5 tiles ahead   row ids of a tile (and the task's request ids)
-//                                -> shared-memory rings, by cp.async
-//   kv cursor    2 tiles ahead   the tile's K/V rows (and the task's Q rows)
-//                                -> 3-stage ring / 3 Q buffers, by cp.async
-//   consumer                     MMA + online softmax; epilogue at a task's last
-//                                tile, staged through the ring stage just freed
-// One cp.async group per tile; metadata of up to MAXT tasks per round sits in
-// shared memory.
+// Task list of worker w out of W: tasks w, w + W, w + 2W, ... of the launch's
+// few-row tasks ((vnode, kv head) pairs in plan order, kv head fastest, so the
+// planner's longest-first order is dealt round-robin and the workers that run
+// side by side read adjacent slices of the same pool rows).  The assignment is
+// static: all workers of a launch start together, and a shared counter would
+// put an atomic's round trip on every worker's start-up path.
+//
+// Pipeline: every loop iteration is one slot.  A slot is a (task, tile) pair or
+// a bubble, decided when it enters; the stages sit at fixed distances,
+//   iteration s      row ids of the tile (and the task's request ids) -> rings
+//   iteration s + 2  are the 64 row ids consecutive?  (one warp; the answer is
+//                    read by everyone one iteration later)
+//   iteration s + 3  K/V rows of the tile -> 3-stage ring: four tiled TMA copies
+//                    (128-byte swizzle, no multicast) for a consecutive tile,
+//                    16-byte cp.async copies row by row otherwise; the task's Q
+//                    rows with cp.async
+//   iteration s + 5  MMA + online softmax; at a task's last tile the epilogue,
+//                    staged through the ring stage just freed
+// Row ids, request ids, Q rows and task metadata travel in cp.async groups, one
+// per iteration with wait_group 1 at the top, so such a copy issued in iteration
+// i is complete in iteration i + 2 whatever its latency.  A K/V tile signals an
+// mbarrier of its ring stage (transaction bytes for TMA, one arrival per thread
+// for cp.async), which the consumer waits on - bounded.  Task metadata enters a
+// 16-entry ring at least two iterations before the task's first slot.  No stage
+// waits on an earlier one: when an input is not there yet the slot is a bubble.
 #pragma once
 
+#include "ft_async.cuh"
 #include "ft_common.cuh"
 #include "ft_stage1_mma.cuh"
 #include "ft_stage1_narrow.cuh"
@@ -37,24 +52,22 @@ struct StreamCfg {
   static constexpr int IDS_SLOTS = 8;
   static constexpr int IDS_OFF = Q_BYTES;
   static constexpr int IDS_BYTES = IDS_SLOTS * 64 * 4;
-  static constexpr int QID_SLOTS = 8;  // more than IDS_AHEAD: while priming, the ids cursor is that many tasks ahead
+  static constexpr int QID_SLOTS = 8;
   static constexpr int QID_OFF = IDS_OFF + IDS_BYTES;
   static constexpr int QID_BYTES = QID_SLOTS * 16 * 4;
-  static constexpr int MAXT = 48;                      // tasks per CTA per round
+  static constexpr int TASK_RING = 16;
   static constexpr int META_OFF = QID_OFF + QID_BYTES;  // 8 ints per task: q_off, q_len, kv_off, kv_len, kv head
-  static constexpr int META_BYTES = MAXT * 32;
+  static constexpr int META_BYTES = TASK_RING * 32;
   static constexpr int ML_OFF = META_OFF + META_BYTES;  // staged (max, sum) of the four warps
   static constexpr int ML_BYTES = 2 * 4 * 16 * 4;
-  static constexpr int PIPE_OFF = ML_OFF + ML_BYTES;
+  static constexpr int DENSE_OFF = ML_OFF + ML_BYTES;   // per ids-ring slot: first row of a consecutive tile, or -1
+  static constexpr int BAR_OFF = DENSE_OFF + IDS_SLOTS * 4;  // one mbarrier per K/V ring stage
+  static constexpr int PIPE_OFF = (BAR_OFF + 3 * 8 + 1023) / 1024 * 1024;  // swizzled tiles sit on 1024-byte boundaries
+  static constexpr int WAIT_LIMIT = 1 << 16;
   static constexpr int SMEM_BYTES = PIPE_OFF + M::PIPE_BYTES;
-  static constexpr int IDS_AHEAD = 5, KV_AHEAD = 2;
 };
 static_assert(StreamCfg<128>::SMEM_BYTES <= 115712, "two CTAs must fit in one SM's shared memory");
-static_assert(StreamCfg<128>::PIPE_OFF % 128 == 0, "ring must stay 128-byte aligned");
-
-struct StreamCursor {
-  int i, t, n;  // task (index inside the round), tile inside the task, tile number inside the round
-};
+static_assert(MmaCfg<128>::STAGES == 3, "one mbarrier per ring stage");
 
 // one 64-token tile for one warp (its 16 tokens); NQ = 8-row blocks of the task (1 or 2)
 template <typename T, int D, int NQ>
@@ -126,12 +139,30 @@ __device__ __forceinline__ void stream_tile(uint32_t k_sm, uint32_t v_sm, int to
   }
 }
 
+// Tasks are numbered first_task .. first_task + ntasks - 1 in the launch's (vnode, kv head) order; this CTA is
+// worker `worker` of `nworkers`.
 template <typename T, int D>
-__global__ void __launch_bounds__(128, 2) stage1_stream_kernel(Stage1Params p) {
+__device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem, const int first_task,
+                                              const int ntasks, const int worker, const int nworkers) {
   using C = MmaCfg<D>;
   using S = StreamCfg<D>;
-  extern __shared__ __align__(1024) uint8_t smem[];
+  const Stage1Params& p = tp.p;
   const uint32_t sm = smem_u32(smem);
+  const uint32_t bars = sm + S::BAR_OFF;
+  int* dense_box = reinterpret_cast<int*>(smem + S::DENSE_OFF);
+  if ((sm & 1023u) != 0u) {  // the swizzled tile layout needs a 1024-byte aligned window
+    if (threadIdx.x == 0) flag_error(FT_DEV_WAIT_TIMEOUT);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    for (int b = 0; b < C::STAGES; ++b) mbar_init(bars + 8 * b, 128);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    if (tp.has_tma) {
+      asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tp.k_map)) : "memory");
+      asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tp.v_map)) : "memory");
+    }
+  }
+  __syncthreads();
   const uint32_t ids_sm = sm + S::IDS_OFF, qid_sm = sm + S::QID_OFF, meta_sm = sm + S::META_OFF, pipe_sm = sm + S::PIPE_OFF;
   const int* ids_ptr = reinterpret_cast<const int*>(smem + S::IDS_OFF);
   const int* qid_ptr = reinterpret_cast<const int*>(smem + S::QID_OFF);
@@ -143,75 +174,62 @@ __global__ void __launch_bounds__(128, 2) stage1_stream_kernel(Stage1Params p) {
   const int g8 = lane >> 2, t4 = lane & 3;
   const int ld_c = tid % C::CPR, ld_r = tid / C::CPR;
   const int G = p.group, H = p.num_kv_heads;
-  const int ntasks = p.node_count * H;
-  const int my_total = (int)blockIdx.x < ntasks ? (ntasks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
   const float scale2 = p.sm_scale * 1.4426950408889634f;
   const uint32_t row_lim = (uint32_t)(p.kv_rows < 0x7fffffffLL ? p.kv_rows : 0x7fffffffLL);
   const int tok0 = warp * 16;
 
-  for (int round0 = 0; round0 < my_total; round0 += S::MAXT) {
-    const int nround = min(S::MAXT, my_total - round0);
-    // ---- metadata of this round's tasks -> shared memory
-    if (tid < nround) {
-      const int b = blockIdx.x + (round0 + tid) * gridDim.x;
-      const int vn = p.node_offset + b / H;
-      cp_async4(meta_sm + tid * 32 + 0, p.q_offs + vn);
-      cp_async4(meta_sm + tid * 32 + 4, p.q_lens + vn);
-      cp_async4(meta_sm + tid * 32 + 8, p.kv_offs + vn);
-      cp_async4(meta_sm + tid * 32 + 12, p.kv_lens + vn);
-      meta_ptr[tid * 8 + 4] = b - (b / H) * H;
+  // readable row ids of a task (a table that ends early is a plan error: flagged, the tokens become padding)
+  auto id_limit = [&](int kv_off, int kv_len) {
+    const int64_t readable = p.kv_entries_len - (int64_t)kv_off;
+    return kv_off < 0 ? 0 : (int)(readable < (int64_t)kv_len ? (readable < 0 ? 0 : readable) : kv_len);
+  };
+  // row ids of tile `t` of the task in metadata slot `m` -> ids ring slot `rs`; at t == 0 also the request ids
+  auto issue_ids = [&](int m, int t, int rs, int qs) {
+    const int q_off = meta_ptr[m * 8 + 0], q_len = meta_ptr[m * 8 + 1];
+    const int kv_off = meta_ptr[m * 8 + 2], kv_len = max(meta_ptr[m * 8 + 3], 0);
+    const int lim = id_limit(kv_off, kv_len);
+    if (tid < C::TILE) {
+      const int pos = t * C::TILE + tid;
+      if (pos < lim) cp_async4(ids_sm + (rs * C::TILE + tid) * 4, p.kv_entries + kv_off + pos);
+      if (tid == 0 && t == 0 && lim < kv_len) flag_error(FT_DEV_BAD_KV_INDEX);
+    } else if (t == 0 && tid - C::TILE < min(q_len, 16)) {  // request ids of the task's (at most 16) slots
+      const int64_t part = (int64_t)q_off + (tid - C::TILE);
+      if (part >= 0 && part < p.num_partial_rows)
+        cp_async4(qid_sm + (qs * 16 + (tid - C::TILE)) * 4, p.q_entries + part);
+      else
+        flag_error(FT_DEV_BAD_ROW_INDEX);
     }
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-
-    auto tiles_of = [&](int i) {
-      const int kv_len = max(meta_ptr[i * 8 + 3], 0);
-      return max(1, (kv_len + C::TILE - 1) / C::TILE);  // an empty chunk still gets one (fully masked) tile
-    };
-    auto advance = [&](StreamCursor& c) {
-      if (c.t + 1 >= tiles_of(c.i)) {
-        ++c.i;
-        c.t = 0;
+  };
+  // K/V rows of the tile -> ring stage `st`; at t == 0 also the task's query rows -> Q buffer `qbuf`
+  auto issue_kv = [&](int m, int t, int rs, int qs, int st, int qbuf) {
+    const int q_off = meta_ptr[m * 8 + 0], q_len = meta_ptr[m * 8 + 1];
+    const int kv_off = meta_ptr[m * 8 + 2], kv_len = max(meta_ptr[m * 8 + 3], 0);
+    const int kvh = meta_ptr[m * 8 + 4];
+    const int lim = id_limit(kv_off, kv_len);
+    const uint32_t k_sm = pipe_sm + st * 2 * C::STAGE_BYTES, v_sm = k_sm + C::STAGE_BYTES;
+    const uint32_t full = bars + 8 * st;
+    const int first_row = dense_box[rs];
+    if (first_row >= 0) {  // 64 consecutive rows: the copy engine writes the tile, no load instructions
+      if (tid == 0) {
+        proxy_fence();  // the stage was last touched with ordinary loads and stores
+        mbar_arrive_expect_tx(full, 2 * C::STAGE_BYTES);
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) {
+          tma_load_3d(k_sm + h * C::BLOCK_BYTES, &tp.k_map, 64 * h, kvh, first_row, full);
+          tma_load_3d(v_sm + h * C::BLOCK_BYTES, &tp.v_map, 64 * h, kvh, first_row, full);
+        }
       } else {
-        ++c.t;
+        mbar_arrive(full);
       }
-      ++c.n;
-    };
-    // readable row ids of a task (a table that ends early is a plan error: flagged, the tokens become padding)
-    auto id_limit = [&](int kv_off, int kv_len) {
-      const int64_t readable = p.kv_entries_len - (int64_t)kv_off;
-      return kv_off < 0 ? 0 : (int)(readable < (int64_t)kv_len ? (readable < 0 ? 0 : readable) : kv_len);
-    };
-    auto issue_ids = [&](const StreamCursor& c) {
-      const int q_off = meta_ptr[c.i * 8 + 0], q_len = meta_ptr[c.i * 8 + 1];
-      const int kv_off = meta_ptr[c.i * 8 + 2], kv_len = max(meta_ptr[c.i * 8 + 3], 0);
-      const int lim = id_limit(kv_off, kv_len);
-      if (tid < C::TILE) {
-        const int pos = c.t * C::TILE + tid;
-        if (pos < lim) cp_async4(ids_sm + ((c.n % S::IDS_SLOTS) * C::TILE + tid) * 4, p.kv_entries + kv_off + pos);
-        if (tid == 0 && c.t == 0 && lim < kv_len) flag_error(FT_DEV_BAD_KV_INDEX);
-      } else if (c.t == 0 && tid - C::TILE < min(q_len, 16)) {  // request ids of the task's (at most 16) slots
-        const int64_t part = (int64_t)q_off + (tid - C::TILE);
-        if (part >= 0 && part < p.num_partial_rows)
-          cp_async4(qid_sm + ((c.i % S::QID_SLOTS) * 16 + (tid - C::TILE)) * 4, p.q_entries + part);
-        else
-          flag_error(FT_DEV_BAD_ROW_INDEX);
-      }
-    };
-    auto issue_kv = [&](const StreamCursor& c) {
-      const int q_off = meta_ptr[c.i * 8 + 0], q_len = meta_ptr[c.i * 8 + 1];
-      const int kv_off = meta_ptr[c.i * 8 + 2], kv_len = max(meta_ptr[c.i * 8 + 3], 0);
-      const int kvh = meta_ptr[c.i * 8 + 4];
-      const int lim = id_limit(kv_off, kv_len);
+    } else {
       const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)kvh * p.k_s1 + ld_c * 8;
       const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)kvh * p.v_s1 + ld_c * 8;
-      const uint32_t k_sm = pipe_sm + (c.n % C::STAGES) * 2 * C::STAGE_BYTES, v_sm = k_sm + C::STAGE_BYTES;
-      const int* ring = ids_ptr + (c.n % S::IDS_SLOTS) * C::TILE + ld_r;
-      const int pos0 = c.t * C::TILE + ld_r;
+      const int* ring = ids_ptr + rs * C::TILE + ld_r;
+      const int pos0 = t * C::TILE + ld_r;
       uint32_t row[C::PASSES];
 #pragma unroll
-      for (int ps = 0; ps < C::PASSES; ++ps) row[ps] = pos0 + ps * C::TPP < lim ? (uint32_t)ring[ps * C::TPP] : 0xffffffffu;
+      for (int ps = 0; ps < C::PASSES; ++ps)
+        row[ps] = pos0 + ps * C::TPP < lim ? (uint32_t)ring[ps * C::TPP] : 0xffffffffu;
       bool bad = false;
 #pragma unroll
       for (int ps = 0; ps < C::PASSES; ++ps) {
@@ -223,81 +241,139 @@ __global__ void __launch_bounds__(128, 2) stage1_stream_kernel(Stage1Params p) {
         cp_async16(v_sm + C::swz(r, ld_c), vbase + off * p.v_s0, ok);
       }
       if (bad) flag_error(FT_DEV_BAD_KV_INDEX);
-      if (c.t == 0) {  // the task's query rows -> Q buffer i % 3
-        const int rows = min(q_len * G, 16);
-        if (tid == 0 && q_len * G > 16) flag_error(FT_DEV_BAD_ROW_INDEX);  // not a few-row task: rows beyond 16 are dropped
-        const uint32_t q_sm = sm + (c.i % S::QBUFS) * 16 * C::ROWB;
-        constexpr int QPASSES = (16 + C::TPP - 1) / C::TPP;
+      mbar_arrive_on_cp_async(full);  // one arrival per thread once its copies have landed
+    }
+    if (t == 0) {
+      const int rows = min(q_len * G, 16);
+      if (tid == 0 && q_len * G > 16) flag_error(FT_DEV_BAD_ROW_INDEX);  // not a few-row task: rows beyond 16 are dropped
+      const uint32_t q_sm = sm + qbuf * 16 * C::ROWB;
+      constexpr int QPASSES = (16 + C::TPP - 1) / C::TPP;
 #pragma unroll
-        for (int ps = 0; ps < QPASSES; ++ps) {
-          const int r = ps * C::TPP + ld_r;
-          if (r < 16) {
-            int64_t src = -1;
-            if (r < rows) {
-              const int slot = r / G, gg = r - slot * G;
-              const int req = qid_ptr[(c.i % S::QID_SLOTS) * 16 + slot];
-              const int64_t part = (int64_t)q_off + slot;
-              if (part >= 0 && part < p.num_partial_rows) {
-                if (req >= 0 && req < p.batch)
-                  src = (int64_t)req * p.q_s0 + (int64_t)(kvh * G + gg) * p.q_s1 + ld_c * 8;
-                else
-                  flag_error(FT_DEV_BAD_Q_INDEX);
-              }
+      for (int ps = 0; ps < QPASSES; ++ps) {
+        const int r = ps * C::TPP + ld_r;
+        if (r < 16) {
+          int64_t src = -1;
+          if (r < rows) {
+            const int slot = r / G, gg = r - slot * G;
+            const int req = qid_ptr[qs * 16 + slot];
+            const int64_t part = (int64_t)q_off + slot;
+            if (part >= 0 && part < p.num_partial_rows) {
+              if (req >= 0 && req < p.batch)
+                src = (int64_t)req * p.q_s0 + (int64_t)(kvh * G + gg) * p.q_s1 + ld_c * 8;
+              else
+                flag_error(FT_DEV_BAD_Q_INDEX);
             }
-            cp_async16(q_sm + C::swz(r, ld_c), reinterpret_cast<const T*>(p.q) + (src >= 0 ? src : 0), src >= 0);
           }
+          cp_async16(q_sm + C::swzq(r, ld_c), reinterpret_cast<const T*>(p.q) + (src >= 0 ? src : 0), src >= 0);
         }
       }
-    };
+    }
+  };
 
-    StreamCursor ic{0, 0, 0}, kc{0, 0, 0}, cc{0, 0, 0};
-    for (int k = 0; k < S::IDS_AHEAD; ++k)
-      if (ic.i < nround) {
-        issue_ids(ic);
-        advance(ic);
-      }
-    cp_async_commit();
-    cp_async_wait<0>();
+  // ---- pipeline state, identical in every thread
+  int next_task = worker;  // next task of this worker's list whose metadata copy is still to issue
+  int meta_issued = 0, meta_1 = 0, meta_2 = 0;             // tasks whose metadata copy was issued by now / 1 / 2 iterations ago
+  int tasks_done = 0;
+  uint32_t stage_phase = 0;  // bit b: phase of ring stage b's mbarrier that its next consumer waits for
+  int front_task = -1, front_tile = 0, front_ntiles = 0;
+  int dt0 = -1, dt1 = -1, dt2 = -1, dt3 = -1, dt4 = -1, dt5 = -1;  // task (sequence number) of the slot that entered k iterations ago
+  int dl0 = 0, dl1 = 0, dl2 = 0, dl3 = 0, dl4 = 0, dl5 = 0;        // its tile
+
+  float o_acc[D / 16][2][4];
+  float m_run[2][2], l_run[2][2];
+  uint32_t qb[2][D / 16][2];
+  int c_rows = 0, c_qoff = 0, c_kvlen = 0, c_kvh = 0, c_tiles = 1;
+
+#ifdef FT_TIMELINE
+  unsigned long long tl_first = 0;
+  int tl_bubbles = 0, tl_claims = 0;  // (claims: unused)
+#endif
+  cp_async_commit();
+  for (unsigned int it = 8;; ++it) {
+    cp_async_wait<1>();
     __syncthreads();
-    for (int k = 0; k < S::KV_AHEAD; ++k) {
-      if (kc.i < nround) {
-        issue_kv(kc);
-        advance(kc);
+
+    // ---- metadata of up to two more tasks -> task ring
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (next_task < ntasks && meta_issued - tasks_done < S::TASK_RING) {
+        const int b = first_task + next_task;
+        const int vn = p.node_offset + b / H;
+        const int m = meta_issued % S::TASK_RING;
+        const int j = tid - 32 * u;
+        if (j >= 0 && j < 4) {
+          const int32_t* tab = j == 0 ? p.q_offs : j == 1 ? p.q_lens : j == 2 ? p.kv_offs : p.kv_lens;
+          cp_async4(meta_sm + m * 32 + j * 4, tab + vn);
+        } else if (j == 4) {
+          meta_ptr[m * 8 + 4] = b - (b / H) * H;
+        }
+        next_task += nworkers;
+        ++meta_issued;
       }
-      cp_async_commit();
     }
 
-    float o_acc[D / 16][2][4];
-    float m_run[2][2], l_run[2][2];
-    uint32_t qb[2][D / 16][2];
-    int c_rows = 0, c_qoff = 0, c_kvlen = 0, c_kvh = 0, c_tiles = 1;
+    // ---- the slot entering the pipeline: next tile of the front task, else the next task whose metadata has landed
+    dt5 = dt4, dt4 = dt3, dt3 = dt2, dt2 = dt1, dt1 = dt0;
+    dl5 = dl4, dl4 = dl3, dl3 = dl2, dl2 = dl1, dl1 = dl0;
+    if (front_tile + 1 < front_ntiles) {
+      ++front_tile;
+      dt0 = front_task;
+      dl0 = front_tile;
+    } else if (front_task + 1 < meta_2) {
+      ++front_task;
+      front_tile = 0;
+      const int kv_len = max(meta_ptr[(front_task % S::TASK_RING) * 8 + 3], 0);
+      front_ntiles = max(1, (kv_len + C::TILE - 1) / C::TILE);  // an empty chunk still gets one (fully masked) tile
+      dt0 = front_task;
+      dl0 = 0;
+    } else {
+      dt0 = -1;
+    }
 
-    while (cc.i < nround) {
-      cp_async_wait<S::KV_AHEAD - 1>();  // tile cc.n has landed (this thread's copies)
-      __syncthreads();                   // ... everyone's; and the stage of tile cc.n - 1 is free
-      if (kc.i < nround) {
-        issue_kv(kc);
-        advance(kc);
+    if (dt0 >= 0) issue_ids(dt0 % S::TASK_RING, dl0, it % S::IDS_SLOTS, dt0 % S::QID_SLOTS);
+    if (dt2 >= 0 && warp == 0) {  // the slot's row ids have landed: is it a full tile of consecutive rows?
+      const int m = dt2 % S::TASK_RING, rs = (it - 2) % S::IDS_SLOTS;
+      const int lim = id_limit(meta_ptr[m * 8 + 2], max(meta_ptr[m * 8 + 3], 0));
+      int first_row = -1;
+      if (tp.has_tma && (dl2 + 1) * C::TILE <= lim) {
+        const int* ids = ids_ptr + rs * C::TILE;
+        const int r0 = ids[0];
+        const bool mine = ids[lane] == r0 + lane && ids[lane + 32] == r0 + lane + 32;
+        if (__all_sync(0xffffffffu, mine) && r0 >= 0 && (uint32_t)(r0 + C::TILE) <= row_lim) first_row = r0;
       }
-      if (ic.i < nround) {
-        issue_ids(ic);
-        advance(ic);
-      }
-      cp_async_commit();
+      if (lane == 0) dense_box[rs] = first_row;
+    }
+    if (dt3 >= 0)
+      issue_kv(dt3 % S::TASK_RING, dl3, (it - 3) % S::IDS_SLOTS, dt3 % S::QID_SLOTS, (it - 3) % C::STAGES, dt3 % S::QBUFS);
+    cp_async_commit();
 
-      if (cc.t == 0) {  // a new task: its Q rows arrived together with this tile
-        c_qoff = meta_ptr[cc.i * 8 + 0];
-        c_rows = min(meta_ptr[cc.i * 8 + 1] * G, 16);
-        c_kvlen = max(meta_ptr[cc.i * 8 + 3], 0);
-        c_kvh = meta_ptr[cc.i * 8 + 4];
+    // ---- consume
+#ifdef FT_TIMELINE
+    if (dt5 < 0) ++tl_bubbles;
+    if (dt5 >= 0 && tl_first == 0) tl_first = timeline_now();
+#endif
+    if (dt5 >= 0) {
+      const int m = dt5 % S::TASK_RING;
+      const int stage = (it - 5) % C::STAGES;
+      const uint32_t parity = (stage_phase >> stage) & 1u;  // bubbles skip stages, so the phase is tracked per stage
+      stage_phase ^= 1u << stage;
+      if (!mbar_wait(bars + 8 * stage, parity, S::WAIT_LIMIT)) {
+        flag_error(FT_DEV_WAIT_TIMEOUT);  // every thread of the CTA sees the same barrier: all leave together
+        break;
+      }
+      if (dl5 == 0) {  // a new task: its Q rows arrived together with this tile
+        c_qoff = meta_ptr[m * 8 + 0];
+        c_rows = min(meta_ptr[m * 8 + 1] * G, 16);
+        c_kvlen = max(meta_ptr[m * 8 + 3], 0);
+        c_kvh = meta_ptr[m * 8 + 4];
         c_tiles = max(1, (c_kvlen + C::TILE - 1) / C::TILE);
-        const uint32_t q_sm = sm + (cc.i % S::QBUFS) * 16 * C::ROWB;
+        const uint32_t q_sm = sm + (dt5 % S::QBUFS) * 16 * C::ROWB;
 #pragma unroll
         for (int nq = 0; nq < 2; ++nq) {
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
-            qb[nq][kk][0] = lds32(q_sm + C::swz(nq * 8 + g8, 2 * kk) + 4 * t4);
-            qb[nq][kk][1] = lds32(q_sm + C::swz(nq * 8 + g8, 2 * kk + 1) + 4 * t4);
+            qb[nq][kk][0] = lds32(q_sm + C::swzq(nq * 8 + g8, 2 * kk) + 4 * t4);
+            qb[nq][kk][1] = lds32(q_sm + C::swzq(nq * 8 + g8, 2 * kk + 1) + 4 * t4);
           }
           m_run[nq][0] = m_run[nq][1] = -INFINITY;
           l_run[nq][0] = l_run[nq][1] = 0.f;
@@ -305,16 +381,16 @@ __global__ void __launch_bounds__(128, 2) stage1_stream_kernel(Stage1Params p) {
           for (int mb = 0; mb < D / 16; ++mb) o_acc[mb][nq][0] = o_acc[mb][nq][1] = o_acc[mb][nq][2] = o_acc[mb][nq][3] = 0.f;
         }
       }
-      const uint32_t k_sm = pipe_sm + (cc.n % C::STAGES) * 2 * C::STAGE_BYTES, v_sm = k_sm + C::STAGE_BYTES;
+      const uint32_t k_sm = pipe_sm + stage * 2 * C::STAGE_BYTES, v_sm = k_sm + C::STAGE_BYTES;
       if (c_rows <= 8)
-        stream_tile<T, D, 1>(k_sm, v_sm, tok0, cc.t * C::TILE, c_kvlen, scale2, qb, o_acc, m_run, l_run, lane);
+        stream_tile<T, D, 1>(k_sm, v_sm, tok0, dl5 * C::TILE, c_kvlen, scale2, qb, o_acc, m_run, l_run, lane);
       else
-        stream_tile<T, D, 2>(k_sm, v_sm, tok0, cc.t * C::TILE, c_kvlen, scale2, qb, o_acc, m_run, l_run, lane);
+        stream_tile<T, D, 2>(k_sm, v_sm, tok0, dl5 * C::TILE, c_kvlen, scale2, qb, o_acc, m_run, l_run, lane);
 
-      if (cc.t == c_tiles - 1) {
+      if (dl5 == c_tiles - 1) {
         // ---- end of the task: merge the four warps through the stage just consumed, write the partial rows
         __syncthreads();  // every warp is done reading this stage
-        float* epi_o = reinterpret_cast<float*>(smem + S::PIPE_OFF + (cc.n % C::STAGES) * 2 * C::STAGE_BYTES);
+        float* epi_o = reinterpret_cast<float*>(smem + S::PIPE_OFF + stage * 2 * C::STAGE_BYTES);
         const int nq_used = c_rows <= 8 ? 1 : 2;
 #pragma unroll
         for (int nq = 0; nq < 2; ++nq) {
@@ -383,13 +459,34 @@ __global__ void __launch_bounds__(128, 2) stage1_stream_kernel(Stage1Params p) {
             }
           }
         }
-        // the stage is refilled only after the barrier at the top of the next iteration
+        ++tasks_done;
+        // the stage is refilled only after the barrier at the top of a later iteration
       }
-      advance(cc);
     }
-    cp_async_wait<0>();
-    __syncthreads();  // the rings and the metadata table are rewritten by the next round
+    meta_2 = meta_1;
+    meta_1 = meta_issued;
+
+    // ---- leave when the list is exhausted and every slot in flight has been consumed
+    if (next_task >= ntasks && tasks_done == meta_issued) break;
   }
+#ifdef FT_TIMELINE
+  if (tid == 0 && blockIdx.x < FT_TIMELINE_CTAS) {
+    g_timeline[16 * blockIdx.x + 4] = tl_first;
+    g_timeline[16 * blockIdx.x + 5] = tl_bubbles;
+    g_timeline[16 * blockIdx.x + 6] = tl_claims;
+    g_timeline[16 * blockIdx.x + 7] = tasks_done;
+    g_timeline[16 * blockIdx.x + 8] = timeline_now();
+  }
+#endif
+  cp_async_wait<0>();
+  __syncthreads();
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(128, 2) stage1_stream_kernel(const __grid_constant__ TcParams tp) {
+  allow_dependent_launch();
+  extern __shared__ __align__(1024) uint8_t smem[];
+  stream_worker<T, D>(tp, smem, 0, tp.p.node_count * tp.p.num_kv_heads, (int)blockIdx.x, (int)gridDim.x);
 }
 
 }  // namespace ft

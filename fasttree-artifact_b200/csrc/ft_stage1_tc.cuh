@@ -30,8 +30,9 @@
 //              ahead of V loads; row ids reach a small shared ring with
 //              cp.async two tiles ahead.
 //   warps 6-7  Q gather (by request id), concurrent with the first K/V loads:
-//              one TMA box per request (its G adjacent heads) when G is a power
-//              of two, 16-byte cp.async copies otherwise.
+//              when G is a power of two, two TMA boxes for the whole tile if the
+//              request ids are consecutive, else one box per request (its G
+//              adjacent heads); 16-byte cp.async copies otherwise.
 // The two warpgroups trade registers at start-up (setmaxnreg): the kernel
 // launches at 128 registers per thread, so that a CTA takes exactly two
 // equal-sized warps per scheduler partition and two CTAs always fit on an SM
@@ -51,13 +52,13 @@
 // output, lse = log(sum) + max.
 #pragma once
 
-#include <cuda.h>
-
 #include <type_traits>
 
+#include "ft_async.cuh"
 #include "ft_common.cuh"
 #include "ft_stage1_mma.cuh"
 #include "ft_stage1_narrow.cuh"
+#include "ft_stage1_stream.cuh"
 
 namespace ft {
 
@@ -85,6 +86,7 @@ struct TcCfg {
                        PV_DONE = 13, Q_FULL = 14;
   static constexpr int OUT_STRIDE = 528;              // bytes between staged output rows (512 + 16: conflict-free 16-byte stores)
   static constexpr int REGS_SOFTMAX = 184, REGS_OTHER = 72;
+  static constexpr int REGS_WORKER = 232;             // few-row workers of the fused kernel: four warps, the other four leave
 };
 static_assert(TcCfg::SMEM_BYTES <= 115712, "two CTAs must fit in one SM's shared memory");
 static_assert(128 * TcCfg::OUT_STRIDE <= TcCfg::P_OFF, "the staged output rows reuse the Q, K and V buffers");
@@ -94,17 +96,6 @@ template <int N>
 __device__ __forceinline__ void reg_grow() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(N)); }
 template <int N>
 __device__ __forceinline__ void reg_shrink() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(N)); }
-
-// Kernel parameters of the tcgen05 path: the common ones plus the TMA descriptors of the K and V buffers
-// ([rows, kv heads, head_dim], box 64 x 1 x 64 elements, 128-byte swizzle).  has_tma == 0: gather only.
-struct alignas(64) TcParams {
-  CUtensorMap k_map;
-  CUtensorMap v_map;
-  CUtensorMap q_map;  // [batch, heads, head_dim], box 64 x q_box_rows x 1
-  Stage1Params p;
-  int has_tma;
-  int q_box_rows;     // 0: gather Q with cp.async (group size not a power of two <= 128, or no descriptor)
-};
 
 // canonical K-major / MN-major 128B-swizzled position of 16-byte chunk `c16` (0..15 over 256 B)
 // of row `r` in an operand whose 64-element blocks are `block_bytes` apart
@@ -138,29 +129,6 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-// the barrier gets one arrival when all earlier cp.async copies of this thread have landed
-__device__ __forceinline__ void mbar_arrive_on_cp_async(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::
-          "r"(dst),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
-      : "memory");
-}
-
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t* r = reinterpret_cast<uint32_t*>(v);
   asm volatile(
@@ -236,8 +204,10 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
   if (tid == 32 && tp.has_tma) {  // the first TMA copy would otherwise pay for fetching its descriptor
     asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tp.k_map)) : "memory");
     asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tp.v_map)) : "memory");
-    if (tp.q_box_rows > 0)
+    if (tp.q_box_rows > 0) {
+      asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tp.q_map_tile)) : "memory");
       asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tp.q_map)) : "memory");
+    }
   }
   if (tid == 0) {
     for (int b = 0; b < 2; ++b) {
@@ -453,7 +423,24 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
         cp_async_wait<0>();
         asm volatile("bar.sync 1, 64;\n" ::: "memory");
         const int* req_of = reinterpret_cast<const int*>(smem + C::P_OFF);
+        // Requests with consecutive ids (the usual case: the leaves under a node are numbered in tree order) make
+        // the whole Q tile one strided block of the Q tensor: two boxes of [128 / G requests][G heads][64].
+        bool in_order = false;
         if (tp.q_box_rows > 0) {
+          const int req0 = req_of[0];
+          bool mine = true;
+          for (int i = lane; i < nslots; i += 32) mine &= req_of[i] == req0 + i;
+          in_order = __all_sync(0xffffffffu, mine) && req0 >= 0 && (int64_t)req0 + nslots <= p.batch;
+        }
+        if (in_order) {
+          if (qt == 0) {
+            mbar_arrive_expect_tx(bar(C::Q_FULL), 32768);  // full boxes: rows past the task's requests are dead rows
+            tma_load_3d(q_sm, &tp.q_map_tile, 0, kvh * G, req_of[0], bar(C::Q_FULL));
+            tma_load_3d(q_sm + 16384, &tp.q_map_tile, 64, kvh * G, req_of[0], bar(C::Q_FULL));
+          } else {
+            mbar_arrive(bar(C::Q_FULL));
+          }
+        } else if (tp.q_box_rows > 0) {
           // The G rows of a request are adjacent heads of one Q row: one box of up to 8 rows x 64 elements per
           // half.  G divides 128 here, so passes start on a request and a box never straddles an 8-row group.
           const int br = tp.q_box_rows;
@@ -648,6 +635,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
 
 template <typename T>
 __global__ void __launch_bounds__(TcCfg::THREADS, 2) stage1_tc_kernel(const __grid_constant__ TcParams tp) {
+  allow_dependent_launch();
   extern __shared__ __align__(1024) uint8_t smem[];
   int vn, kvh;
   task_of_block(tp.p, blockIdx.x, vn, kvh);
@@ -656,28 +644,44 @@ __global__ void __launch_bounds__(TcCfg::THREADS, 2) stage1_tc_kernel(const __gr
   FT_TL_END(1);
 }
 
-// Both task families in one grid (head_dim 128): the first `p.node_split` vnodes of the launch are
-// many-row tasks for the tcgen05 body, the rest few-row tasks for the swapped-operand body.  The
-// tensor-bound and the memory-bound CTAs then share the SMs instead of running back to back.
+// Both task families in one grid (head_dim 128): the tensor-bound many-row CTAs (tcgen05 body, one task each)
+// and the memory-bound few-row CTAs (swapped-operand body) share the SMs instead of running back to back.
+// Block order, which is the order the hardware starts them in:
+//   [0, lead)                 many-row tasks 0 .. lead-1
+//   [lead, lead + few_ctas)   few-row CTAs: persistent workers that split the few-row tasks between them
+//                             (p.workers > 0), or one CTA per few-row task (p.workers == 0)
+//   the rest                  the remaining many-row tasks
+// `lead` leaves room for the few-row CTAs to start at once beside the first many-row CTAs.
 template <typename T>
 __global__ void __launch_bounds__(TcCfg::THREADS, 2) stage1_fused_kernel(const __grid_constant__ TcParams tp) {
+  allow_dependent_launch();
   extern __shared__ __align__(1024) uint8_t smem[];
-  int vn, kvh;
-  task_of_block(tp.p, blockIdx.x, vn, kvh);  // blocks [0, node_split * heads) are the many-row tasks: they start first
+  const Stage1Params& p = tp.p;
+  const int H = p.num_kv_heads;
+  const int wide_tasks = p.node_split * H, few_tasks = (p.node_count - p.node_split) * H;
+  const int few_ctas = p.workers > 0 ? p.workers : few_tasks;
+  const int b = (int)blockIdx.x;
   FT_TL_BEGIN();
-  if (vn - tp.p.node_offset < tp.p.node_split) {
-    tc_body<T>(tp, smem, vn, kvh);
+  if (b < p.lead_wide || b >= p.lead_wide + few_ctas) {
+    const int task = b < p.lead_wide ? b : b - few_ctas;
+    tc_body<T>(tp, smem, p.node_offset + task / H, task % H);
     FT_TL_END(1);
   } else {
     // This CTA will not allocate tensor memory.  Saying so at once matters: the SM admits no second CTA of a
     // kernel that uses tensor memory while a resident one still holds the right to allocate.
     if (threadIdx.x < 32) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-    if (threadIdx.x >= 128) {  // the few-row body is written for four warps: the others hand over their registers
+    if (threadIdx.x >= 128) {  // the few-row bodies are written for four warps: the others hand over their registers
       reg_shrink<24>();
       return;
     }
-    reg_grow<TcCfg::REGS_SOFTMAX>();
-    narrow_dispatch<T, 128>(tp.p, smem, vn, kvh);
+    reg_grow<TcCfg::REGS_WORKER>();
+    const int w = b - p.lead_wide;
+    if (p.workers > 0) {
+      stream_worker<T, 128>(tp, smem, wide_tasks, few_tasks, w, p.workers);
+    } else {
+      const int task = wide_tasks + w;
+      narrow_dispatch<T, 128>(p, smem, p.node_offset + task / H, task % H);
+    }
     FT_TL_END(2);
   }
 }

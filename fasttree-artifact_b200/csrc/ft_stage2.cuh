@@ -24,11 +24,13 @@ __global__ void __launch_bounds__(128) stage2_merge_kernel(Stage2Params p) {
   const int off = p.r2v_offs[req];
   const int n = p.r2v_lens[req];
   const int chunks = p.head_dim >> 2;
+  int first_rows = lane < n ? p.r2v_entries[off + lane] : -1;  // plan data: readable before stage 1 is done
+  wait_for_prior_grid();                                       // the partial buffers are complete from here on
 
   // pass 1: maximum LSE over the request's partial rows
   float mx = -INFINITY;
   for (int i = lane; i < n; i += 32) {
-    const int row = p.r2v_entries[off + i];
+    const int row = i < 32 ? first_rows : p.r2v_entries[off + i];
     if (row < 0 || row >= p.num_partial_rows) {
       flag_error(FT_DEV_BAD_ROW_INDEX);
       continue;
