@@ -345,15 +345,22 @@ int launch_fused(ft::TcParams p, int hkv, cudaStream_t st) {
   return FT_OK;
 }
 
-// path: AUTO (narrow <= 16 rows, tcgen05 above when head_dim is 128, else wide), MMA (narrow / wide),
-// MMA_WIDE (wide for everything), TCGEN05 (tcgen05 for everything)
+// path: AUTO (<= 16 rows: persistent workers or narrow; above: tcgen05 when head_dim is 128, else wide),
+// STREAM (like AUTO, always the persistent workers), MMA (narrow / wide), MMA_WIDE (wide for everything),
+// TCGEN05 (tcgen05 for everything)
 template <typename T, int D>
 int launch_tensor(const ft::Stage1Params& p, const ft_decode_args* a, int hkv, cudaStream_t st, int max_rows, int path) {
   if constexpr (D == 128) {
     if (path == FT_PATH_TCGEN05 || ((path == FT_PATH_AUTO || path == FT_PATH_STREAM) && max_rows > 16))
       return launch_tc<T>(tc_params(p, a), hkv, st);
   }
-  if (path == FT_PATH_STREAM && max_rows <= 16) return launch_stream<T, D>(tc_params(p, a), hkv, st);
+  if (max_rows <= 16) {
+    // few-row tasks only: persistent workers when there are several tasks per CTA slot, else one CTA per task
+    int dev = 0;
+    FT_CUDA_OK(cudaGetDevice(&dev));
+    const bool many = (int64_t)p.node_count * hkv >= 8LL * sm_count(dev);
+    if (path == FT_PATH_STREAM || (path == FT_PATH_AUTO && many)) return launch_stream<T, D>(tc_params(p, a), hkv, st);
+  }
   if (path != FT_PATH_MMA_WIDE && max_rows <= 16) return launch_narrow<T, D>(p, hkv, st);
   return launch_mma<T, D>(p, hkv, st);
 }
