@@ -47,6 +47,7 @@ DTYPES = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
 HEAD_DIM = 128
 L2_BYTES = 126 * 2 ** 20
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
 
 
 def build_tree(workload, seed):
@@ -79,6 +80,15 @@ def measured_peak():
             return float(json.load(fh)["hbm_gbs"]), "measured"
     except Exception:
         return FALLBACK_HBM_GBS, "fallback"
+
+
+def measured_tensor_peak():
+    """Dense bf16 TFLOP/s: the burst figure (the kernel is timed alone)."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            return float(json.load(fh)["bf16_tflops"]), "measured"
+    except Exception:
+        return FALLBACK_BF16_TFLOPS, "fallback"
 
 
 def recorded_traffic(workload, n_gpus):
@@ -440,6 +450,21 @@ def main():
                 "traffic": recorded_traffic(args.workload, world), "peak_source": f"of {peak_kind}",
                 "kernel": f"stage1_{s1_path}", "kernel_us": s1_ms * 1e3, "algorithmic_bytes": algo_bytes,
                 "timing": s1_timing}
+    # The same launch against the tensor roofline: 4*D flop per (query head, request, token on the request's path).
+    # Whichever fraction is larger names the bound (a deep shared prefix with many requests is tensor-bound).
+    depth = [0] * len(nodes)
+    for i, nd in enumerate(nodes):
+        depth[i] = nd.seqlen + (depth[nd.parent] if nd.parent >= 0 else 0)
+    path_tokens = sum(depth[i] for i, nd in enumerate(nodes) if nd.num_children == 0)
+    algo_flop = 4.0 * HEAD_DIM * hq_l * path_tokens
+    tpeak, tpeak_kind = measured_tensor_peak()
+    tflops = algo_flop / (s1_ms * 1e-3) / 1e12
+    if tflops / tpeak > roofline["frac"]:
+        roofline.update({"bound": "tensor", "achieved": tflops, "peak": tpeak, "unit": "TFLOP/s", "frac": tflops / tpeak,
+                         "peak_source": f"of {tpeak_kind}", "algorithmic_flop": algo_flop,
+                         "hbm_frac": achieved / peak})
+    else:
+        roofline["tensor_frac"] = tflops / tpeak
 
     # ---- end to end: query from pinned host memory in, output to pinned host memory out, every step
     e2e = None

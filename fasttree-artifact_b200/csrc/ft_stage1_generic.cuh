@@ -3,7 +3,8 @@
 // One CTA per (vnode, kv head), as in the reference launch grid
 // (kernel_bench/fasttree.py:448-451).  Each warp owns one packed query row
 // (request slot x group member) at a time, lanes span the head dimension, and
-// the KV chunk is walked four tokens per step with a warp-shuffle online
+// the KV chunk is walked sixteen tokens per step (their row ids, then their K
+// rows, are independent loads in flight together) with a warp-shuffle online
 // softmax.  It is the correctness path for fp32 inputs and unusual head sizes;
 // the 16-bit / head_dim 64,128 cases go to the tensor-core kernels.
 #pragma once
@@ -16,7 +17,7 @@ template <typename T>
 __global__ void __launch_bounds__(128) stage1_generic_kernel(Stage1Params p) {
   allow_dependent_launch();
   constexpr int MAXJ = 8;  // 8 x 32 lanes = head_dim up to 256
-  constexpr int TB = 4;    // tokens per step
+  constexpr int TB = 16;   // tokens per step
   const int vn = blockIdx.x + p.node_offset;
   const int kvh = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -50,7 +51,7 @@ __global__ void __launch_bounds__(128) stage1_generic_kernel(Stage1Params p) {
     }
     float m = -INFINITY, l = 0.f;
     for (int t0 = 0; t0 < kv_len; t0 += TB) {
-      int64_t rowid[TB];
+      int rowid[TB];
       float s[TB];
 #pragma unroll
       for (int u = 0; u < TB; ++u) {
@@ -63,10 +64,13 @@ __global__ void __launch_bounds__(128) stage1_generic_kernel(Stage1Params p) {
             idx = -1;
           }
         }
-        rowid[u] = idx;
+        rowid[u] = (int)idx;
+      }
+#pragma unroll
+      for (int u = 0; u < TB; ++u) {
         float part = 0.f;
-        if (idx >= 0) {
-          const T* __restrict__ kp = kbase + idx * p.k_s0;
+        if (rowid[u] >= 0) {
+          const T* __restrict__ kp = kbase + (int64_t)rowid[u] * p.k_s0;
 #pragma unroll
           for (int j = 0; j < MAXJ; ++j) {
             const int d = lane + 32 * j;
@@ -98,7 +102,7 @@ __global__ void __launch_bounds__(128) stage1_generic_kernel(Stage1Params p) {
         l += pr;
         // the reference casts the probabilities to V's type before P*V (fasttree.py:391)
         const float pv = to_float<T>(from_float<T>(pr));
-        const T* __restrict__ vp = vbase + rowid[u] * p.v_s0;
+        const T* __restrict__ vp = vbase + (int64_t)rowid[u] * p.v_s0;
 #pragma unroll
         for (int j = 0; j < MAXJ; ++j) {
           const int d = lane + 32 * j;

@@ -175,13 +175,20 @@ struct KvPipe {
       if (pos < id_lim) cp_async4(dst + t * 4, p.kv_entries + kv_off + pos);
     }
   }
-  // blocks 0 and 1, waited for; call once before the first tile
-  __device__ __forceinline__ void prime_indices() {
+  // blocks 0 and 1: issue early (their round trip then overlaps the caller's own dependent loads), wait before
+  // the first tile
+  __device__ __forceinline__ void issue_first_indices() {
     issue_idx_block(0);
     if (IDXB < kv_len) issue_idx_block(1);
     cp_async_commit();
+  }
+  __device__ __forceinline__ void wait_indices() {
     cp_async_wait<0>();
     __syncthreads();
+  }
+  __device__ __forceinline__ void prime_indices() {
+    issue_first_indices();
+    wait_indices();
   }
   // K/V rows of tile `tile` -> stage tile % STAGES (joins the open group)
   __device__ __forceinline__ void issue_tile(int tile) {

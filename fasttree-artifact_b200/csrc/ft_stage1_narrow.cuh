@@ -63,6 +63,7 @@ __device__ __forceinline__ void narrow_body(const Stage1Params& p, uint8_t* smem
   const int G = p.group;
   const int rows = q_len * G;
   if (rows <= 0) return;
+  if (tid == 0) FT_TL_MARK(0);
   const float scale2 = p.sm_scale * 1.4426950408889634f;
   const int ntiles = (kv_len + C::TILE - 1) / C::TILE;
   const int ld_c = tid % C::CPR, ld_r = tid / C::CPR;
@@ -71,7 +72,8 @@ __device__ __forceinline__ void narrow_body(const Stage1Params& p, uint8_t* smem
   KvPipe<T, D, N::IDXB> pipe(p, kvh, kv_off, kv_len, smem + N::Q_BYTES, idx_sm, pipe_sm);
 
   for (int row0 = 0; row0 < rows; row0 += N::ROWS) {
-    // ---- row ids first (independent loads), then the copies
+    pipe.issue_first_indices();  // the K/V row ids travel while the request ids below are fetched
+    // ---- request ids first (independent loads), then the copies
     constexpr int QPASSES = (N::ROWS + C::TPP - 1) / C::TPP;
     int64_t q_src[QPASSES];
 #pragma unroll
@@ -101,7 +103,9 @@ __device__ __forceinline__ void narrow_body(const Stage1Params& p, uint8_t* smem
         cp_async16(q_sm + C::swzq(r, ld_c), reinterpret_cast<const T*>(p.q) + (ok ? q_src[ps] : 0), ok);
       }
     }
-    pipe.prime_indices();  // also lands Q
+    cp_async_commit();
+    pipe.wait_indices();  // also lands Q
+    if (tid == 0) FT_TL_MARK(1);
     pipe.prologue();
 
     float o_acc[D / 16][NQ][4];
@@ -119,6 +123,7 @@ __device__ __forceinline__ void narrow_body(const Stage1Params& p, uint8_t* smem
 
     for (int j = 0; j < ntiles; ++j) {
       pipe.advance(j);
+      if (tid == 0 && j < 4) FT_TL_MARK(2 + j);
       if (j == 0) {
 #pragma unroll
         for (int nq = 0; nq < NQ; ++nq)
@@ -197,6 +202,7 @@ __device__ __forceinline__ void narrow_body(const Stage1Params& p, uint8_t* smem
       }
     }
     pipe.drain();  // ring idle: reuse it as the staging area
+    if (tid == 0) FT_TL_MARK(6);
 
     // ---- stage this warp's (max, sum, O^T) partial
 #pragma unroll
