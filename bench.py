@@ -8,7 +8,9 @@ A step is one tree-attention decode call (one layer) over a synthetic radix
 tree.  Default workload: N=[1,64] nodes per level, C=[4096,256] tokens per
 node, 32 query / 8 KV heads, head_dim 128, fp16 - 64 decode requests sharing a
 4096-token prefix.  Under torchrun the KV heads are sharded across ranks
-(tensor parallel) and the per-head outputs are all-gathered with NCCL.
+(tensor parallel); the output stays head-sharded on its rank, as it does in
+tensor-parallel serving where it feeds a row-parallel projection, so the step
+has no collective (``--gather-output`` adds an NCCL all-gather of the heads).
 
 Prints ONE JSON line on rank 0.  ``value`` is microseconds per step with
 everything resident in HBM; ``e2e`` is the same call fed from pinned host
@@ -245,6 +247,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every timed step from Python instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--gather-output", action="store_true",
+                    help="multi-GPU: all-gather the head-sharded outputs with NCCL inside every step")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -287,7 +291,8 @@ def main():
           for _ in range(copies)]
     q = (torch.randn(batch, hq_l, HEAD_DIM, generator=g, device=dev, dtype=torch.float32) * qs).to(dtype)
     o = torch.empty_like(q)
-    o_all = torch.empty(world, batch, hq_l, HEAD_DIM, device=dev, dtype=dtype) if world > 1 else None
+    gather = world > 1 and args.gather_output
+    o_all = torch.empty(world, batch, hq_l, HEAD_DIM, device=dev, dtype=dtype) if gather else None
 
     # ---- plan (host) with the LOCAL head counts
     params = fasttree.FastTreeParams()
@@ -321,7 +326,7 @@ def main():
             fasttree.fasttree_decode(q, ks[c], vs[c], o, *aux, tsq, tsk, scale)
         else:
             engine.decode(q, ks[c], vs[c], o, *aux, tsq, tsk, scale, path=args.path)
-        if world > 1:
+        if gather:
             dist.all_gather_into_tensor(o_all, o)
 
     def fence():
@@ -470,7 +475,7 @@ def main():
     e2e = None
     if not args.no_e2e:
         q_host = q.cpu().pin_memory()
-        o_src = o_all if world > 1 else o
+        o_src = o_all if gather else o
         o_host = torch.empty(o_src.shape, dtype=dtype).pin_memory()
         n_e2e = min(args.steps, 1000)
 
@@ -496,7 +501,7 @@ def main():
         e2e = {"value": t.item() / n_e2e * 1e3, "unit": "us/step",
                "h2d_bytes_per_step": q_host.numel() * esize, "d2h_bytes_per_step": o_host.numel() * esize,
                "steps": n_e2e, "wall_us_per_step": wall_ms / n_e2e * 1e3,
-               "call": "fasttree_decode(...) + NCCL all-gather" if world > 1 else "fasttree_decode(...)"}
+               "call": "fasttree_decode(...) + NCCL all-gather" if gather else "fasttree_decode(...)"}
     clocks = sampler.finish()
 
     cpu = None
@@ -516,7 +521,9 @@ def main():
                             f"one decode token per leaf",
                 "requests": batch, "tokens": tokens, "planner": args.planner, "stage1_path": s1_path,
                 "vnodes": n_vnodes, "partial_rows": n_rows, "plan_ms_host": plan_ms, "launch": launch_mode,
-                "parallelism": f"tp{world} (kv heads sharded, {hkv_l} per GPU)" if world > 1 else "single GPU",
+                "parallelism": (f"tp{world} (kv heads sharded, {hkv_l} per GPU; "
+                                + ("outputs all-gathered with NCCL" if gather else "outputs stay head-sharded, no collective")
+                                + ")") if world > 1 else "single GPU",
                 "l2": f"K/V rotated over {copies} copies = {copies * kv_bytes / 2 ** 20:.0f} MiB per GPU (> 126 MiB L2)",
             },
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,

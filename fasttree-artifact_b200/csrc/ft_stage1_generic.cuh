@@ -54,18 +54,20 @@ __global__ void __launch_bounds__(128) stage1_generic_kernel(Stage1Params p) {
       int rowid[TB];
       float s[TB];
 #pragma unroll
+      bool bad = false;  // flagged once after the loads: an atomic between them would serialise them
       for (int u = 0; u < TB; ++u) {
         const int64_t e = (int64_t)kv_off + t0 + u;
         int64_t idx = -1;
         if (t0 + u < kv_len) {
           if (e >= 0 && e < p.kv_entries_len) idx = p.kv_entries[e];
           if (idx < 0 || idx >= p.kv_rows) {
-            if (lane == 0) flag_error(FT_DEV_BAD_KV_INDEX);
+            bad = true;
             idx = -1;
           }
         }
         rowid[u] = (int)idx;
       }
+      if (bad && lane == 0) flag_error(FT_DEV_BAD_KV_INDEX);
 #pragma unroll
       for (int u = 0; u < TB; ++u) {
         float part = 0.f;
