@@ -3,7 +3,7 @@
 // One CTA per (vnode, kv head), as in the reference launch grid
 // (kernel_bench/fasttree.py:448-451).  Each warp owns one packed query row
 // (request slot x group member) at a time, lanes span the head dimension, and
-// the KV chunk is walked sixteen tokens per step (their row ids, then their K
+// the KV chunk is walked four tokens per step (their row ids, then their K
 // rows, are independent loads in flight together) with a warp-shuffle online
 // softmax.  It is the correctness path for fp32 inputs and unusual head sizes;
 // the 16-bit / head_dim 64,128 cases go to the tensor-core kernels.
@@ -17,7 +17,7 @@ template <typename T>
 __global__ void __launch_bounds__(128) stage1_generic_kernel(Stage1Params p) {
   allow_dependent_launch();
   constexpr int MAXJ = 8;  // 8 x 32 lanes = head_dim up to 256
-  constexpr int TB = 16;   // tokens per step
+  constexpr int TB = 4;    // tokens per step (more in flight per step measured slower: register pressure)
   const int vn = blockIdx.x + p.node_offset;
   const int kvh = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
