@@ -333,7 +333,11 @@ int launch_fused(ft::TcParams p, int hkv, cudaStream_t st) {
   const int64_t wide = (int64_t)p.p.node_split * hkv;
   const int64_t few = (int64_t)(p.p.node_count - p.p.node_split) * hkv;
   const int64_t slots = 2LL * sm_count(dev);
+#ifdef FT_FORCE_WORKERS  // developer builds: persistent workers in every free slot, whatever the task count
+  const int64_t workers = few < slots - wide ? few : (slots - wide > slots / 4 ? slots - wide : slots);
+#else
   const int64_t workers = few >= 4 * slots && wide <= slots ? slots : 0;
+#endif
   const int64_t few_ctas = workers > 0 ? workers : few;
   const int64_t lead = wide;
   if (wide + few_ctas > 0x7fffffffLL) return fail(FT_ERR_TOO_LARGE, "vnodes x kv heads exceeds the grid limit");

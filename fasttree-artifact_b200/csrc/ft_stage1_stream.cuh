@@ -20,20 +20,22 @@
 // Pipeline: every loop iteration is one slot.  A slot is a (task, tile) pair or
 // a bubble, decided when it enters; the stages sit at fixed distances,
 //   iteration s      row ids of the tile (and the task's request ids) -> rings
-//   iteration s + 2  are the 64 row ids consecutive?  (one warp; the answer is
+//   iteration s + 4  are the 64 row ids consecutive?  (one warp; the answer is
 //                    read by everyone one iteration later)
-//   iteration s + 3  K/V rows of the tile -> 3-stage ring: four tiled TMA copies
+//   iteration s + 5  K/V rows of the tile -> 3-stage ring: four tiled TMA copies
 //                    (128-byte swizzle, no multicast) for a consecutive tile,
 //                    16-byte cp.async copies row by row otherwise; the task's Q
 //                    rows with cp.async
-//   iteration s + 5  MMA + online softmax; at a task's last tile the epilogue,
+//   iteration s + 7  MMA + online softmax; at a task's last tile the epilogue,
 //                    staged through the ring stage just freed
-// Row ids, request ids, Q rows and task metadata travel in cp.async groups, one
-// per iteration with wait_group 1 at the top, so such a copy issued in iteration
-// i is complete in iteration i + 2 whatever its latency.  A K/V tile signals an
-// mbarrier of its ring stage (transaction bytes for TMA, one arrival per thread
-// for cp.async), which the consumer waits on - bounded.  Task metadata enters a
-// 16-entry ring at least two iterations before the task's first slot.  No stage
+// Row ids, request ids and task metadata travel in cp.async groups, one per
+// iteration with wait_group 3 at the top, so such a copy issued in iteration i
+// is complete in iteration i + 4 whatever its latency (small reads queue behind
+// the bulk traffic: with two iterations of slack they gated every iteration).
+// A K/V tile and the task's Q rows signal the mbarrier of the tile's ring stage
+// (transaction bytes for TMA, one arrival per thread when its cp.async copies
+// have landed), which the consumer waits on - bounded.  Task metadata enters a
+// 16-entry ring at least four iterations before the task's first slot.  No stage
 // waits on an earlier one: when an input is not there yet the slot is a bubble.
 #pragma once
 
@@ -212,14 +214,12 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
     if (first_row >= 0) {  // 64 consecutive rows: the copy engine writes the tile, no load instructions
       if (tid == 0) {
         proxy_fence();  // the stage was last touched with ordinary loads and stores
-        mbar_arrive_expect_tx(full, 2 * C::STAGE_BYTES);
+        mbar_expect_tx(full, 2 * C::STAGE_BYTES);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) {
           tma_load_3d(k_sm + h * C::BLOCK_BYTES, &tp.k_map, 64 * h, kvh, first_row, full);
           tma_load_3d(v_sm + h * C::BLOCK_BYTES, &tp.v_map, 64 * h, kvh, first_row, full);
         }
-      } else {
-        mbar_arrive(full);
       }
     } else {
       const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)kvh * p.k_s1 + ld_c * 8;
@@ -241,7 +241,6 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
         cp_async16(v_sm + C::swz(r, ld_c), vbase + off * p.v_s0, ok);
       }
       if (bad) flag_error(FT_DEV_BAD_KV_INDEX);
-      mbar_arrive_on_cp_async(full);  // one arrival per thread once its copies have landed
     }
     if (t == 0) {
       const int rows = min(q_len * G, 16);
@@ -268,16 +267,19 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
         }
       }
     }
+    // one arrival per thread once all its copies so far (gathered rows, Q rows) have landed; a TMA tile adds its
+    // transaction bytes on top
+    mbar_arrive_on_cp_async(full);
   };
 
   // ---- pipeline state, identical in every thread
   int next_task = worker;  // next task of this worker's list whose metadata copy is still to issue
-  int meta_issued = 0, meta_1 = 0, meta_2 = 0;             // tasks whose metadata copy was issued by now / 1 / 2 iterations ago
+  int meta_issued = 0, meta_1 = 0, meta_2 = 0, meta_3 = 0, meta_4 = 0;  // tasks whose metadata copy was issued by now / 1..4 iterations ago
   int tasks_done = 0;
   uint32_t stage_phase = 0;  // bit b: phase of ring stage b's mbarrier that its next consumer waits for
   int front_task = -1, front_tile = 0, front_ntiles = 0;
-  int dt0 = -1, dt1 = -1, dt2 = -1, dt3 = -1, dt4 = -1, dt5 = -1;  // task (sequence number) of the slot that entered k iterations ago
-  int dl0 = 0, dl1 = 0, dl2 = 0, dl3 = 0, dl4 = 0, dl5 = 0;        // its tile
+  int dt0 = -1, dt1 = -1, dt2 = -1, dt3 = -1, dt4 = -1, dt5 = -1, dt6 = -1, dt7 = -1;  // task (sequence number) of the slot that entered k iterations ago
+  int dl0 = 0, dl1 = 0, dl2 = 0, dl3 = 0, dl4 = 0, dl5 = 0, dl6 = 0, dl7 = 0;              // its tile
 
   float o_acc[D / 16][2][4];
   float m_run[2][2], l_run[2][2];
@@ -286,11 +288,11 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
 
 #ifdef FT_TIMELINE
   unsigned long long tl_first = 0;
-  int tl_bubbles = 0, tl_claims = 0;  // (claims: unused)
+  int tl_bubbles = 0;
 #endif
   cp_async_commit();
   for (unsigned int it = 8;; ++it) {
-    cp_async_wait<1>();
+    cp_async_wait<3>();
     __syncthreads();
 
     // ---- metadata of up to two more tasks -> task ring
@@ -313,13 +315,13 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
     }
 
     // ---- the slot entering the pipeline: next tile of the front task, else the next task whose metadata has landed
-    dt5 = dt4, dt4 = dt3, dt3 = dt2, dt2 = dt1, dt1 = dt0;
-    dl5 = dl4, dl4 = dl3, dl3 = dl2, dl2 = dl1, dl1 = dl0;
+    dt7 = dt6, dt6 = dt5, dt5 = dt4, dt4 = dt3, dt3 = dt2, dt2 = dt1, dt1 = dt0;
+    dl7 = dl6, dl6 = dl5, dl5 = dl4, dl4 = dl3, dl3 = dl2, dl2 = dl1, dl1 = dl0;
     if (front_tile + 1 < front_ntiles) {
       ++front_tile;
       dt0 = front_task;
       dl0 = front_tile;
-    } else if (front_task + 1 < meta_2) {
+    } else if (front_task + 1 < meta_4) {
       ++front_task;
       front_tile = 0;
       const int kv_len = max(meta_ptr[(front_task % S::TASK_RING) * 8 + 3], 0);
@@ -331,11 +333,11 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
     }
 
     if (dt0 >= 0) issue_ids(dt0 % S::TASK_RING, dl0, it % S::IDS_SLOTS, dt0 % S::QID_SLOTS);
-    if (dt2 >= 0 && warp == 0) {  // the slot's row ids have landed: is it a full tile of consecutive rows?
-      const int m = dt2 % S::TASK_RING, rs = (it - 2) % S::IDS_SLOTS;
+    if (dt4 >= 0 && warp == 0) {  // the slot's row ids have landed: is it a full tile of consecutive rows?
+      const int m = dt4 % S::TASK_RING, rs = (it - 4) % S::IDS_SLOTS;
       const int lim = id_limit(meta_ptr[m * 8 + 2], max(meta_ptr[m * 8 + 3], 0));
       int first_row = -1;
-      if (tp.has_tma && (dl2 + 1) * C::TILE <= lim) {
+      if (tp.has_tma && (dl4 + 1) * C::TILE <= lim) {
         const int* ids = ids_ptr + rs * C::TILE;
         const int r0 = ids[0];
         const bool mine = ids[lane] == r0 + lane && ids[lane + 32] == r0 + lane + 32;
@@ -343,31 +345,35 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
       }
       if (lane == 0) dense_box[rs] = first_row;
     }
-    if (dt3 >= 0)
-      issue_kv(dt3 % S::TASK_RING, dl3, (it - 3) % S::IDS_SLOTS, dt3 % S::QID_SLOTS, (it - 3) % C::STAGES, dt3 % S::QBUFS);
+    if (dt5 >= 0)
+      issue_kv(dt5 % S::TASK_RING, dl5, (it - 5) % S::IDS_SLOTS, dt5 % S::QID_SLOTS, (it - 5) % C::STAGES, dt5 % S::QBUFS);
     cp_async_commit();
 
     // ---- consume
 #ifdef FT_TIMELINE
-    if (dt5 < 0) ++tl_bubbles;
-    if (dt5 >= 0 && tl_first == 0) tl_first = timeline_now();
+    if (dt7 < 0) ++tl_bubbles;
+    if (dt7 >= 0 && tl_first == 0) tl_first = timeline_now();
 #endif
-    if (dt5 >= 0) {
-      const int m = dt5 % S::TASK_RING;
-      const int stage = (it - 5) % C::STAGES;
+#ifdef FT_TIMELINE
+    if (tid == 0 && it - 8 < 12 && blockIdx.x < FT_TIMELINE_CTAS)
+      g_timeline[16 * blockIdx.x + 4 + (it - 8)] = ((timeline_now() & 0xffffffffffffull) << 8) | (unsigned long long)((dt7 >= 0) | ((dt5 >= 0) << 1) | ((dt0 >= 0) << 2));
+#endif
+    if (dt7 >= 0) {
+      const int m = dt7 % S::TASK_RING;
+      const int stage = (it - 7) % C::STAGES;
       const uint32_t parity = (stage_phase >> stage) & 1u;  // bubbles skip stages, so the phase is tracked per stage
       stage_phase ^= 1u << stage;
       if (!mbar_wait(bars + 8 * stage, parity, S::WAIT_LIMIT)) {
         flag_error(FT_DEV_WAIT_TIMEOUT);  // every thread of the CTA sees the same barrier: all leave together
         break;
       }
-      if (dl5 == 0) {  // a new task: its Q rows arrived together with this tile
+      if (dl7 == 0) {  // a new task: its Q rows arrived together with this tile
         c_qoff = meta_ptr[m * 8 + 0];
         c_rows = min(meta_ptr[m * 8 + 1] * G, 16);
         c_kvlen = max(meta_ptr[m * 8 + 3], 0);
         c_kvh = meta_ptr[m * 8 + 4];
         c_tiles = max(1, (c_kvlen + C::TILE - 1) / C::TILE);
-        const uint32_t q_sm = sm + (dt5 % S::QBUFS) * 16 * C::ROWB;
+        const uint32_t q_sm = sm + (dt7 % S::QBUFS) * 16 * C::ROWB;
 #pragma unroll
         for (int nq = 0; nq < 2; ++nq) {
 #pragma unroll
@@ -383,11 +389,11 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
       }
       const uint32_t k_sm = pipe_sm + stage * 2 * C::STAGE_BYTES, v_sm = k_sm + C::STAGE_BYTES;
       if (c_rows <= 8)
-        stream_tile<T, D, 1>(k_sm, v_sm, tok0, dl5 * C::TILE, c_kvlen, scale2, qb, o_acc, m_run, l_run, lane);
+        stream_tile<T, D, 1>(k_sm, v_sm, tok0, dl7 * C::TILE, c_kvlen, scale2, qb, o_acc, m_run, l_run, lane);
       else
-        stream_tile<T, D, 2>(k_sm, v_sm, tok0, dl5 * C::TILE, c_kvlen, scale2, qb, o_acc, m_run, l_run, lane);
+        stream_tile<T, D, 2>(k_sm, v_sm, tok0, dl7 * C::TILE, c_kvlen, scale2, qb, o_acc, m_run, l_run, lane);
 
-      if (dl5 == c_tiles - 1) {
+      if (dl7 == c_tiles - 1) {
         // ---- end of the task: merge the four warps through the stage just consumed, write the partial rows
         __syncthreads();  // every warp is done reading this stage
         float* epi_o = reinterpret_cast<float*>(smem + S::PIPE_OFF + stage * 2 * C::STAGE_BYTES);
@@ -463,17 +469,18 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
         // the stage is refilled only after the barrier at the top of a later iteration
       }
     }
+    meta_4 = meta_3;
+    meta_3 = meta_2;
     meta_2 = meta_1;
     meta_1 = meta_issued;
 
     // ---- leave when the list is exhausted and every slot in flight has been consumed
     if (next_task >= ntasks && tasks_done == meta_issued) break;
   }
-#ifdef FT_TIMELINE
+#if defined(FT_TIMELINE) && defined(FT_TIMELINE_WORKER_SUMMARY)
   if (tid == 0 && blockIdx.x < FT_TIMELINE_CTAS) {
     g_timeline[16 * blockIdx.x + 4] = tl_first;
     g_timeline[16 * blockIdx.x + 5] = tl_bubbles;
-    g_timeline[16 * blockIdx.x + 6] = tl_claims;
     g_timeline[16 * blockIdx.x + 7] = tasks_done;
     g_timeline[16 * blockIdx.x + 8] = timeline_now();
   }
