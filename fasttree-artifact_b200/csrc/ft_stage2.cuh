@@ -4,8 +4,8 @@
 // One warp per (request, head); lanes span head_dim in float4 chunks, so a
 // partial row of head_dim 128 is one 512-byte coalesced warp load.  The
 // weights exp(lse_i - max) are computed lane-parallel (32 partial rows at a
-// time) and broadcast by shuffle, which keeps the dependent chain per partial
-// to one FMA.  Memory-bound on the partial buffers; those are written by stage
+// time, running maximum across batches) and broadcast by shuffle, which keeps
+// the dependent chain per partial to one FMA.  Memory-bound on the partial buffers; those are written by stage
 // 1 just before and are normally still in L2.
 #pragma once
 
@@ -27,52 +27,67 @@ __global__ void __launch_bounds__(128) stage2_merge_kernel(Stage2Params p) {
   int first_rows = lane < n ? p.r2v_entries[off + lane] : -1;  // plan data: readable before stage 1 is done
   wait_for_prior_grid();                                       // the partial buffers are complete from here on
 
-  // pass 1: maximum LSE over the request's partial rows
+  // One pass with a running maximum (as in the online softmax): per batch of up to 32 partial rows the lanes
+  // fetch their row's LSE while the first rows of the batch are already being loaded - the row addresses depend
+  // on the plan only - so a request with few partials costs one round trip to the partial buffers, not two.
+  constexpr int RB = 4;  // partial rows in flight per lane
   float mx = -INFINITY;
-  for (int i = lane; i < n; i += 32) {
-    const int row = i < 32 ? first_rows : p.r2v_entries[off + i];
-    if (row < 0 || row >= p.num_partial_rows) {
-      flag_error(FT_DEV_BAD_ROW_INDEX);
-      continue;
-    }
-    mx = fmaxf(mx, p.mid_lse[(int64_t)row * p.ml_s0 + head]);
-  }
-  mx = warp_max(mx);
-
   float4 acc[MAXC];
 #pragma unroll
   for (int c = 0; c < MAXC; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
   float wsum = 0.f;
-  if (mx > -INFINITY) {
-    for (int base = 0; base < n; base += 32) {
-      const int cnt = min(32, n - base);
-      int my_row = -1;
-      float my_w = 0.f;
-      if (lane < cnt) {
-        const int row = p.r2v_entries[off + base + lane];
-        if (row >= 0 && row < p.num_partial_rows) {
-          my_row = row;
-          my_w = expf(p.mid_lse[(int64_t)row * p.ml_s0 + head] - mx);
-        }
-      }
-      wsum += my_w;
-#pragma unroll 4
-      for (int i = 0; i < cnt; ++i) {
-        const int row = __shfl_sync(0xffffffffu, my_row, i);
-        const float w = __shfl_sync(0xffffffffu, my_w, i);
-        if (row < 0 || w == 0.f) continue;  // -inf LSE marks an empty partial
+  for (int base = 0; base < n; base += 32) {
+    const int cnt = min(32, n - base);
+    int my_row = -1;
+    if (lane < cnt) {
+      const int row = base == 0 ? first_rows : p.r2v_entries[off + base + lane];
+      if (row >= 0 && row < p.num_partial_rows)
+        my_row = row;
+      else
+        flag_error(FT_DEV_BAD_ROW_INDEX);
+    }
+    const float my_lse = my_row >= 0 ? __ldcg(p.mid_lse + (int64_t)my_row * p.ml_s0 + head) : -INFINITY;
+    float my_w = 0.f;
+    for (int i0 = 0; i0 < cnt; i0 += RB) {
+      float4 x[RB][MAXC];
+      int rows[RB];
+#pragma unroll
+      for (int r = 0; r < RB; ++r) {
+        rows[r] = i0 + r < cnt ? __shfl_sync(0xffffffffu, my_row, (i0 + r) & 31) : -1;
         const float4* __restrict__ src =
-            reinterpret_cast<const float4*>(p.mid_o + (int64_t)row * p.mo_s0 + (int64_t)head * p.mo_s1);
+            reinterpret_cast<const float4*>(p.mid_o + (int64_t)(rows[r] >= 0 ? rows[r] : 0) * p.mo_s0 + (int64_t)head * p.mo_s1);
 #pragma unroll
         for (int c = 0; c < MAXC; ++c) {
           const int ch = lane + 32 * c;
-          if (ch < chunks) {
-            const float4 x = __ldcg(src + ch);
-            acc[c].x = fmaf(w, x.x, acc[c].x);
-            acc[c].y = fmaf(w, x.y, acc[c].y);
-            acc[c].z = fmaf(w, x.z, acc[c].z);
-            acc[c].w = fmaf(w, x.w, acc[c].w);
-          }
+          x[r][c] = rows[r] >= 0 && ch < chunks ? __ldcg(src + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+      if (i0 == 0) {  // the batch's LSEs are needed only now: rescale what has been summed so far to the new maximum
+        const float bm = warp_max(my_lse);
+        const float new_mx = fmaxf(mx, bm);
+        const float corr = new_mx == -INFINITY ? 1.f : expf(mx - new_mx);  // 0 for the first batch
+        wsum *= corr;
+#pragma unroll
+        for (int c = 0; c < MAXC; ++c) {
+          acc[c].x *= corr;
+          acc[c].y *= corr;
+          acc[c].z *= corr;
+          acc[c].w *= corr;
+        }
+        mx = new_mx;
+        my_w = my_lse > -INFINITY ? expf(my_lse - mx) : 0.f;  // -inf LSE marks an empty partial
+        wsum += my_w;
+      }
+#pragma unroll
+      for (int r = 0; r < RB; ++r) {
+        const float w = __shfl_sync(0xffffffffu, my_w, (i0 + r) & 31);
+        if (rows[r] < 0 || w == 0.f) continue;
+#pragma unroll
+        for (int c = 0; c < MAXC; ++c) {
+          acc[c].x = fmaf(w, x[r][c].x, acc[c].x);
+          acc[c].y = fmaf(w, x[r][c].y, acc[c].y);
+          acc[c].z = fmaf(w, x[r][c].z, acc[c].z);
+          acc[c].w = fmaf(w, x[r][c].w, acc[c].w);
         }
       }
     }
