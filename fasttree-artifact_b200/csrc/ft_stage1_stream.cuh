@@ -187,33 +187,35 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
   };
   // row ids of tile `t` of the task in metadata slot `m` -> ids ring slot `rs`; at t == 0 also the request ids
   auto issue_ids = [&](int m, int t, int rs, int qs) {
-    const int q_off = meta_ptr[m * 8 + 0], q_len = meta_ptr[m * 8 + 1];
-    const int kv_off = meta_ptr[m * 8 + 2], kv_len = max(meta_ptr[m * 8 + 3], 0);
-    const int lim = id_limit(kv_off, kv_len);
-    if (tid < C::TILE) {
-      const int pos = t * C::TILE + tid;
-      if (pos < lim) cp_async4(ids_sm + (rs * C::TILE + tid) * 4, p.kv_entries + kv_off + pos);
-      if (tid == 0 && t == 0 && lim < kv_len) flag_error(FT_DEV_BAD_KV_INDEX);
-    } else if (t == 0 && tid - C::TILE < min(q_len, 16)) {  // request ids of the task's (at most 16) slots
-      const int64_t part = (int64_t)q_off + (tid - C::TILE);
-      if (part >= 0 && part < p.num_partial_rows)
-        cp_async4(qid_sm + (qs * 16 + (tid - C::TILE)) * 4, p.q_entries + part);
-      else
-        flag_error(FT_DEV_BAD_ROW_INDEX);
+    if (warp >= 2) {  // warps 2-3: the tile's 64 row ids
+      const int i = tid - 64;
+      const int kv_off = meta_ptr[m * 8 + 2], kv_len = max(meta_ptr[m * 8 + 3], 0);
+      const int lim = id_limit(kv_off, kv_len);
+      const int pos = t * C::TILE + i;
+      if (pos < lim) cp_async4(ids_sm + (rs * C::TILE + i) * 4, p.kv_entries + kv_off + pos);
+      if (i == 0 && t == 0 && lim < kv_len) flag_error(FT_DEV_BAD_KV_INDEX);
+    } else if (warp == 1 && t == 0) {  // warp 1: request ids of the task's (at most 16) slots
+      const int q_off = meta_ptr[m * 8 + 0], q_len = meta_ptr[m * 8 + 1];
+      if (lane < min(q_len, 16)) {
+        const int64_t part = (int64_t)q_off + lane;
+        if (part >= 0 && part < p.num_partial_rows)
+          cp_async4(qid_sm + (qs * 16 + lane) * 4, p.q_entries + part);
+        else
+          flag_error(FT_DEV_BAD_ROW_INDEX);
+      }
     }
   };
   // K/V rows of the tile -> ring stage `st`; at t == 0 also the task's query rows -> Q buffer `qbuf`
   auto issue_kv = [&](int m, int t, int rs, int qs, int st, int qbuf) {
-    const int q_off = meta_ptr[m * 8 + 0], q_len = meta_ptr[m * 8 + 1];
-    const int kv_off = meta_ptr[m * 8 + 2], kv_len = max(meta_ptr[m * 8 + 3], 0);
-    const int kvh = meta_ptr[m * 8 + 4];
-    const int lim = id_limit(kv_off, kv_len);
     const uint32_t k_sm = pipe_sm + st * 2 * C::STAGE_BYTES, v_sm = k_sm + C::STAGE_BYTES;
     const uint32_t full = bars + 8 * st;
     const int first_row = dense_box[rs];
     if (first_row >= 0) {  // 64 consecutive rows: the copy engine writes the tile, no load instructions
-      if (tid == 0) {
-        proxy_fence();  // the stage was last touched with ordinary loads and stores
+      if (tid == 96) {
+        // The stage was last touched with ordinary loads and stores (tile reads, epilogue staging), all of them
+        // before a CTA barrier of an earlier iteration, i.e. complete.  No proxy fence here: it would also wait
+        // for this thread's copies in flight (the row ids just issued) - a full memory round trip per iteration.
+        const int kvh = meta_ptr[m * 8 + 4];
         mbar_expect_tx(full, 2 * C::STAGE_BYTES);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) {
@@ -222,6 +224,9 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
         }
       }
     } else {
+      const int kv_off = meta_ptr[m * 8 + 2], kv_len = max(meta_ptr[m * 8 + 3], 0);
+      const int kvh = meta_ptr[m * 8 + 4];
+      const int lim = id_limit(kv_off, kv_len);
       const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)kvh * p.k_s1 + ld_c * 8;
       const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)kvh * p.v_s1 + ld_c * 8;
       const int* ring = ids_ptr + rs * C::TILE + ld_r;
@@ -243,6 +248,8 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
       if (bad) flag_error(FT_DEV_BAD_KV_INDEX);
     }
     if (t == 0) {
+      const int q_off = meta_ptr[m * 8 + 0], q_len = meta_ptr[m * 8 + 1];
+      const int kvh = meta_ptr[m * 8 + 4];
       const int rows = min(q_len * G, 16);
       if (tid == 0 && q_len * G > 16) flag_error(FT_DEV_BAD_ROW_INDEX);  // not a few-row task: rows beyond 16 are dropped
       const uint32_t q_sm = sm + qbuf * 16 * C::ROWB;
@@ -267,9 +274,13 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
         }
       }
     }
-    // one arrival per thread once all its copies so far (gathered rows, Q rows) have landed; a TMA tile adds its
-    // transaction bytes on top
-    mbar_arrive_on_cp_async(full);
+    // one arrival per thread: at once when this thread copied nothing for the slot (a TMA tile that is not the
+    // task's first: the transaction bytes alone gate the barrier), else once all its copies so far (gathered rows,
+    // Q rows) have landed
+    if (first_row >= 0 && t != 0)
+      mbar_arrive(full);
+    else
+      mbar_arrive_on_cp_async(full);
   };
 
   // ---- pipeline state, identical in every thread
@@ -289,25 +300,35 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
 #ifdef FT_TIMELINE
   unsigned long long tl_first = 0;
   int tl_bubbles = 0;
+  long long tl_c0 = 0, tl_sum_top = 0, tl_sum_issue = 0, tl_sum_wait = 0, tl_sum_tile = 0, tl_sum_epi = 0;
+  int tl_iters = 0, tl_tiles = 0;
 #endif
   cp_async_commit();
   for (unsigned int it = 8;; ++it) {
+#ifdef FT_TIMELINE
+    tl_c0 = clock64();
+#endif
     cp_async_wait<3>();
     __syncthreads();
+#ifdef FT_TIMELINE
+    { const long long c = clock64(); tl_sum_top += c - tl_c0; tl_c0 = c; ++tl_iters; }
+#endif
 
     // ---- metadata of up to two more tasks -> task ring
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       if (next_task < ntasks && meta_issued - tasks_done < S::TASK_RING) {
-        const int b = first_task + next_task;
-        const int vn = p.node_offset + b / H;
-        const int m = meta_issued % S::TASK_RING;
-        const int j = tid - 32 * u;
-        if (j >= 0 && j < 4) {
-          const int32_t* tab = j == 0 ? p.q_offs : j == 1 ? p.q_lens : j == 2 ? p.kv_offs : p.kv_lens;
-          cp_async4(meta_sm + m * 32 + j * 4, tab + vn);
-        } else if (j == 4) {
-          meta_ptr[m * 8 + 4] = b - (b / H) * H;
+        const int j = tid - 8 * u;
+        if (j >= 0 && j < 5) {  // warp 0, five lanes per task
+          const int b = first_task + next_task;
+          const int vn = p.node_offset + b / H;
+          const int m = meta_issued % S::TASK_RING;
+          if (j < 4) {
+            const int32_t* tab = j == 0 ? p.q_offs : j == 1 ? p.q_lens : j == 2 ? p.kv_offs : p.kv_lens;
+            cp_async4(meta_sm + m * 32 + j * 4, tab + vn);
+          } else {
+            meta_ptr[m * 8 + 4] = b - (b / H) * H;
+          }
         }
         next_task += nworkers;
         ++meta_issued;
@@ -333,7 +354,7 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
     }
 
     if (dt0 >= 0) issue_ids(dt0 % S::TASK_RING, dl0, it % S::IDS_SLOTS, dt0 % S::QID_SLOTS);
-    if (dt4 >= 0 && warp == 0) {  // the slot's row ids have landed: is it a full tile of consecutive rows?
+    if (dt4 >= 0 && warp == 1) {  // the slot's row ids have landed: is it a full tile of consecutive rows?
       const int m = dt4 % S::TASK_RING, rs = (it - 4) % S::IDS_SLOTS;
       const int lim = id_limit(meta_ptr[m * 8 + 2], max(meta_ptr[m * 8 + 3], 0));
       int first_row = -1;
@@ -351,12 +372,9 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
 
     // ---- consume
 #ifdef FT_TIMELINE
+    { const long long c = clock64(); tl_sum_issue += c - tl_c0; tl_c0 = c; }
     if (dt7 < 0) ++tl_bubbles;
     if (dt7 >= 0 && tl_first == 0) tl_first = timeline_now();
-#endif
-#ifdef FT_TIMELINE
-    if (tid == 0 && it - 8 < 12 && blockIdx.x < FT_TIMELINE_CTAS)
-      g_timeline[16 * blockIdx.x + 4 + (it - 8)] = ((timeline_now() & 0xffffffffffffull) << 8) | (unsigned long long)((dt7 >= 0) | ((dt5 >= 0) << 1) | ((dt0 >= 0) << 2));
 #endif
     if (dt7 >= 0) {
       const int m = dt7 % S::TASK_RING;
@@ -367,6 +385,9 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
         flag_error(FT_DEV_WAIT_TIMEOUT);  // every thread of the CTA sees the same barrier: all leave together
         break;
       }
+#ifdef FT_TIMELINE
+      { const long long c = clock64(); tl_sum_wait += c - tl_c0; tl_c0 = c; ++tl_tiles; }
+#endif
       if (dl7 == 0) {  // a new task: its Q rows arrived together with this tile
         c_qoff = meta_ptr[m * 8 + 0];
         c_rows = min(meta_ptr[m * 8 + 1] * G, 16);
@@ -393,6 +414,9 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
       else
         stream_tile<T, D, 2>(k_sm, v_sm, tok0, dl7 * C::TILE, c_kvlen, scale2, qb, o_acc, m_run, l_run, lane);
 
+#ifdef FT_TIMELINE
+      { const long long c = clock64(); tl_sum_tile += c - tl_c0; tl_c0 = c; }
+#endif
       if (dl7 == c_tiles - 1) {
         // ---- end of the task: merge the four warps through the stage just consumed, write the partial rows
         __syncthreads();  // every warp is done reading this stage
@@ -466,6 +490,9 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
           }
         }
         ++tasks_done;
+#ifdef FT_TIMELINE
+        { const long long c = clock64(); tl_sum_epi += c - tl_c0; tl_c0 = c; }
+#endif
         // the stage is refilled only after the barrier at the top of a later iteration
       }
     }
@@ -477,12 +504,19 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
     // ---- leave when the list is exhausted and every slot in flight has been consumed
     if (next_task >= ntasks && tasks_done == meta_issued) break;
   }
-#if defined(FT_TIMELINE) && defined(FT_TIMELINE_WORKER_SUMMARY)
-  if (tid == 0 && blockIdx.x < FT_TIMELINE_CTAS) {
-    g_timeline[16 * blockIdx.x + 4] = tl_first;
-    g_timeline[16 * blockIdx.x + 5] = tl_bubbles;
-    g_timeline[16 * blockIdx.x + 7] = tasks_done;
-    g_timeline[16 * blockIdx.x + 8] = timeline_now();
+#ifdef FT_TIMELINE
+  if (tid == 0 && blockIdx.x < FT_TIMELINE_CTAS) {  // developer builds: where this worker's cycles went
+    unsigned long long* rec = g_timeline + 16 * blockIdx.x;
+    rec[4] = tl_first;
+    rec[5] = tl_bubbles;
+    rec[6] = tl_iters;
+    rec[7] = tasks_done;
+    rec[8] = tl_tiles;
+    rec[9] = tl_sum_top;
+    rec[10] = tl_sum_issue;
+    rec[11] = tl_sum_wait;
+    rec[12] = tl_sum_tile;
+    rec[13] = tl_sum_epi;
   }
 #endif
   cp_async_wait<0>();
