@@ -246,6 +246,34 @@ def test_bump_kv_lens():
     assert lens.tolist() == [5, 7, 7, 9]
 
 
+@pytest.mark.parametrize("name", ["mini3_fp16", "rand3_fp16"])
+def test_decode_captured_in_a_cuda_graph(name):
+    """The decode call (fused stage 1 + dependent stage 2, no allocation, no host sync) is captured into a CUDA
+    graph; replays with new query values in the same buffers must match eager calls bit for bit."""
+    c = cases.build_decode_case(name)
+    run, first = gpu_utils.run_case(c, planner="b200", path="auto")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        fasttree.fasttree_decode(run.q, run.k, run.v, run.o, *run.aux, run.tiles[0], run.tiles[1], run.scale)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            fasttree.fasttree_decode(run.q, run.k, run.v, run.o, *run.aux, run.tiles[0], run.tiles[1], run.scale)
+    torch.cuda.current_stream().wait_stream(side)
+    for seed in (1, 2):
+        g = torch.Generator().manual_seed(seed)
+        run.q.copy_(torch.randn(run.q.shape, generator=g).to(run.q.dtype))
+        run.o.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        replayed = run.o.float().cpu()
+        eager = run.decode_via_dropin()
+        assert torch.isfinite(replayed).all()
+        assert torch.equal(replayed, eager)
+    assert lib.read_device_status() == 0
+
+
 # ------------------------------------------------------------ benchmark sizes
 FULL = {
     "cfg3": dict(sizes=[1, 16, 256], lens=[2048, 512, 64], hq=32, hkv=8, dtype=torch.bfloat16, q_scale=0.5),
