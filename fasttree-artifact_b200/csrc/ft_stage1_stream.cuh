@@ -30,8 +30,10 @@
 //                    staged through the ring stage just freed
 // Row ids, request ids and task metadata travel in cp.async groups, one per
 // iteration with wait_group 3 at the top, so such a copy issued in iteration i
-// is complete in iteration i + 4 whatever its latency (small reads queue behind
-// the bulk traffic: with two iterations of slack they gated every iteration).
+// is complete in iteration i + 4 whatever its latency.  The issue work of an
+// iteration is spread over the warps (warp 0 task metadata, warp 1 request ids
+// and the consecutive-ids test, warps 2-3 row ids, one lane of warp 3 the TMA
+// copies), each reading only the metadata it needs.
 // A K/V tile and the task's Q rows signal the mbarrier of the tile's ring stage
 // (transaction bytes for TMA, one arrival per thread when its cp.async copies
 // have landed), which the consumer waits on - bounded.  Task metadata enters a
