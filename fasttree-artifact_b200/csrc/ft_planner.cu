@@ -1,0 +1,303 @@
+// Host-side tree splitter (no device code): the native twin of ft_b200.planner.plan_b200, which stays the
+// specification - the tests require both to produce identical tables.  It turns the radix tree into balanced
+// (node KV chunk x request tile) tasks for one B200 and emits the nine int32 tables of the reference plan
+// format (kernel_bench/fasttree.py:193-262).
+//
+// Steps: (1) greedy walk over the parent->child edges, breadth first, children in id order, on a cost model in
+// streamed-byte equivalents (K/V re-read by a child that carries its parent's KV, fp32 partial rows written and
+// read back, a fixed cost per CTA, tensor-core time); (2) request tile = rows_per_cta / G requests; (3) KV chunks
+// from a global byte target = streamed bytes of the step / (SMs x CTAs per SM x waves), equal chunks per node on
+// 64-token boundaries and never below min_chunk; (4) tasks with more requests than the small tile first (phase
+// 0), longest first inside each phase (stable).  All cost arithmetic is IEEE double in the same order as the
+// Python code, so the decisions agree bit for bit.
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <deque>
+#include <new>
+#include <numeric>
+#include <vector>
+
+#include "fasttree_b200.h"
+
+namespace {
+
+struct Model {
+  int num_sms = 148, ctas_per_sm = 2;
+  double waves = 1.0;
+  int tile_tokens = 64, rows_per_cta = 64, min_chunk = 128, nominal_split = 512;
+  double ridge_flop_per_byte = 90.0;
+  int task_overhead_bytes = 16384, elem_bytes = 2;
+};
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+double task_cost(int64_t n_req, int64_t length, int group, int head_dim, const Model& m) {
+  if (n_req <= 0 || length <= 0) return 0.0;
+  const int64_t rows = n_req * group;
+  const int64_t row_blocks = ceil_div(rows, m.rows_per_cta);
+  const int64_t chunks = ceil_div(length, m.nominal_split);
+  const double stream = (double)(row_blocks * length * 2 * head_dim * m.elem_bytes);
+  const double tensor = (double)(ceil_div(rows, 16) * 16 * length * 4 * head_dim) / m.ridge_flop_per_byte;
+  const double partial = (double)(chunks * rows * (head_dim + 1) * 4 * 2);
+  return std::max(stream, tensor) + partial + (double)(row_blocks * chunks * m.task_overhead_bytes);
+}
+
+}  // namespace
+
+struct ft_plan {
+  std::vector<int32_t> kv_entries, kv_offs, kv_lens, q_entries, q_offs, q_lens, r2v_entries, r2v_offs, r2v_lens;
+  std::vector<int32_t> assignments;
+  ft_plan_info info;
+};
+
+extern "C" {
+
+int ft_plan_b200_build(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, const int64_t* req_offs,
+                       const int32_t* req_ids, const int64_t* kv_ptrs, int32_t batch, int32_t num_qo_heads,
+                       int32_t num_kv_heads, int32_t head_dim, const ft_b200_model* model, ft_plan** out) {
+  if (out == nullptr) return FT_ERR_INVALID_ARGUMENT;
+  *out = nullptr;
+  if (parent == nullptr || seqlen == nullptr || req_offs == nullptr || kv_ptrs == nullptr || n_nodes <= 0 || batch < 0 ||
+      num_qo_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0)
+    return FT_ERR_INVALID_ARGUMENT;
+  if (req_ids == nullptr && req_offs[n_nodes] > 0) return FT_ERR_INVALID_ARGUMENT;
+  for (int i = 1; i < n_nodes; ++i)
+    if (parent[i] < 0 || parent[i] >= i) return FT_ERR_INVALID_ARGUMENT;  // node 0 is the root, parents precede children
+  Model m;
+  if (model != nullptr) {
+    m.num_sms = model->num_sms;
+    m.ctas_per_sm = model->ctas_per_sm;
+    m.waves = model->waves;
+    m.tile_tokens = model->tile_tokens;
+    m.rows_per_cta = model->rows_per_cta;
+    m.min_chunk = model->min_chunk;
+    m.nominal_split = model->nominal_split;
+    m.ridge_flop_per_byte = model->ridge_flop_per_byte;
+    m.task_overhead_bytes = model->task_overhead_bytes;
+    m.elem_bytes = model->elem_bytes;
+    if (m.num_sms <= 0 || m.ctas_per_sm <= 0 || !(m.waves > 0) || m.tile_tokens <= 0 || m.rows_per_cta <= 0 ||
+        m.min_chunk <= 0 || m.nominal_split <= 0 || !(m.ridge_flop_per_byte > 0) || m.elem_bytes <= 0)
+      return FT_ERR_INVALID_ARGUMENT;
+  } else if (head_dim == 128) {
+    m.rows_per_cta = 128;  // the tcgen05 stage-1 kernel holds 128 query rows per CTA
+    m.ridge_flop_per_byte = 4 * m.ridge_flop_per_byte;
+  }
+  ft_plan* plan = new (std::nothrow) ft_plan();
+  if (plan == nullptr) return FT_ERR_TOO_LARGE;
+  try {
+    const int n = n_nodes;
+    const int group = std::max(1, num_qo_heads / num_kv_heads);
+    const int q_tile = std::max(1, m.rows_per_cta / group);
+    const int small_tile = std::max(1, std::min(q_tile, group <= 16 ? 16 / group : 1));
+    auto n_req = [&](int i) { return req_offs[i + 1] - req_offs[i]; };
+
+    // ---- 1. edges
+    std::vector<std::vector<int>> kids(n);
+    for (int i = 1; i < n; ++i) kids[parent[i]].push_back(i);
+    std::vector<int64_t> run_len(seqlen, seqlen + n);
+    std::vector<int32_t>& assign = plan->assignments;
+    assign.assign(n, 0);
+    std::deque<int> frontier{0};
+    while (!frontier.empty()) {
+      const int v = frontier.front();
+      frontier.pop_front();
+      int64_t n_here = n_req(v);
+      for (int c : kids[v]) {
+        const int64_t n_c = n_req(c);
+        const double own = task_cost(n_here, run_len[v], group, head_dim, m) + task_cost(n_c, run_len[c], group, head_dim, m);
+        const double carried = task_cost(n_here - n_c, run_len[v], group, head_dim, m) +
+                               task_cost(n_c, run_len[c] + run_len[v], group, head_dim, m);
+        if (carried < own) {
+          assign[c] = 1;
+          n_here -= n_c;
+          run_len[c] += run_len[v];
+        }
+        frontier.push_back(c);
+      }
+    }
+
+    // ---- 2./3. virtual nodes: requests a node still serves, its row ranges, its chunk length
+    struct Spec {
+      std::vector<std::pair<int64_t, int64_t>> ranges;
+      std::vector<int32_t> reqs;
+      int64_t length;
+      int64_t chunk;
+    };
+    std::vector<Spec> specs;
+    const int64_t row_bytes = 2LL * head_dim * m.elem_bytes;
+    int64_t total_stream = 0;
+    std::vector<uint8_t> gone((size_t)std::max(batch, 1));
+    for (int i = 0; i < n; ++i) {
+      // requests of this node minus those of children that carry its KV, sorted, duplicates removed
+      std::vector<int32_t> reqs(req_ids + req_offs[i], req_ids + req_offs[i + 1]);
+      std::sort(reqs.begin(), reqs.end());
+      reqs.erase(std::unique(reqs.begin(), reqs.end()), reqs.end());
+      for (int32_t r : reqs)
+        if (r < 0 || r >= batch) {
+          delete plan;
+          return FT_ERR_INVALID_ARGUMENT;
+        }
+      bool any_gone = false;
+      for (int c : kids[i])
+        if (assign[c] == 1) {
+          for (int64_t k = req_offs[c]; k < req_offs[c + 1]; ++k)
+            if (req_ids[k] >= 0 && req_ids[k] < batch) gone[req_ids[k]] = 1, any_gone = true;
+        }
+      if (any_gone) {
+        std::vector<int32_t> kept;
+        for (int32_t r : reqs)
+          if (!gone[r]) kept.push_back(r);
+        for (int c : kids[i])
+          if (assign[c] == 1)
+            for (int64_t k = req_offs[c]; k < req_offs[c + 1]; ++k)
+              if (req_ids[k] >= 0 && req_ids[k] < batch) gone[req_ids[k]] = 0;
+        reqs.swap(kept);
+      }
+      if (reqs.empty()) continue;
+      Spec s;
+      s.ranges.emplace_back(kv_ptrs[i], kv_ptrs[i + 1]);
+      for (int up = i; assign[up] == 1;) {
+        up = parent[up];
+        s.ranges.emplace_back(kv_ptrs[up], kv_ptrs[up + 1]);
+      }
+      std::reverse(s.ranges.begin(), s.ranges.end());  // root-most segment first
+      s.length = 0;
+      for (auto& r : s.ranges) s.length += r.second - r.first;
+      if (s.length <= 0) continue;
+      s.reqs.swap(reqs);
+      total_stream += ceil_div((int64_t)s.reqs.size(), q_tile) * s.length * row_bytes;
+      specs.push_back(std::move(s));
+    }
+    const double slots = (double)(m.num_sms * m.ctas_per_sm) * m.waves;
+    const double target = std::max((double)(total_stream * num_kv_heads) / slots, (double)(m.min_chunk * row_bytes));
+    for (Spec& s : specs) {
+      const int64_t want = (int64_t)std::nearbyint((double)(s.length * row_bytes) / target);  // ties to even, like round()
+      const int64_t n_chunks = std::max<int64_t>(1, std::min(want, ceil_div(s.length, m.min_chunk)));
+      s.chunk = ceil_div(ceil_div(s.length, n_chunks), m.tile_tokens) * m.tile_tokens;
+    }
+
+    // ---- emission: chunk-major, request-tile-minor; every chunk repeats the node's request list
+    std::vector<int64_t> kv_offs, kv_lens, q_offs, q_lens;
+    int64_t kv_total = 0, q_total = 0;
+    for (const Spec& s : specs) {
+      const int64_t nreq = (int64_t)s.reqs.size();
+      for (auto& r : s.ranges)
+        for (int64_t row = r.first; row < r.second; ++row) plan->kv_entries.push_back((int32_t)row);
+      const int64_t n_kv = ceil_div(s.length, s.chunk), n_q = ceil_div(nreq, q_tile);
+      for (int64_t c = 0; c < n_kv; ++c) {
+        const int64_t c_off = c * s.chunk, c_len = std::min(c_off + s.chunk, s.length) - c_off;
+        for (int64_t t = 0; t < n_q; ++t) {
+          const int64_t t_off = t * q_tile;
+          kv_offs.push_back(kv_total + c_off);
+          kv_lens.push_back(c_len);
+          q_offs.push_back(q_total + c * nreq + t_off);
+          q_lens.push_back(std::min(t_off + q_tile, nreq) - t_off);
+        }
+        plan->q_entries.insert(plan->q_entries.end(), s.reqs.begin(), s.reqs.end());
+      }
+      kv_total += s.length;
+      q_total += n_kv * nreq;
+    }
+    const int64_t pad = 32;  // the reference appends 32 x -1 to both index lists (fasttree.py:261-262)
+    int64_t max_off = 0;
+    for (int64_t o : kv_offs) max_off = std::max(max_off, o);
+    if (kv_total + pad >= (1LL << 31) || q_total >= (1LL << 31) || max_off >= (1LL << 31)) {
+      delete plan;
+      return FT_ERR_TOO_LARGE;
+    }
+    plan->kv_entries.insert(plan->kv_entries.end(), (size_t)pad, -1);
+
+    // request -> partial rows: rows grouped by request id, emission order kept inside a group
+    std::vector<int64_t> counts((size_t)batch, 0);
+    for (int32_t r : plan->q_entries) ++counts[r];
+    plan->r2v_offs.resize(batch);
+    plan->r2v_lens.resize(batch);
+    int64_t acc = 0;
+    for (int b = 0; b < batch; ++b) {
+      plan->r2v_offs[b] = (int32_t)acc;
+      plan->r2v_lens[b] = (int32_t)counts[b];
+      acc += counts[b];
+    }
+    plan->r2v_entries.assign((size_t)(q_total + pad), -1);
+    {
+      std::vector<int64_t> cursor(plan->r2v_offs.begin(), plan->r2v_offs.end());
+      for (int64_t row = 0; row < q_total; ++row) plan->r2v_entries[(size_t)cursor[plan->q_entries[row]]++] = (int32_t)row;
+    }
+
+    // phases and order: more requests than the small tile first; inside a phase longest KV chunk first, then
+    // more requests first (key = kv_len * 64 + min(q_len, 63)), stable
+    const size_t nv = kv_offs.size();
+    std::vector<size_t> big, small;
+    for (size_t i = 0; i < nv; ++i) (q_lens[i] > small_tile ? big : small).push_back(i);
+    auto key = [&](size_t i) { return kv_lens[i] * 64 + std::min<int64_t>(q_lens[i], 63); };
+    auto by_key = [&](size_t a, size_t b) { return key(a) > key(b); };
+    std::stable_sort(big.begin(), big.end(), by_key);
+    std::stable_sort(small.begin(), small.end(), by_key);
+    std::vector<size_t> perm(big);
+    perm.insert(perm.end(), small.begin(), small.end());
+    plan->kv_offs.resize(nv);
+    plan->kv_lens.resize(nv);
+    plan->q_offs.resize(nv);
+    plan->q_lens.resize(nv);
+    for (size_t i = 0; i < nv; ++i) {
+      plan->kv_offs[i] = (int32_t)kv_offs[perm[i]];
+      plan->kv_lens[i] = (int32_t)kv_lens[perm[i]];
+      plan->q_offs[i] = (int32_t)q_offs[perm[i]];
+      plan->q_lens[i] = (int32_t)q_lens[perm[i]];
+    }
+    ft_plan_info& info = plan->info;
+    std::memset(&info, 0, sizeof(info));
+    info.kv_entries = (int64_t)plan->kv_entries.size();
+    info.vnodes = (int64_t)nv;
+    info.partial_rows = q_total;
+    info.batch = batch;
+    info.nodes = n;
+    info.phase_node_nums[0] = (int32_t)big.size();
+    info.phase_node_nums[1] = (int32_t)small.size();
+    info.phase_node_offsets[0] = 0;
+    info.phase_node_offsets[1] = (int32_t)big.size();
+    info.q_tile = q_tile;
+    info.small_tile = small_tile;
+    info.tile_tokens = m.tile_tokens;
+    info.target_bytes = target;
+    info.virtual_nodes = (int64_t)specs.size();
+  } catch (const std::bad_alloc&) {
+    delete plan;
+    return FT_ERR_TOO_LARGE;
+  }
+  *out = plan;
+  return FT_OK;
+}
+
+int ft_plan_get_info(const ft_plan* plan, ft_plan_info* info) {
+  if (plan == nullptr || info == nullptr) return FT_ERR_INVALID_ARGUMENT;
+  *info = plan->info;
+  return FT_OK;
+}
+
+// Copies the tables into caller-provided host arrays of the sizes ft_plan_get_info reports (NULL: skip that table).
+int ft_plan_copy_tables(const ft_plan* plan, int32_t* kv_entries, int32_t* kv_offs, int32_t* kv_lens, int32_t* q_entries,
+                        int32_t* q_offs, int32_t* q_lens, int32_t* r2v_entries, int32_t* r2v_offs, int32_t* r2v_lens,
+                        int32_t* node_assignments) {
+  if (plan == nullptr) return FT_ERR_INVALID_ARGUMENT;
+  auto put = [](int32_t* dst, const std::vector<int32_t>& src) {
+    if (dst != nullptr && !src.empty()) std::memcpy(dst, src.data(), src.size() * sizeof(int32_t));
+  };
+  put(kv_entries, plan->kv_entries);
+  put(kv_offs, plan->kv_offs);
+  put(kv_lens, plan->kv_lens);
+  put(q_entries, plan->q_entries);
+  put(q_offs, plan->q_offs);
+  put(q_lens, plan->q_lens);
+  put(r2v_entries, plan->r2v_entries);
+  put(r2v_offs, plan->r2v_offs);
+  put(r2v_lens, plan->r2v_lens);
+  put(node_assignments, plan->assignments);
+  return FT_OK;
+}
+
+void ft_plan_free(ft_plan* plan) { delete plan; }
+
+}  // extern "C"

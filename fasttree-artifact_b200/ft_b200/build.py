@@ -13,7 +13,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(ROOT, "include")
 LIB_PATH = os.path.join(PKG_DIR, "libfasttree_b200.so")
 
-SOURCES = ["ft_api.cu"]
+SOURCES = ["ft_api.cu", "ft_planner.cu"]
 
 
 def _nvcc():

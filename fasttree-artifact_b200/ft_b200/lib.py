@@ -21,7 +21,8 @@ FT_DEV_BAD_KV_INDEX, FT_DEV_BAD_Q_INDEX, FT_DEV_BAD_ROW_INDEX, FT_DEV_WAIT_TIMEO
 
 EXPORTS = ["ft_version", "ft_decode_args_size", "ft_last_error", "ft_decode", "ft_stage1", "ft_stage2",
            "ft_decode_static_scratch", "ft_bump_kv_lens",
-           "ft_read_device_status", "ft_launch_count", "ft_stage1_path_name"]
+           "ft_read_device_status", "ft_launch_count", "ft_stage1_path_name",
+           "ft_plan_b200_build", "ft_plan_get_info", "ft_plan_copy_tables", "ft_plan_free"]
 
 
 class FastTreeError(RuntimeError):
@@ -30,6 +31,23 @@ class FastTreeError(RuntimeError):
     def __init__(self, code, message):
         super().__init__(f"fasttree_b200 error {code}: {message}")
         self.code = code
+
+
+class B200ModelStruct(ctypes.Structure):
+    """Mirror of ``struct ft_b200_model``."""
+    _fields_ = [("num_sms", ctypes.c_int32), ("ctas_per_sm", ctypes.c_int32), ("waves", ctypes.c_double),
+                ("tile_tokens", ctypes.c_int32), ("rows_per_cta", ctypes.c_int32), ("min_chunk", ctypes.c_int32),
+                ("nominal_split", ctypes.c_int32), ("ridge_flop_per_byte", ctypes.c_double),
+                ("task_overhead_bytes", ctypes.c_int32), ("elem_bytes", ctypes.c_int32)]
+
+
+class PlanInfo(ctypes.Structure):
+    """Mirror of ``struct ft_plan_info``."""
+    _fields_ = [("kv_entries", ctypes.c_int64), ("vnodes", ctypes.c_int64), ("partial_rows", ctypes.c_int64),
+                ("batch", ctypes.c_int64), ("nodes", ctypes.c_int64), ("virtual_nodes", ctypes.c_int64),
+                ("phase_node_nums", ctypes.c_int32 * 2), ("phase_node_offsets", ctypes.c_int32 * 2),
+                ("q_tile", ctypes.c_int32), ("small_tile", ctypes.c_int32), ("tile_tokens", ctypes.c_int32),
+                ("reserved", ctypes.c_int32), ("target_bytes", ctypes.c_double)]
 
 
 class DecodeArgs(ctypes.Structure):
@@ -105,6 +123,17 @@ def load():
         lib.ft_launch_count.restype = ctypes.c_int64
         lib.ft_stage1_path_name.argtypes = [argp]
         lib.ft_stage1_path_name.restype = ctypes.c_char_p
+        i32p, i64p = ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int64)
+        lib.ft_plan_b200_build.argtypes = [i32p, i32p, ctypes.c_int32, i64p, i32p, i64p, ctypes.c_int32, ctypes.c_int32,
+                                           ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(B200ModelStruct),
+                                           ctypes.POINTER(ctypes.c_void_p)]
+        lib.ft_plan_b200_build.restype = ctypes.c_int
+        lib.ft_plan_get_info.argtypes = [ctypes.c_void_p, ctypes.POINTER(PlanInfo)]
+        lib.ft_plan_get_info.restype = ctypes.c_int
+        lib.ft_plan_copy_tables.argtypes = [ctypes.c_void_p] + [i32p] * 10
+        lib.ft_plan_copy_tables.restype = ctypes.c_int
+        lib.ft_plan_free.argtypes = [ctypes.c_void_p]
+        lib.ft_plan_free.restype = None
         _lib = lib
     return _lib
 

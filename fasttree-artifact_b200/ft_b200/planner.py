@@ -366,6 +366,60 @@ def plan_b200(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, p
                 info={"planner": "b200", "target_bytes": float(target), "vnodes": len(vnodes)}, **tabs)
 
 
+def plan_b200_native(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, params, model=None):
+    """:func:`plan_b200` computed by the native splitter of the shared library
+    (``ft_plan_b200_build``, csrc/ft_planner.cu).  Same arguments, same result -
+    the tests hold the two to identical tables; this one is one to two orders of
+    magnitude faster on large trees.  Node 0 must be the root and parents must
+    precede their children, as in the reference tree format."""
+    import ctypes
+    from . import lib as _lib
+    L = _lib.load()
+    n = len(tree)
+    parent = np.fromiter((nd.parent for nd in tree), dtype=np.int32, count=n)
+    seqlen = np.fromiter((nd.seqlen for nd in tree), dtype=np.int32, count=n)
+    counts = np.fromiter((len(nd.requests) for nd in tree), dtype=np.int64, count=n)
+    req_offs = np.zeros(n + 1, dtype=np.int64)
+    np.cumsum(counts, out=req_offs[1:])
+    req_ids = np.zeros(max(int(req_offs[-1]), 1), dtype=np.int32)
+    for i, nd in enumerate(tree):
+        if counts[i]:
+            req_ids[req_offs[i]:req_offs[i + 1]] = nd.requests
+    ptrs = np.ascontiguousarray(np.asarray(kv_ptrs, dtype=np.int64))
+    if ptrs.size != n + 1:
+        raise ValueError("kv_ptrs must have one entry more than the tree has nodes")
+    m = b200_model_for(params, head_dim, model)
+    ms = _lib.B200ModelStruct(m.num_sms, m.ctas_per_sm, m.waves, m.tile_tokens, m.rows_per_cta, m.min_chunk,
+                              m.nominal_split, m.ridge_flop_per_byte, m.task_overhead_bytes, m.elem_bytes)
+    i32p, i64p = ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int64)
+    as32 = lambda a: a.ctypes.data_as(i32p)
+    handle = ctypes.c_void_p()
+    _lib.check(L.ft_plan_b200_build(as32(parent), as32(seqlen), n, req_offs.ctypes.data_as(i64p), as32(req_ids),
+                                    ptrs.ctypes.data_as(i64p), batch_size, num_qo_heads, num_kv_heads, head_dim,
+                                    ctypes.byref(ms), ctypes.byref(handle)))
+    try:
+        info = _lib.PlanInfo()
+        _lib.check(L.ft_plan_get_info(handle, ctypes.byref(info)))
+        tabs = dict(
+            vnode_to_kv_entries=np.empty(info.kv_entries, dtype=np.int32),
+            vnode_to_kv_offs=np.empty(info.vnodes, dtype=np.int32), vnode_to_kv_lens=np.empty(info.vnodes, dtype=np.int32),
+            vnode_to_q_entries=np.empty(info.partial_rows, dtype=np.int32),
+            vnode_to_q_offs=np.empty(info.vnodes, dtype=np.int32), vnode_to_q_lens=np.empty(info.vnodes, dtype=np.int32),
+            req_to_vnode_entries=np.empty(info.partial_rows + PAD_ENTRIES, dtype=np.int32),
+            req_to_vnode_offs=np.empty(info.batch, dtype=np.int32), req_to_vnode_lens=np.empty(info.batch, dtype=np.int32))
+        assign = np.empty(info.nodes, dtype=np.int32)
+        _lib.check(L.ft_plan_copy_tables(handle, *(as32(t) for t in tabs.values()), as32(assign)))
+    finally:
+        L.ft_plan_free(handle)
+    params.set_q_tile_sizes([info.q_tile, info.small_tile])
+    params.set_kv_tile_sizes([info.tile_tokens, info.tile_tokens])
+    return Plan(node_assignments=[int(a) for a in assign], phase_q_tile_sizes=[info.q_tile, info.small_tile],
+                phase_kv_tile_sizes=[info.tile_tokens, info.tile_tokens], kv_split_sizes=[],
+                info={"planner": "b200", "target_bytes": float(info.target_bytes), "vnodes": int(info.virtual_nodes)},
+                phase_node_nums=[int(x) for x in info.phase_node_nums],
+                phase_node_offsets=[int(x) for x in info.phase_node_offsets], **tabs)
+
+
 def b200_model_for(params, head_dim, model=None):
     explicit = model or getattr(params, "b200_model", None)
     m = explicit or B200Model()

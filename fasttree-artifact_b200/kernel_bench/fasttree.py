@@ -3,8 +3,9 @@
 Exports the three names the harnesses import (kernel_bench/benchmark.py:7):
 ``FastTreeParams``, ``fasttree_preparation`` and ``fasttree_decode``, with the
 reference's signatures and the reference's 13-slot auxiliary tuple.  The
-planner runs on the host (ft_b200.planner); the decode call goes to hand-written
-sm_100a CUDA through the C ABI (include/fasttree_b200.h).  There is no Triton
+planner runs on the host (the native splitter of the shared library, specified
+by ft_b200.planner); the decode call goes to hand-written sm_100a CUDA through
+the C ABI (include/fasttree_b200.h).  There is no Triton
 and no CPU fallback: tensors must be CUDA tensors and the shared library must be
 present, otherwise the calls raise.
 """
@@ -37,6 +38,7 @@ class FastTreeParams:
     TSKs = [32, 128]
     kv_group_num = 1
     planner = "b200"
+    native_planner = True
     verbose = False
 
     def set_values(self, alpha, beta, gamma):
@@ -68,7 +70,10 @@ def build_plan(tree_info, KV_ptrs, batch_size, num_qo_heads, num_kv_heads, head_
         plan = _planner.plan_reference(tree_info, KV_ptrs, batch_size, num_kv_heads, KV_SPLIT_SIZES,
                                        para_threshs1, para_threshs2, params, log=log)
     else:
-        plan = _planner.plan_b200(tree_info, KV_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, params)
+        # the native splitter of the shared library; ft_b200.planner.plan_b200 is its Python specification
+        # (params.native_planner = False selects it; the tests hold the two to identical tables)
+        split = _planner.plan_b200_native if getattr(params, "native_planner", True) else _planner.plan_b200
+        plan = split(tree_info, KV_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, params)
     if log:
         for what, val in log:
             print(f"{what}:", val)

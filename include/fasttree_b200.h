@@ -171,6 +171,56 @@ int64_t ft_launch_count(void);
  * ("generic", "mma", "tcgen05"), or NULL with ft_last_error() set. */
 const char* ft_stage1_path_name(const ft_decode_args* args);
 
+/* ---- host-side planner -------------------------------------------------------------------------------------
+ * Native counterpart of the tree splitter that produces the plan tables above (the tables the reference builds
+ * in Python, kernel_bench/fasttree.py:99-296; this splitter uses a B200 cost model instead of the reference's
+ * padding heuristic and is what ft_b200.planner.plan_b200 specifies).  Pure host code: no CUDA call, no device
+ * memory.  ft_plan_b200_build creates a plan object, ft_plan_get_info reports the table sizes,
+ * ft_plan_copy_tables copies the tables into caller-owned host arrays, ft_plan_free releases the object. */
+typedef struct ft_plan ft_plan;
+
+typedef struct ft_b200_model { /* machine constants of the cost model; NULL in ft_plan_b200_build = defaults */
+  int32_t num_sms;             /* 148 */
+  int32_t ctas_per_sm;         /* 2 */
+  double waves;                /* rounds of resident CTAs to aim for: 1.0 */
+  int32_t tile_tokens;         /* KV tile of the stage-1 kernels: 64 */
+  int32_t rows_per_cta;        /* query rows one CTA holds: 64 (128 at head_dim 128) */
+  int32_t min_chunk;           /* never cut a node's KV finer than this many tokens: 128 */
+  int32_t nominal_split;       /* chunk length assumed while deciding the edges: 512 */
+  double ridge_flop_per_byte;  /* flops that cost as much time as one streamed byte: 90 (360 at head_dim 128) */
+  int32_t task_overhead_bytes; /* fixed cost of one more CTA in streamed-byte equivalents: 16384 */
+  int32_t elem_bytes;          /* 2 */
+} ft_b200_model;
+
+typedef struct ft_plan_info {
+  int64_t kv_entries;   /* length of vnode_to_kv_entries, including the 32 trailing -1 */
+  int64_t vnodes;       /* length of the six per-vnode tables */
+  int64_t partial_rows; /* length of vnode_to_q_entries = rows of mid_o / mid_lse; req_to_vnode_entries has 32 more */
+  int64_t batch;        /* length of req_to_vnode_offs / lens */
+  int64_t nodes;        /* length of node_assignments */
+  int64_t virtual_nodes;
+  int32_t phase_node_nums[2];
+  int32_t phase_node_offsets[2];
+  int32_t q_tile;       /* requests per task in phase 0 / 1: the tile sizes to pass as phase_q_tile_sizes */
+  int32_t small_tile;
+  int32_t tile_tokens;
+  int32_t reserved;
+  double target_bytes;  /* streamed bytes one task was sized for */
+} ft_plan_info;
+
+/* Tree: n_nodes records in id order, node 0 the root, parents before children (parent[0] = -1); seqlen tokens per
+ * node; the requests whose path contains node i are req_ids[req_offs[i] .. req_offs[i+1]); kv_ptrs[i] .. kv_ptrs[i+1]
+ * are the node's rows in the K/V buffers.  num_kv_heads is the LOCAL head count of this GPU. */
+int ft_plan_b200_build(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, const int64_t* req_offs,
+                       const int32_t* req_ids, const int64_t* kv_ptrs, int32_t batch, int32_t num_qo_heads,
+                       int32_t num_kv_heads, int32_t head_dim, const ft_b200_model* model, ft_plan** out);
+int ft_plan_get_info(const ft_plan* plan, ft_plan_info* info);
+int ft_plan_copy_tables(const ft_plan* plan, int32_t* vnode_to_kv_entries, int32_t* vnode_to_kv_offs,
+                        int32_t* vnode_to_kv_lens, int32_t* vnode_to_q_entries, int32_t* vnode_to_q_offs,
+                        int32_t* vnode_to_q_lens, int32_t* req_to_vnode_entries, int32_t* req_to_vnode_offs,
+                        int32_t* req_to_vnode_lens, int32_t* node_assignments);
+void ft_plan_free(ft_plan* plan);
+
 #ifdef __cplusplus
 }
 #endif

@@ -132,6 +132,66 @@ def test_b200_plan_on_random_trees(seed):
     check_plan_covers_every_path_once(tree, ptrs, batch, plan)
 
 
+def _same_plan(a, b):
+    for x, y, name in zip(a.tables(), b.tables(), cases.TABLES):
+        np.testing.assert_array_equal(x, y, err_msg=name)
+    assert list(a.node_assignments) == list(b.node_assignments)
+    assert list(a.phase_node_nums) == list(b.phase_node_nums)
+    assert list(a.phase_node_offsets) == list(b.phase_node_offsets)
+    assert list(a.phase_q_tile_sizes) == list(b.phase_q_tile_sizes)
+    assert a.info["target_bytes"] == b.info["target_bytes"] and a.info["vnodes"] == b.info["vnodes"]
+
+
+NATIVE_TREES = dict(B200_TREES)
+NATIVE_TREES.update({
+    "cfg4": ([1, 1024], [16384, 32], 64, 8),
+    "mha_chain": ([1, 1, 1, 4], [100, 7, 300, 20], 8, 8),
+    "gqa16": ([1, 2, 64], [8, 256, 32], 16, 1),
+})
+
+
+@pytest.mark.parametrize("name", sorted(NATIVE_TREES))
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_native_splitter_matches_the_python_specification(name, head_dim):
+    """ft_plan_b200_build (C++, in the shared library; host code only) against ft_b200.planner.plan_b200."""
+    sizes, lens, hq, hkv = NATIVE_TREES[name]
+    tree, batch, ptrs = product_tree(ref_inputs.layered_tree(sizes, lens))
+    pa, pb = make_params(hq, hkv, [16, 4], planner_name="b200"), make_params(hq, hkv, [16, 4], planner_name="b200")
+    spec = planner.plan_b200(tree, ptrs, batch, hq, hkv, head_dim, pa)
+    native = planner.plan_b200_native(tree, ptrs, batch, hq, hkv, head_dim, pb)
+    _same_plan(spec, native)
+    assert list(pa.TSQs) == list(pb.TSQs) and list(pa.TSKs) == list(pb.TSKs)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_native_splitter_matches_on_random_trees_and_models(seed):
+    from dataclasses import replace
+    rng = np.random.default_rng(seed)
+    tree, batch, ptrs = product_tree(ref_inputs.random_tree(3 + seed % 3, seed, max_children=6 + seed, lam=2.0 + seed % 3,
+                                                            len_lo=1, len_hi=40 * (1 + seed)))
+    hq, hkv = [(32, 8), (8, 8), (16, 1), (64, 8)][seed % 4]
+    model = replace(planner.B200Model(), waves=float(rng.choice([0.5, 1.0, 2.0, 3.0])), min_chunk=int(rng.choice([64, 128, 256])),
+                    rows_per_cta=int(rng.choice([64, 128])), ridge_flop_per_byte=float(rng.choice([90.0, 360.0])))
+    pa, pb = make_params(hq, hkv, [16, 4], planner_name="b200"), make_params(hq, hkv, [16, 4], planner_name="b200")
+    spec = planner.plan_b200(tree, ptrs, batch, hq, hkv, 128, pa, model=model)
+    native = planner.plan_b200_native(tree, ptrs, batch, hq, hkv, 128, pb, model=model)
+    _same_plan(spec, native)
+    check_plan_covers_every_path_once(tree, ptrs, batch, native)
+
+
+def test_native_splitter_rejects_bad_trees():
+    from ft_b200 import lib
+    tree, batch, ptrs = product_tree(ref_inputs.layered_tree([1, 2], [5, 5]))
+    p = make_params(8, 8, [16, 4], planner_name="b200")
+    with pytest.raises(ValueError):
+        planner.plan_b200_native(tree, ptrs[:-1], batch, 8, 8, 128, p)
+    with pytest.raises(lib.FastTreeError):                      # a request id outside the batch
+        planner.plan_b200_native(tree, ptrs, batch - 1, 8, 8, 128, p)
+    tree[1].parent = 2                                         # parent after child
+    with pytest.raises(lib.FastTreeError):
+        planner.plan_b200_native(tree, ptrs, batch, 8, 8, 128, p)
+
+
 def test_b200_plan_splits_long_prefix_and_keeps_leaves_whole():
     tree, batch, ptrs = product_tree(ref_inputs.layered_tree([1, 64], [4096, 256]))
     p = make_params(32, 8, [16, 4], planner_name="b200")
