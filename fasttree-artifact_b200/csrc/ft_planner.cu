@@ -52,15 +52,32 @@ struct ft_plan {
   ft_plan_info info;
 };
 
-extern "C" {
+namespace {
 
-int ft_plan_b200_build(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, const int64_t* req_offs,
-                       const int32_t* req_ids, const int64_t* kv_ptrs, int32_t batch, int32_t num_qo_heads,
-                       int32_t num_kv_heads, int32_t head_dim, const ft_b200_model* model, ft_plan** out) {
+// Addressing of the serving path: a node's KV (and that of the ancestors it carries) is ONE run of positions in
+// an existing row-id table (SGLang's flattened req_to_token): [base[i] + offset[top carried ancestor],
+// base[i] + offset[i] + seqlen[i]).  No row-id table is emitted; vnode_to_kv_offs are positions in that table.
+// `extra` pairings (one request each: its private tail) join the byte budget and come last in emission order.
+struct Direct {
+  const int64_t* node_base = nullptr;
+  const int64_t* node_offset = nullptr;
+  int64_t n_extra = 0;
+  const int64_t* extra_begin = nullptr;
+  const int64_t* extra_end = nullptr;
+  const int32_t* extra_req = nullptr;
+};
+
+int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, const int64_t* req_offs,
+               const int32_t* req_ids, const int64_t* kv_ptrs, const Direct* direct, int32_t batch, int32_t num_qo_heads,
+               int32_t num_kv_heads, int32_t head_dim, const ft_b200_model* model, ft_plan** out) {
   if (out == nullptr) return FT_ERR_INVALID_ARGUMENT;
   *out = nullptr;
-  if (parent == nullptr || seqlen == nullptr || req_offs == nullptr || kv_ptrs == nullptr || n_nodes <= 0 || batch < 0 ||
-      num_qo_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0)
+  if (parent == nullptr || seqlen == nullptr || req_offs == nullptr || (kv_ptrs == nullptr && direct == nullptr) ||
+      n_nodes <= 0 || batch < 0 || num_qo_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0)
+    return FT_ERR_INVALID_ARGUMENT;
+  if (direct != nullptr &&
+      (direct->node_base == nullptr || direct->node_offset == nullptr || direct->n_extra < 0 ||
+       (direct->n_extra > 0 && (direct->extra_begin == nullptr || direct->extra_end == nullptr || direct->extra_req == nullptr))))
     return FT_ERR_INVALID_ARGUMENT;
   if (req_ids == nullptr && req_offs[n_nodes] > 0) return FT_ERR_INVALID_ARGUMENT;
   for (int i = 1; i < n_nodes; ++i)
@@ -157,18 +174,42 @@ int ft_plan_b200_build(const int32_t* parent, const int32_t* seqlen, int32_t n_n
       }
       if (reqs.empty()) continue;
       Spec s;
-      s.ranges.emplace_back(kv_ptrs[i], kv_ptrs[i + 1]);
-      for (int up = i; assign[up] == 1;) {
-        up = parent[up];
-        s.ranges.emplace_back(kv_ptrs[up], kv_ptrs[up + 1]);
+      if (direct != nullptr) {
+        int top = i;
+        while (assign[top] == 1) top = parent[top];
+        s.ranges.emplace_back(direct->node_base[i] + direct->node_offset[top],
+                              direct->node_base[i] + direct->node_offset[i] + seqlen[i]);
+      } else {
+        s.ranges.emplace_back(kv_ptrs[i], kv_ptrs[i + 1]);
+        for (int up = i; assign[up] == 1;) {
+          up = parent[up];
+          s.ranges.emplace_back(kv_ptrs[up], kv_ptrs[up + 1]);
+        }
+        std::reverse(s.ranges.begin(), s.ranges.end());  // root-most segment first
       }
-      std::reverse(s.ranges.begin(), s.ranges.end());  // root-most segment first
       s.length = 0;
       for (auto& r : s.ranges) s.length += r.second - r.first;
       if (s.length <= 0) continue;
       s.reqs.swap(reqs);
       total_stream += ceil_div((int64_t)s.reqs.size(), q_tile) * s.length * row_bytes;
       specs.push_back(std::move(s));
+    }
+    if (direct != nullptr) {
+      for (int64_t e = 0; e < direct->n_extra; ++e) {
+        const int64_t length = direct->extra_end[e] - direct->extra_begin[e];
+        const int32_t r = direct->extra_req[e];
+        if (r < 0 || r >= batch) {
+          delete plan;
+          return FT_ERR_INVALID_ARGUMENT;
+        }
+        if (length <= 0) continue;
+        Spec s;
+        s.ranges.emplace_back(direct->extra_begin[e], direct->extra_end[e]);
+        s.reqs.push_back(r);
+        s.length = length;
+        total_stream += ceil_div(1, q_tile) * length * row_bytes;
+        specs.push_back(std::move(s));
+      }
     }
     const double slots = (double)(m.num_sms * m.ctas_per_sm) * m.waves;
     const double target = std::max((double)(total_stream * num_kv_heads) / slots, (double)(m.min_chunk * row_bytes));
@@ -183,14 +224,16 @@ int ft_plan_b200_build(const int32_t* parent, const int32_t* seqlen, int32_t n_n
     int64_t kv_total = 0, q_total = 0;
     for (const Spec& s : specs) {
       const int64_t nreq = (int64_t)s.reqs.size();
-      for (auto& r : s.ranges)
-        for (int64_t row = r.first; row < r.second; ++row) plan->kv_entries.push_back((int32_t)row);
+      const int64_t kv_base = direct != nullptr ? s.ranges[0].first : kv_total;
+      if (direct == nullptr)
+        for (auto& r : s.ranges)
+          for (int64_t row = r.first; row < r.second; ++row) plan->kv_entries.push_back((int32_t)row);
       const int64_t n_kv = ceil_div(s.length, s.chunk), n_q = ceil_div(nreq, q_tile);
       for (int64_t c = 0; c < n_kv; ++c) {
         const int64_t c_off = c * s.chunk, c_len = std::min(c_off + s.chunk, s.length) - c_off;
         for (int64_t t = 0; t < n_q; ++t) {
           const int64_t t_off = t * q_tile;
-          kv_offs.push_back(kv_total + c_off);
+          kv_offs.push_back(kv_base + c_off);
           kv_lens.push_back(c_len);
           q_offs.push_back(q_total + c * nreq + t_off);
           q_lens.push_back(std::min(t_off + q_tile, nreq) - t_off);
@@ -207,7 +250,7 @@ int ft_plan_b200_build(const int32_t* parent, const int32_t* seqlen, int32_t n_n
       delete plan;
       return FT_ERR_TOO_LARGE;
     }
-    plan->kv_entries.insert(plan->kv_entries.end(), (size_t)pad, -1);
+    if (direct == nullptr) plan->kv_entries.insert(plan->kv_entries.end(), (size_t)pad, -1);
 
     // request -> partial rows: rows grouped by request id, emission order kept inside a group
     std::vector<int64_t> counts((size_t)batch, 0);
@@ -269,6 +312,33 @@ int ft_plan_b200_build(const int32_t* parent, const int32_t* seqlen, int32_t n_n
   }
   *out = plan;
   return FT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ft_plan_b200_build(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, const int64_t* req_offs,
+                       const int32_t* req_ids, const int64_t* kv_ptrs, int32_t batch, int32_t num_qo_heads,
+                       int32_t num_kv_heads, int32_t head_dim, const ft_b200_model* model, ft_plan** out) {
+  return build_plan(parent, seqlen, n_nodes, req_offs, req_ids, kv_ptrs, nullptr, batch, num_qo_heads, num_kv_heads,
+                    head_dim, model, out);
+}
+
+int ft_plan_b200_build_direct(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, const int64_t* req_offs,
+                              const int32_t* req_ids, const int64_t* node_base, const int64_t* node_offset,
+                              int64_t n_extra, const int64_t* extra_begin, const int64_t* extra_end,
+                              const int32_t* extra_req, int32_t batch, int32_t num_qo_heads, int32_t num_kv_heads,
+                              int32_t head_dim, const ft_b200_model* model, ft_plan** out) {
+  Direct d;
+  d.node_base = node_base;
+  d.node_offset = node_offset;
+  d.n_extra = n_extra;
+  d.extra_begin = extra_begin;
+  d.extra_end = extra_end;
+  d.extra_req = extra_req;
+  return build_plan(parent, seqlen, n_nodes, req_offs, req_ids, nullptr, &d, batch, num_qo_heads, num_kv_heads, head_dim,
+                    model, out);
 }
 
 int ft_plan_get_info(const ft_plan* plan, ft_plan_info* info) {

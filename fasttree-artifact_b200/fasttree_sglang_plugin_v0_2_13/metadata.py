@@ -41,6 +41,7 @@ class FastTreeMetadata:
         self.para_threshs1 = para_threshs1
         self.para_threshs2 = para_threshs2
         self.planner = planner
+        self.native_planner = True      # "b200": the library's native splitter (False: its Python specification)
         self.max_vnodes = max_vnodes
         self.max_vnode_to_q_entries = max_vnode_to_q_entries
         self.max_batch_size = max_batch_size

@@ -194,13 +194,20 @@ def _plan_b200(batch, md, node_to_reqs, covered, order, offsets, parents, req_id
         end = len(req.origin_input_ids) + len(req.output_ids) + 1
         base = stride * int(req_idx[rid])
         extra.append(([(base + covered[rid], base + end)], [rid]))
-    vnodes, _assign, q_tile, small_tile, _target = _planner.b200_virtual_nodes(
-        tree, md.num_qo_heads, md.num_kv_heads, md.head_dim, model, ranges_of, extra=extra)
-    perm = []
-    tabs = _planner.emit_tables(vnodes, len(batch.reqs), small_tile=small_tile, direct_offsets=True,
-                                order_key=_planner.b200_task_order, order_out=perm)
+    if getattr(md, "native_planner", True):
+        # the native splitter of the shared library; the Python branch below is its specification
+        node_base = [stride * int(req_idx[nd.requests[0]]) if nd.requests else 0 for nd in tree]
+        tabs, q_tile, small_tile, tile_tokens = _planner.b200_tables_native_direct(
+            tree, node_base, offsets, [(r[0][0], r[0][1], q[0]) for r, q in extra], len(batch.reqs),
+            md.num_qo_heads, md.num_kv_heads, md.head_dim, model)
+    else:
+        vnodes, _assign, q_tile, small_tile, _target = _planner.b200_virtual_nodes(
+            tree, md.num_qo_heads, md.num_kv_heads, md.head_dim, model, ranges_of, extra=extra)
+        tabs = _planner.emit_tables(vnodes, len(batch.reqs), small_tile=small_tile, direct_offsets=True,
+                                    order_key=_planner.b200_task_order)
+        tile_tokens = model.tile_tokens
     md.phase_q_tile_sizes = [q_tile, small_tile]
-    md.phase_kv_tile_sizes = [model.tile_tokens, model.tile_tokens]
+    md.phase_kv_tile_sizes = [tile_tokens, tile_tokens]
     # the task holding the END of each request's tail (the one that grows during the burst)
     ends = {}
     for rid, req in enumerate(batch.reqs):

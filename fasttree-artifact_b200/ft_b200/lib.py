@@ -22,7 +22,7 @@ FT_DEV_BAD_KV_INDEX, FT_DEV_BAD_Q_INDEX, FT_DEV_BAD_ROW_INDEX, FT_DEV_WAIT_TIMEO
 EXPORTS = ["ft_version", "ft_decode_args_size", "ft_last_error", "ft_decode", "ft_stage1", "ft_stage2",
            "ft_decode_static_scratch", "ft_bump_kv_lens",
            "ft_read_device_status", "ft_launch_count", "ft_stage1_path_name",
-           "ft_plan_b200_build", "ft_plan_get_info", "ft_plan_copy_tables", "ft_plan_free"]
+           "ft_plan_b200_build", "ft_plan_b200_build_direct", "ft_plan_get_info", "ft_plan_copy_tables", "ft_plan_free"]
 
 
 class FastTreeError(RuntimeError):
@@ -128,6 +128,10 @@ def load():
                                            ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(B200ModelStruct),
                                            ctypes.POINTER(ctypes.c_void_p)]
         lib.ft_plan_b200_build.restype = ctypes.c_int
+        lib.ft_plan_b200_build_direct.argtypes = [i32p, i32p, ctypes.c_int32, i64p, i32p, i64p, i64p, ctypes.c_int64, i64p,
+                                                  i64p, i32p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                                  ctypes.POINTER(B200ModelStruct), ctypes.POINTER(ctypes.c_void_p)]
+        lib.ft_plan_b200_build_direct.restype = ctypes.c_int
         lib.ft_plan_get_info.argtypes = [ctypes.c_void_p, ctypes.POINTER(PlanInfo)]
         lib.ft_plan_get_info.restype = ctypes.c_int
         lib.ft_plan_copy_tables.argtypes = [ctypes.c_void_p] + [i32p] * 10

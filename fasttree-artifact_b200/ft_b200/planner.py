@@ -366,15 +366,7 @@ def plan_b200(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, p
                 info={"planner": "b200", "target_bytes": float(target), "vnodes": len(vnodes)}, **tabs)
 
 
-def plan_b200_native(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, params, model=None):
-    """:func:`plan_b200` computed by the native splitter of the shared library
-    (``ft_plan_b200_build``, csrc/ft_planner.cu).  Same arguments, same result -
-    the tests hold the two to identical tables; this one is one to two orders of
-    magnitude faster on large trees.  Node 0 must be the root and parents must
-    precede their children, as in the reference tree format."""
-    import ctypes
-    from . import lib as _lib
-    L = _lib.load()
+def _tree_arrays(tree):
     n = len(tree)
     parent = np.fromiter((nd.parent for nd in tree), dtype=np.int32, count=n)
     seqlen = np.fromiter((nd.seqlen for nd in tree), dtype=np.int32, count=n)
@@ -385,18 +377,17 @@ def plan_b200_native(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head
     for i, nd in enumerate(tree):
         if counts[i]:
             req_ids[req_offs[i]:req_offs[i + 1]] = nd.requests
-    ptrs = np.ascontiguousarray(np.asarray(kv_ptrs, dtype=np.int64))
-    if ptrs.size != n + 1:
-        raise ValueError("kv_ptrs must have one entry more than the tree has nodes")
-    m = b200_model_for(params, head_dim, model)
-    ms = _lib.B200ModelStruct(m.num_sms, m.ctas_per_sm, m.waves, m.tile_tokens, m.rows_per_cta, m.min_chunk,
-                              m.nominal_split, m.ridge_flop_per_byte, m.task_overhead_bytes, m.elem_bytes)
-    i32p, i64p = ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int64)
-    as32 = lambda a: a.ctypes.data_as(i32p)
+    return parent, seqlen, req_offs, req_ids
+
+
+def _native_tables(build, direct):
+    """Run one of the library's plan builders (``build(handle_ref) -> status``) and copy its tables out."""
+    import ctypes
+    from . import lib as _lib
+    L = _lib.load()
+    as32 = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_int32))
     handle = ctypes.c_void_p()
-    _lib.check(L.ft_plan_b200_build(as32(parent), as32(seqlen), n, req_offs.ctypes.data_as(i64p), as32(req_ids),
-                                    ptrs.ctypes.data_as(i64p), batch_size, num_qo_heads, num_kv_heads, head_dim,
-                                    ctypes.byref(ms), ctypes.byref(handle)))
+    _lib.check(build(L, ctypes.byref(handle)))
     try:
         info = _lib.PlanInfo()
         _lib.check(L.ft_plan_get_info(handle, ctypes.byref(info)))
@@ -411,13 +402,69 @@ def plan_b200_native(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head
         _lib.check(L.ft_plan_copy_tables(handle, *(as32(t) for t in tabs.values()), as32(assign)))
     finally:
         L.ft_plan_free(handle)
+    if direct:
+        tabs["vnode_to_kv_entries"] = None
+    tabs["phase_node_nums"] = [int(x) for x in info.phase_node_nums]
+    tabs["phase_node_offsets"] = [int(x) for x in info.phase_node_offsets]
+    return tabs, [int(a) for a in assign], info
+
+
+def _model_struct(m):
+    from . import lib as _lib
+    return _lib.B200ModelStruct(m.num_sms, m.ctas_per_sm, m.waves, m.tile_tokens, m.rows_per_cta, m.min_chunk,
+                                m.nominal_split, m.ridge_flop_per_byte, m.task_overhead_bytes, m.elem_bytes)
+
+
+def plan_b200_native(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, params, model=None):
+    """:func:`plan_b200` computed by the native splitter of the shared library
+    (``ft_plan_b200_build``, csrc/ft_planner.cu).  Same arguments, same result -
+    the tests hold the two to identical tables; this one is one to two orders of
+    magnitude faster on large trees.  Node 0 must be the root and parents must
+    precede their children, as in the reference tree format."""
+    import ctypes
+    parent, seqlen, req_offs, req_ids = _tree_arrays(tree)
+    ptrs = np.ascontiguousarray(np.asarray(kv_ptrs, dtype=np.int64))
+    if ptrs.size != len(tree) + 1:
+        raise ValueError("kv_ptrs must have one entry more than the tree has nodes")
+    ms = _model_struct(b200_model_for(params, head_dim, model))
+    i32p, i64p = ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int64)
+    as32, as64 = (lambda a: a.ctypes.data_as(i32p)), (lambda a: a.ctypes.data_as(i64p))
+    tabs, assign, info = _native_tables(
+        lambda L, out: L.ft_plan_b200_build(as32(parent), as32(seqlen), len(tree), as64(req_offs), as32(req_ids),
+                                            as64(ptrs), batch_size, num_qo_heads, num_kv_heads, head_dim,
+                                            ctypes.byref(ms), out), direct=False)
     params.set_q_tile_sizes([info.q_tile, info.small_tile])
     params.set_kv_tile_sizes([info.tile_tokens, info.tile_tokens])
-    return Plan(node_assignments=[int(a) for a in assign], phase_q_tile_sizes=[info.q_tile, info.small_tile],
+    return Plan(node_assignments=assign, phase_q_tile_sizes=[info.q_tile, info.small_tile],
                 phase_kv_tile_sizes=[info.tile_tokens, info.tile_tokens], kv_split_sizes=[],
                 info={"planner": "b200", "target_bytes": float(info.target_bytes), "vnodes": int(info.virtual_nodes)},
-                phase_node_nums=[int(x) for x in info.phase_node_nums],
-                phase_node_offsets=[int(x) for x in info.phase_node_offsets], **tabs)
+                **tabs)
+
+
+def b200_tables_native_direct(tree, node_base, node_offset, extra, batch_size, num_qo_heads, num_kv_heads, head_dim,
+                              model):
+    """The serving path's tables from the native splitter (``ft_plan_b200_build_direct``): what
+    :func:`b200_virtual_nodes` + :func:`emit_tables` (``direct_offsets=True``, ordered by
+    :func:`b200_task_order`) produce for a tree whose node i covers positions
+    ``[node_base[i] + node_offset[top carried ancestor], node_base[i] + node_offset[i] + seqlen_i)`` of an
+    existing row-id table, plus the ``extra`` pairings ``(begin, end, request)``.
+    Returns (tables dict, request tile, small request tile, tile tokens)."""
+    import ctypes
+    parent, seqlen, req_offs, req_ids = _tree_arrays(tree)
+    base = np.ascontiguousarray(np.asarray(node_base, dtype=np.int64))
+    offs = np.ascontiguousarray(np.asarray(node_offset, dtype=np.int64))
+    ex = np.asarray(extra, dtype=np.int64).reshape(-1, 3)
+    eb, ee = np.ascontiguousarray(ex[:, 0]), np.ascontiguousarray(ex[:, 1])
+    er = np.ascontiguousarray(ex[:, 2].astype(np.int32))
+    ms = _model_struct(model)
+    i32p, i64p = ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int64)
+    as32, as64 = (lambda a: a.ctypes.data_as(i32p)), (lambda a: a.ctypes.data_as(i64p))
+    tabs, _assign, info = _native_tables(
+        lambda L, out: L.ft_plan_b200_build_direct(as32(parent), as32(seqlen), len(tree), as64(req_offs), as32(req_ids),
+                                                   as64(base), as64(offs), int(ex.shape[0]), as64(eb), as64(ee), as32(er),
+                                                   batch_size, num_qo_heads, num_kv_heads, head_dim, ctypes.byref(ms),
+                                                   out), direct=True)
+    return tabs, int(info.q_tile), int(info.small_tile), int(info.tile_tokens)
 
 
 def b200_model_for(params, head_dim, model=None):

@@ -214,6 +214,17 @@ typedef struct ft_plan_info {
 int ft_plan_b200_build(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, const int64_t* req_offs,
                        const int32_t* req_ids, const int64_t* kv_ptrs, int32_t batch, int32_t num_qo_heads,
                        int32_t num_kv_heads, int32_t head_dim, const ft_b200_model* model, ft_plan** out);
+/* The serving path's addressing (fasttree_sglang_plugin_v0_2_13/schedule.py:159-232 of the reference): a node's
+ * KV, together with that of the ancestors it carries, is one run of positions in an existing row-id table (the
+ * flattened req_to_token): [node_base[i] + node_offset[top carried ancestor], node_base[i] + node_offset[i] +
+ * seqlen[i]).  n_extra further pairings of one request with one run (each request's private tail) take part in
+ * the byte budget and are emitted last.  No vnode_to_kv_entries table is built (ft_plan_info.kv_entries = 0);
+ * vnode_to_kv_offs are positions in the existing table; req_to_vnode_entries still gets its 32 trailing -1. */
+int ft_plan_b200_build_direct(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, const int64_t* req_offs,
+                              const int32_t* req_ids, const int64_t* node_base, const int64_t* node_offset,
+                              int64_t n_extra, const int64_t* extra_begin, const int64_t* extra_end,
+                              const int32_t* extra_req, int32_t batch, int32_t num_qo_heads, int32_t num_kv_heads,
+                              int32_t head_dim, const ft_b200_model* model, ft_plan** out);
 int ft_plan_get_info(const ft_plan* plan, ft_plan_info* info);
 int ft_plan_copy_tables(const ft_plan* plan, int32_t* vnode_to_kv_entries, int32_t* vnode_to_kv_offs,
                         int32_t* vnode_to_kv_lens, int32_t* vnode_to_q_entries, int32_t* vnode_to_q_offs,

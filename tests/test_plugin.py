@@ -78,6 +78,29 @@ def test_plans_cover_every_position_once(name, planner, extra):
     check_cover(batch, rows, md, extra)
 
 
+@pytest.mark.parametrize("name", sorted(plugin_cases.CASES))
+@pytest.mark.parametrize("extra", [0, 5])
+def test_native_schedule_matches_the_python_specification(name, extra):
+    """ft_plan_b200_build_direct against b200_virtual_nodes + emit_tables on the same burst."""
+    got = []
+    for native in (True, False):
+        batch, _rows, hq, hkv = plugin_cases.build(name, extra_prompt=extra)
+        md = make_md(hq, hkv, "b200")
+        md.native_planner = native
+        schedule.prepare_for_fasttree_meta(batch, md)
+        nv, rows = md.num_vnodes, md.num_partial_rows
+        got.append(dict(
+            kv_offs=md.vnode_to_kv_offs[:nv].clone(), kv_lens=md.vnode_to_kv_lens[:nv].clone(),
+            q_entries=md.vnode_to_q_entries[:rows].clone(), q_offs=md.vnode_to_q_offs[:nv].clone(),
+            q_lens=md.vnode_to_q_lens[:nv].clone(), r2v=md.req_to_vnode_entries[:rows].clone(),
+            r2v_offs=md.req_to_vnode_offs[:len(batch.reqs)].clone(), r2v_lens=md.req_to_vnode_lens[:len(batch.reqs)].clone(),
+            nums=list(md.phase_node_nums), offs=list(md.phase_node_offsets), last=list(md.req_last_vnodes),
+            tiles=(list(md.phase_q_tile_sizes), list(md.phase_kv_tile_sizes))))
+    for k in got[0]:
+        a, b = got[0][k], got[1][k]
+        assert torch.equal(a, b) if torch.is_tensor(a) else a == b, k
+
+
 def test_b200_plan_is_deterministic():
     tabs = []
     for _ in range(2):
