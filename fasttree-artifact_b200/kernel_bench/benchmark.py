@@ -9,9 +9,11 @@ cleared before every repetition, median reported - implemented here with CUDA
 events so that Triton is not needed.  ``--choice flash_attn`` / ``all`` also time
 flash-attn's ``flash_attn_with_kvcache`` on the padded per-request cache when the
 flash_attn package is importable (the reference's yard-stick,
-flash_attn_wrap.py:82-86) and print the reference's allclose(1e-2) check; the
-other baselines of the reference (SGLang Triton, FlashInfer, DeFT) are not part
-of this build and are reported as skipped.
+flash_attn_wrap.py:82-86) and print the reference's allclose(1e-2) check, and
+``--choice sglang_flashinfer`` / ``all`` FlashInfer's paged batch decode over the
+tree rows when flashinfer is importable (flashinfer_wrap.py); the reference's
+SGLang-Triton and DeFT baselines are not part of this build and are reported
+as skipped.
 """
 import argparse
 import ctypes
@@ -117,13 +119,26 @@ def main(args):
 
         out_tree = run_and_bench(call_tree_attn, "fasttree attn").cpu()
 
-    for name in ("sglang_triton", "sglang_flashinfer", "DeFT"):
+    out_fi = None
+    if args.choice in ("sglang_flashinfer", "all"):
+        try:
+            from flashinfer_wrap import flashinfer_preparation, flashinfer_decode
+            wrapper = flashinfer_preparation(tree_info, KV_ptrs, batch_size, args.num_qo_heads, args.num_kv_heads,
+                                             args.head_dim, dtype)
+            out_fi = run_and_bench(lambda: flashinfer_decode(wrapper, Q, K_tree, V_tree), "sglang flashinfer").cpu()
+        except Exception as exc:          # optional baseline: not installed, or no kernel for this GPU / shape
+            print(f"sglang_flashinfer skipped ({type(exc).__name__}: {str(exc)[:120]})")
+
+    for name in ("sglang_triton", "DeFT"):
         if args.choice in (name, "all"):
             print(f"{name} skipped (baseline kernels are not part of this build)")
 
     if out_flash is not None and out_tree is not None:
         ok = torch.allclose(out_flash, out_tree, rtol=1e-2, atol=1e-2)
         print("fasttree attn Check passed!" if ok else "fasttree attn Check failed!")
+    if out_fi is not None and out_tree is not None:
+        ok = torch.allclose(out_fi, out_tree, rtol=1e-2, atol=1e-2)
+        print("fasttree vs flashinfer Check passed!" if ok else "fasttree vs flashinfer Check failed!")
 
 
 if __name__ == "__main__":
