@@ -233,10 +233,10 @@ EncodeTiledFn encode_tiled_fn() {
 struct MapKey {
   const void* base;
   int64_t rows, s0, s1;
-  int heads, dtype, box_heads;
+  int heads, dtype, box_heads, device;
   bool operator==(const MapKey& o) const {
     return base == o.base && rows == o.rows && s0 == o.s0 && s1 == o.s1 && heads == o.heads && dtype == o.dtype &&
-           box_heads == o.box_heads;
+           box_heads == o.box_heads && device == o.device;
   }
 };
 
@@ -249,7 +249,9 @@ bool tensor_map_3d(CUtensorMap* out, const void* base, int dtype, int head_dim, 
   static MapKey keys[SLOTS];
   static CUtensorMap maps[SLOTS];
   static int used = 0, next = 0;
-  const MapKey key{base, rows, s0, s1, heads, dtype + 16 * head_dim, box_heads * 1024 + box_rows};
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess) return false;  // the same address can name different memory on two devices
+  const MapKey key{base, rows, s0, s1, heads, dtype + 16 * head_dim, box_heads * 1024 + box_rows, device};
   std::lock_guard<std::mutex> lock(mu);
   for (int i = 0; i < used; ++i)
     if (keys[i] == key) {
