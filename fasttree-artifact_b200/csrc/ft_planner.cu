@@ -116,20 +116,48 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
     std::vector<int64_t> run_len(seqlen, seqlen + n);
     std::vector<int32_t>& assign = plan->assignments;
     assign.assign(n, 0);
+    // Per parent three candidates - the greedy walk over its children in id order, no child carrying, every child
+    // carrying (the only one that removes the parent's own tasks) - and the cheapest wins (ties: greedy, then none).
     std::deque<int> frontier{0};
+    std::vector<int> greedy;
     while (!frontier.empty()) {
       const int v = frontier.front();
       frontier.pop_front();
-      int64_t n_here = n_req(v);
+      if (kids[v].empty()) continue;
+      const int64_t n_v = n_req(v), len_v = run_len[v];
+      int64_t n_here = n_v;
+      double greedy_cost = 0.0;
+      greedy.clear();
       for (int c : kids[v]) {
         const int64_t n_c = n_req(c);
-        const double own = task_cost(n_here, run_len[v], group, head_dim, m) + task_cost(n_c, run_len[c], group, head_dim, m);
-        const double carried = task_cost(n_here - n_c, run_len[v], group, head_dim, m) +
-                               task_cost(n_c, run_len[c] + run_len[v], group, head_dim, m);
-        if (carried < own) {
+        const double own = task_cost(n_here, len_v, group, head_dim, m) + task_cost(n_c, run_len[c], group, head_dim, m);
+        const double carried = task_cost(n_here - n_c, len_v, group, head_dim, m) +
+                               task_cost(n_c, run_len[c] + len_v, group, head_dim, m);
+        const bool take = carried < own;
+        greedy.push_back(take ? 1 : 0);
+        if (take) n_here -= n_c;
+        greedy_cost += task_cost(n_c, run_len[c] + (take ? len_v : 0), group, head_dim, m);
+      }
+      greedy_cost += task_cost(n_here, len_v, group, head_dim, m);
+      double none_cost = task_cost(n_v, len_v, group, head_dim, m), all_cost = 0.0;
+      int64_t n_left = n_v;
+      for (int c : kids[v]) {
+        const int64_t n_c = n_req(c);
+        none_cost += task_cost(n_c, run_len[c], group, head_dim, m);
+        all_cost += task_cost(n_c, run_len[c] + len_v, group, head_dim, m);
+        n_left -= n_c;
+      }
+      all_cost += task_cost(n_left, len_v, group, head_dim, m);  // requests that end at v itself keep its vnode
+      int mode = 0;  // 0 greedy, 1 none, 2 all
+      double best = greedy_cost;
+      if (none_cost < best) mode = 1, best = none_cost;
+      if (all_cost < best) mode = 2, best = all_cost;
+      for (size_t k = 0; k < kids[v].size(); ++k) {
+        const int c = kids[v][k];
+        const bool take = mode == 2 || (mode == 0 && greedy[k] == 1);
+        if (take) {
           assign[c] = 1;
-          n_here -= n_c;
-          run_len[c] += run_len[v];
+          run_len[c] += len_v;
         }
         frontier.push_back(c);
       }

@@ -316,27 +316,54 @@ def _task_cost(n_req, length, group, head_dim, m):
 
 
 def b200_edge_assignments(tree, group, head_dim, m):
-    """Same greedy walk as the reference heuristic (breadth first, children in id
-    order, the parent's remaining request count shrinking as children carry its
-    KV away) but on a cost model that charges what a B200 pays for: re-reading the
-    parent's KV for the carrying child, partial-row traffic, and per-CTA overhead."""
+    """Which children take their parent's accumulated KV along (1) and which keep a
+    vnode of their own (0).  Breadth first, one parent at a time, on a cost model
+    that charges what a B200 pays for: re-reading the parent's KV for a carrying
+    child, partial-row traffic, and per-CTA overhead.  Three candidates per
+    parent: the reference's greedy walk over the children in id order (the
+    parent's remaining request count shrinking as children carry its KV away),
+    no child carrying, and every child carrying - which is the only one that
+    removes the parent's own tasks, something the edge-by-edge walk cannot see
+    before its last child.  The cheapest wins (ties: greedy, then none)."""
     kids = _children(tree)
     run_len = [nd.seqlen for nd in tree]
     assign = [0] * len(tree)
     frontier = deque((0,))
     while frontier:
         v = frontier.popleft()
-        n_here = len(tree[v].requests)
-        for c in kids[v]:
-            n_c = len(tree[c].requests)
-            own = _task_cost(n_here, run_len[v], group, head_dim, m) + _task_cost(n_c, run_len[c], group, head_dim, m)
-            carried = (_task_cost(n_here - n_c, run_len[v], group, head_dim, m)
-                       + _task_cost(n_c, run_len[c] + run_len[v], group, head_dim, m))
-            if carried < own:
-                assign[c] = 1
-                n_here -= n_c
-                run_len[c] += run_len[v]
-            frontier.append(c)
+        n_v, len_v = len(tree[v].requests), run_len[v]
+        if kids[v]:
+            n_here, greedy, greedy_cost = n_v, [], 0.0
+            for c in kids[v]:
+                n_c = len(tree[c].requests)
+                own = _task_cost(n_here, len_v, group, head_dim, m) + _task_cost(n_c, run_len[c], group, head_dim, m)
+                carried = (_task_cost(n_here - n_c, len_v, group, head_dim, m)
+                           + _task_cost(n_c, run_len[c] + len_v, group, head_dim, m))
+                take = carried < own
+                greedy.append(1 if take else 0)
+                if take:
+                    n_here -= n_c
+                greedy_cost += _task_cost(n_c, run_len[c] + (len_v if take else 0), group, head_dim, m)
+            greedy_cost += _task_cost(n_here, len_v, group, head_dim, m)
+            none_cost = _task_cost(n_v, len_v, group, head_dim, m)
+            all_cost, n_left = 0.0, n_v
+            for c in kids[v]:
+                n_c = len(tree[c].requests)
+                none_cost += _task_cost(n_c, run_len[c], group, head_dim, m)
+                all_cost += _task_cost(n_c, run_len[c] + len_v, group, head_dim, m)
+                n_left -= n_c
+            all_cost += _task_cost(n_left, len_v, group, head_dim, m)   # requests that end at v itself keep its vnode
+            choice = greedy
+            best = greedy_cost
+            if none_cost < best:
+                choice, best = [0] * len(kids[v]), none_cost
+            if all_cost < best:
+                choice, best = [1] * len(kids[v]), all_cost
+            for c, take in zip(kids[v], choice):
+                if take:
+                    assign[c] = 1
+                    run_len[c] += len_v
+                frontier.append(c)
     return assign
 
 
