@@ -233,6 +233,9 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
       const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)kvh * p.v_s1 + ld_c * 8;
       const int* ring = ids_ptr + rs * C::TILE + ld_r;
       const int pos0 = t * C::TILE + ld_r;
+      // Only the 16-token blocks that hold tokens of the chunk are filled (zeros after the last token): a warp
+      // whose block lies past the end of the chunk skips the tile altogether, so nothing reads the other rows.
+      const int fill = min(C::TILE, (max(kv_len - t * C::TILE, 0) + 15) & ~15);
       uint32_t row[C::PASSES];
 #pragma unroll
       for (int ps = 0; ps < C::PASSES; ++ps)
@@ -241,11 +244,13 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
 #pragma unroll
       for (int ps = 0; ps < C::PASSES; ++ps) {
         const int r = ps * C::TPP + ld_r;
-        const bool ok = row[ps] < row_lim;
-        bad |= !ok && pos0 + ps * C::TPP < lim;
-        const int64_t off = (int64_t)(ok ? row[ps] : 0u);
-        cp_async16(k_sm + C::swz(r, ld_c), kbase + off * p.k_s0, ok);
-        cp_async16(v_sm + C::swz(r, ld_c), vbase + off * p.v_s0, ok);
+        if (r < fill) {
+          const bool ok = row[ps] < row_lim;
+          bad |= !ok && pos0 + ps * C::TPP < lim;
+          const int64_t off = (int64_t)(ok ? row[ps] : 0u);
+          cp_async16(k_sm + C::swz(r, ld_c), kbase + off * p.k_s0, ok);
+          cp_async16(v_sm + C::swz(r, ld_c), vbase + off * p.v_s0, ok);
+        }
       }
       if (bad) flag_error(FT_DEV_BAD_KV_INDEX);
     }
@@ -279,10 +284,14 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
     // one arrival per thread: at once when this thread copied nothing for the slot (a TMA tile that is not the
     // task's first: the transaction bytes alone gate the barrier), else once all its copies so far (gathered rows,
     // Q rows) have landed
+#ifdef FT_EXPERIMENT_PLAIN_ARRIVE  // timing experiment only: results are wrong
+    mbar_arrive(full);
+#else
     if (first_row >= 0 && t != 0)
       mbar_arrive(full);
     else
       mbar_arrive_on_cp_async(full);
+#endif
   };
 
   // ---- pipeline state, identical in every thread
@@ -411,10 +420,12 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
         }
       }
       const uint32_t k_sm = pipe_sm + stage * 2 * C::STAGE_BYTES, v_sm = k_sm + C::STAGE_BYTES;
-      if (c_rows <= 8)
-        stream_tile<T, D, 1>(k_sm, v_sm, tok0, dl7 * C::TILE, c_kvlen, scale2, qb, o_acc, m_run, l_run, lane);
-      else
-        stream_tile<T, D, 2>(k_sm, v_sm, tok0, dl7 * C::TILE, c_kvlen, scale2, qb, o_acc, m_run, l_run, lane);
+      if (dl7 * C::TILE + tok0 < c_kvlen) {  // else: this warp's 16 tokens are all past the end of the chunk
+        if (c_rows <= 8)
+          stream_tile<T, D, 1>(k_sm, v_sm, tok0, dl7 * C::TILE, c_kvlen, scale2, qb, o_acc, m_run, l_run, lane);
+        else
+          stream_tile<T, D, 2>(k_sm, v_sm, tok0, dl7 * C::TILE, c_kvlen, scale2, qb, o_acc, m_run, l_run, lane);
+      }
 
 #ifdef FT_TIMELINE
       { const long long c = clock64(); tl_sum_tile += c - tl_c0; tl_c0 = c; }
@@ -436,6 +447,7 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
             const int r = nq * 8 + 2 * t4;
             float* dst = epi_o + (warp * 16 + r) * D;
             const int sw = t4 << 3;  // rows are D floats apart: rotate the columns by the row pair to spread the banks
+            if (tok0 < c_kvlen || c_tiles > 1)  // a warp that saw no token stages no output (its maximum stays -inf)
 #pragma unroll
             for (int mb = 0; mb < D / 16; ++mb) {
               dst[(mb * 16 + g8) ^ sw] = o_acc[mb][nq][0];
@@ -468,7 +480,8 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
 #pragma unroll
               for (int w = 0; w < 4; ++w) {
                 const float mw = epi_m[w * 16 + r];
-                const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - M);
+                if (mw == -INFINITY) continue;  // that warp saw no valid token for this row and staged nothing
+                const float f = fast_exp2(mw - M);
                 L = fmaf(epi_l[w * 16 + r], f, L);
                 const float4* src = reinterpret_cast<const float4*>(epi_o + (w * 16 + r) * D);
 #pragma unroll
