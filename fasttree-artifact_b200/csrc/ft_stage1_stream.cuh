@@ -284,14 +284,10 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
     // one arrival per thread: at once when this thread copied nothing for the slot (a TMA tile that is not the
     // task's first: the transaction bytes alone gate the barrier), else once all its copies so far (gathered rows,
     // Q rows) have landed
-#ifdef FT_EXPERIMENT_PLAIN_ARRIVE  // timing experiment only: results are wrong
-    mbar_arrive(full);
-#else
     if (first_row >= 0 && t != 0)
       mbar_arrive(full);
     else
       mbar_arrive_on_cp_async(full);
-#endif
   };
 
   // ---- pipeline state, identical in every thread
