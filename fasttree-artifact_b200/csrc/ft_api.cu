@@ -117,6 +117,7 @@ ft::Stage1Params stage1_params(const ft_decode_args* a) {
   p.q_entries = a->vnode_to_q_entries;
   p.q_offs = a->vnode_to_q_offs;
   p.q_lens = a->vnode_to_q_lens;
+  p.q_ranges = a->vnode_q_kv_ranges;
   p.mid_o = a->mid_o;
   p.mid_lse = a->mid_lse;
   p.q_s0 = a->q_stride0;

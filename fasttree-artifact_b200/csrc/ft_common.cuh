@@ -58,6 +58,7 @@ struct Stage1Params {
   const int32_t* q_entries;
   const int32_t* q_offs;
   const int32_t* q_lens;
+  const int32_t* q_ranges;  // optional [num_partial_rows][2]: the chunk tokens [begin, end) a partial row attends to
   float* mid_o;
   float* mid_lse;
   int64_t q_s0, q_s1, k_s0, k_s1, v_s0, v_s1, mo_s0, mo_s1, ml_s0;

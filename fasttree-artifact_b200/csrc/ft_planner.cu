@@ -29,6 +29,7 @@ struct Model {
   int tile_tokens = 64, rows_per_cta = 64, min_chunk = 128, nominal_split = 512;
   double ridge_flop_per_byte = 90.0;
   int task_overhead_bytes = 16384, elem_bytes = 2;
+  int group_member_tokens = 128, group_min_members = 6;
 };
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
@@ -49,6 +50,7 @@ double task_cost(int64_t n_req, int64_t length, int group, int head_dim, const M
 struct ft_plan {
   std::vector<int32_t> kv_entries, kv_offs, kv_lens, q_entries, q_offs, q_lens, r2v_entries, r2v_offs, r2v_lens;
   std::vector<int32_t> assignments;
+  std::vector<int32_t> q_ranges;  // [partial rows][2] when the plan holds groups of short nodes, else empty
   ft_plan_info info;
 };
 
@@ -94,6 +96,9 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
     m.ridge_flop_per_byte = model->ridge_flop_per_byte;
     m.task_overhead_bytes = model->task_overhead_bytes;
     m.elem_bytes = model->elem_bytes;
+    m.group_member_tokens = model->group_member_tokens;
+    m.group_min_members = model->group_min_members;
+    if (m.group_member_tokens < 0 || m.group_min_members < 0) return FT_ERR_INVALID_ARGUMENT;
     if (m.num_sms <= 0 || m.ctas_per_sm <= 0 || !(m.waves > 0) || m.tile_tokens <= 0 || m.rows_per_cta <= 0 ||
         m.min_chunk <= 0 || m.nominal_split <= 0 || !(m.ridge_flop_per_byte > 0) || m.elem_bytes <= 0)
       return FT_ERR_INVALID_ARGUMENT;
@@ -169,6 +174,7 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
       std::vector<int32_t> reqs;
       int64_t length;
       int64_t chunk;
+      std::vector<std::pair<int32_t, int32_t>> row_ranges;  // group of short nodes: per request, its tokens of the chunk
     };
     std::vector<Spec> specs;
     const int64_t row_bytes = 2LL * head_dim * m.elem_bytes;
@@ -247,6 +253,62 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
       s.chunk = ceil_div(ceil_div(s.length, n_chunks), m.tile_tokens) * m.tile_tokens;
     }
 
+    // ---- groups of short nodes (table-building mode, head_dim 128, 16-bit elements: the shape whose kernels honour
+    // per-row token ranges).  Candidates - at most small_tile requests, at most group_member_tokens tokens - are
+    // taken in order; a group is closed when the next candidate would exceed q_tile requests or the token cap (the
+    // per-task target, between 4 and 16 tiles) or shares a request with it; groups with fewer than
+    // group_min_members members, or not more requests than small_tile, are dissolved.  Result: the other virtual
+    // nodes in their order, then groups and dissolved candidates in the order they were closed.
+    bool any_groups = false;
+    if (direct == nullptr && head_dim == 128 && m.elem_bytes == 2 && m.group_member_tokens > 0) {
+      const int64_t tile = m.tile_tokens;
+      const int64_t target_tokens = (int64_t)std::floor(target / (double)row_bytes);
+      const int64_t cap = std::min(std::max(target_tokens / tile * tile, 4 * tile), 16 * tile);
+      std::vector<Spec> kept, tail;
+      std::vector<Spec> cur;
+      std::vector<uint8_t> in_group((size_t)std::max(batch, 1), 0);
+      int64_t cur_tokens = 0, cur_n = 0;
+      auto close = [&]() {
+        for (const Spec& c : cur)
+          for (int32_t r : c.reqs) in_group[r] = 0;
+        if ((int64_t)cur.size() >= m.group_min_members && cur_n > small_tile) {
+          Spec g;
+          int64_t start = 0;
+          for (Spec& c : cur) {
+            g.ranges.insert(g.ranges.end(), c.ranges.begin(), c.ranges.end());
+            g.reqs.insert(g.reqs.end(), c.reqs.begin(), c.reqs.end());
+            g.row_ranges.insert(g.row_ranges.end(), c.reqs.size(), std::make_pair((int32_t)start, (int32_t)(start + c.length)));
+            start += c.length;
+          }
+          g.length = start;
+          g.chunk = ceil_div(start, tile) * tile;
+          tail.push_back(std::move(g));
+          any_groups = true;
+        } else {
+          for (Spec& c : cur) tail.push_back(std::move(c));
+        }
+        cur.clear();
+        cur_tokens = cur_n = 0;
+      };
+      for (Spec& s : specs) {
+        const int64_t nreq = (int64_t)s.reqs.size();
+        if (nreq <= small_tile && s.length <= m.group_member_tokens) {
+          bool shared = false;
+          for (int32_t r : s.reqs) shared = shared || in_group[r] != 0;
+          if (!cur.empty() && (cur_n + nreq > q_tile || cur_tokens + s.length > cap || shared)) close();
+          for (int32_t r : s.reqs) in_group[r] = 1;
+          cur_tokens += s.length;
+          cur_n += nreq;
+          cur.push_back(std::move(s));
+        } else {
+          kept.push_back(std::move(s));
+        }
+      }
+      close();
+      specs.swap(kept);
+      for (Spec& t : tail) specs.push_back(std::move(t));
+    }
+
     // ---- emission: chunk-major, request-tile-minor; every chunk repeats the node's request list
     std::vector<int64_t> kv_offs, kv_lens, q_offs, q_lens;
     int64_t kv_total = 0, q_total = 0;
@@ -267,6 +329,12 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
           q_lens.push_back(std::min(t_off + q_tile, nreq) - t_off);
         }
         plan->q_entries.insert(plan->q_entries.end(), s.reqs.begin(), s.reqs.end());
+        if (any_groups) {
+          for (int64_t r = 0; r < nreq; ++r) {
+            plan->q_ranges.push_back(s.row_ranges.empty() ? 0 : s.row_ranges[(size_t)r].first);
+            plan->q_ranges.push_back(s.row_ranges.empty() ? (int32_t)c_len : s.row_ranges[(size_t)r].second);
+          }
+        }
       }
       kv_total += s.length;
       q_total += n_kv * nreq;
@@ -332,6 +400,7 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
     info.q_tile = q_tile;
     info.small_tile = small_tile;
     info.tile_tokens = m.tile_tokens;
+    info.has_row_ranges = any_groups ? 1 : 0;
     info.target_bytes = target;
     info.virtual_nodes = (int64_t)specs.size();
   } catch (const std::bad_alloc&) {
@@ -393,6 +462,12 @@ int ft_plan_copy_tables(const ft_plan* plan, int32_t* kv_entries, int32_t* kv_of
   put(r2v_offs, plan->r2v_offs);
   put(r2v_lens, plan->r2v_lens);
   put(node_assignments, plan->assignments);
+  return FT_OK;
+}
+
+int ft_plan_copy_row_ranges(const ft_plan* plan, int32_t* q_kv_ranges) {
+  if (plan == nullptr || q_kv_ranges == nullptr || plan->q_ranges.empty()) return FT_ERR_INVALID_ARGUMENT;
+  std::memcpy(q_kv_ranges, plan->q_ranges.data(), plan->q_ranges.size() * sizeof(int32_t));
   return FT_OK;
 }
 

@@ -50,15 +50,21 @@ __global__ void __launch_bounds__(128) stage1_generic_kernel(Stage1Params p) {
       acc[j] = 0.f;
     }
     float m = -INFINITY, l = 0.f;
-    for (int t0 = 0; t0 < kv_len; t0 += TB) {
+    // the chunk tokens [r_lo, r_hi) this row attends to: the whole chunk unless the plan narrows it
+    int r_lo = 0, r_hi = kv_len;
+    if (p.q_ranges != nullptr) {
+      r_lo = max(p.q_ranges[2 * prow], 0);
+      r_hi = min(p.q_ranges[2 * prow + 1], kv_len);
+    }
+    for (int t0 = r_lo; t0 < r_hi; t0 += TB) {
       int rowid[TB];
       float s[TB];
-#pragma unroll
       bool bad = false;  // flagged once after the loads: an atomic between them would serialise them
+#pragma unroll
       for (int u = 0; u < TB; ++u) {
         const int64_t e = (int64_t)kv_off + t0 + u;
         int64_t idx = -1;
-        if (t0 + u < kv_len) {
+        if (t0 + u < r_hi) {
           if (e >= 0 && e < p.kv_entries_len) idx = p.kv_entries[e];
           if (idx < 0 || idx >= p.kv_rows) {
             bad = true;

@@ -243,7 +243,7 @@ struct KvPipe {
 // One 64-token tile for one warp: NB = 8-token blocks this warp owns (2, 4 or 8).
 template <typename T, int D, int NB>
 __device__ __forceinline__ void mma_tile(const uint32_t k_sm, const uint32_t v_sm, const int tok0,
-                                         const int first_pos, const int kv_len, const bool masked,
+                                         const int first_pos, const int (&lo)[2], const int (&hi)[2],
                                          const float scale2, const uint32_t (&qf)[D / 16][4],
                                          float (&o_acc)[D / 8][4], float (&m_run)[2], float (&l_run)[2],
                                          const int lane) {
@@ -265,7 +265,9 @@ __device__ __forceinline__ void mma_tile(const uint32_t k_sm, const uint32_t v_s
     }
   }
 
-  // scale (log2 domain), mask the tail of the chunk
+  // scale (log2 domain); mask the tokens outside [lo, hi) of this thread's two rows (row g8: elements 0-1,
+  // row g8+8: elements 2-3) - the tail of the chunk, or what a row of a group of short nodes does not attend to
+  const bool masked = first_pos < max(lo[0], lo[1]) || first_pos + NB * 8 > min(hi[0], hi[1]);
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
@@ -273,7 +275,7 @@ __device__ __forceinline__ void mma_tile(const uint32_t k_sm, const uint32_t v_s
       float x = s[nb][e] * scale2;
       if (masked) {
         const int pos = first_pos + nb * 8 + 2 * t4 + (e & 1);
-        if (pos >= kv_len) x = -INFINITY;
+        if (pos < lo[e >> 1] || pos >= hi[e >> 1]) x = -INFINITY;
       }
       s[nb][e] = x;
     }
@@ -401,6 +403,19 @@ __global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
     for (int nd = 0; nd < D / 8; ++nd) o_acc[nd][0] = o_acc[nd][1] = o_acc[nd][2] = o_acc[nd][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     uint32_t qf[D / 16][4];
+    // chunk tokens [lo, hi) this thread's two rows attend to: the whole chunk unless the plan narrows it
+    int lo[2] = {0, 0}, hi[2] = {kv_len, kv_len};
+    if (p.q_ranges != nullptr && active) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int prow = row0 + my_rb * 16 + (lane >> 2) + 8 * h;
+        const int64_t part = (int64_t)q_off + prow / G;
+        if (prow < rows && part >= 0 && part < p.num_partial_rows) {
+          lo[h] = max(p.q_ranges[2 * part], 0);
+          hi[h] = min(p.q_ranges[2 * part + 1], kv_len);
+        }
+      }
+    }
 
     for (int j = 0; j < ntiles; ++j) {
       pipe.advance(j);  // tile j has landed for every thread; tile j-1's stage is being refilled
@@ -411,17 +426,14 @@ __global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
       }
       if (active) {
         const uint32_t k_sm = pipe.k_stage(j), v_sm = pipe.v_stage(j);
-        const bool masked = (j + 1) * C::TILE > kv_len;
         if (ways == 4) {
           const int tok0 = my_way * 16;
-          mma_tile<T, D, 2>(k_sm, v_sm, tok0, j * C::TILE + tok0, kv_len, masked, scale2, qf, o_acc, m_run, l_run,
-                            lane);
+          mma_tile<T, D, 2>(k_sm, v_sm, tok0, j * C::TILE + tok0, lo, hi, scale2, qf, o_acc, m_run, l_run, lane);
         } else if (ways == 2) {
           const int tok0 = my_way * 32;
-          mma_tile<T, D, 4>(k_sm, v_sm, tok0, j * C::TILE + tok0, kv_len, masked, scale2, qf, o_acc, m_run, l_run,
-                            lane);
+          mma_tile<T, D, 4>(k_sm, v_sm, tok0, j * C::TILE + tok0, lo, hi, scale2, qf, o_acc, m_run, l_run, lane);
         } else {
-          mma_tile<T, D, 8>(k_sm, v_sm, 0, j * C::TILE, kv_len, masked, scale2, qf, o_acc, m_run, l_run, lane);
+          mma_tile<T, D, 8>(k_sm, v_sm, 0, j * C::TILE, lo, hi, scale2, qf, o_acc, m_run, l_run, lane);
         }
       }
     }

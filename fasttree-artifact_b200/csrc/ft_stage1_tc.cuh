@@ -267,6 +267,15 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
         // ================================================================ softmax (one query row per thread)
         const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32-lane quadrant
         float m_used = -INFINITY, l_run = 0.f;
+        // the chunk tokens [r_lo, r_hi) this thread's row attends to: the whole chunk unless the plan narrows it
+        int r_lo = 0, r_hi = kv_len;
+        if (p.q_ranges != nullptr && row0 + tid < rows) {
+          const int64_t part = (int64_t)q_off + (row0 + tid) / G;
+          if (part >= 0 && part < p.num_partial_rows) {
+            r_lo = max(p.q_ranges[2 * part], 0);
+            r_hi = min(p.q_ranges[2 * part + 1], kv_len);
+          }
+        }
         for (int j = 0; j < ntiles && !dead; ++j) {
           const int g = g0 + j, b = g & 1;
           if (!tc_wait(bar(C::S_FULL + b), (uint32_t)(g >> 1) & 1u, abort_flag)) {
@@ -282,11 +291,12 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           tmem_ld32(s_col + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
           tc_fence_before();
           mbar_arrive(bar(C::S_EMPTY + b));  // the scores are in registers: the buffer may take tile j+2
-          const int valid = kv_len - j * C::TILE;  // columns >= valid are padding (last tile only)
-          if (valid < C::TILE) {
+          // columns outside [lo, hi) are padding (last tile) or tokens this row does not attend to
+          const int lo = r_lo - j * C::TILE, hi = r_hi - j * C::TILE;
+          if (lo > 0 || hi < C::TILE) {
 #pragma unroll
             for (int c = 0; c < 64; ++c)
-              if (c >= valid) s[c] = -INFINITY;
+              if (c < lo || c >= hi) s[c] = -INFINITY;
           }
           float mx = fmaxf(s[0], s[1]);
 #pragma unroll

@@ -41,6 +41,19 @@ def _pair(name, x):
     return int(x[0]), int(x[1])
 
 
+def attach_row_ranges(vnode_to_q_entries, ranges):
+    """The B200 plan format's optional tenth table - per partial row the tokens
+    ``[begin, end)`` of its vnode's KV chunk that the row attends to (int32
+    ``[rows, 2]``) - has no slot in the reference's 13-entry tuple, so it rides on
+    the ``vnode_to_q_entries`` tensor object it is parallel to."""
+    vnode_to_q_entries.ft_row_ranges = ranges
+    return vnode_to_q_entries
+
+
+def row_ranges_of(vnode_to_q_entries):
+    return getattr(vnode_to_q_entries, "ft_row_ranges", None)
+
+
 def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, vnode_to_kv_lens,
                vnode_to_q_entries, vnode_to_q_offs, vnode_to_q_lens, req_to_vnode_entries,
                req_to_vnode_offs, req_to_vnode_lens, mid_o, mid_lse, phase_node_nums, phase_node_offsets,
@@ -95,7 +108,14 @@ def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, 
     if path not in _lib.PATHS:
         raise ValueError(f"path must be one of {sorted(_lib.PATHS)}")
 
+    ranges = row_ranges_of(vnode_to_q_entries)
+    if ranges is not None:
+        _table("row ranges", ranges)
+        if ranges.numel() < 2 * vnode_to_q_entries.numel():
+            raise ValueError("the row-range table needs two entries per partial row")
+
     a = _lib.DecodeArgs()
+    a.vnode_q_kv_ranges = ranges.data_ptr() if ranges is not None else None
     a.q, a.k_buffer, a.v_buffer, a.o = q.data_ptr(), k_buffer.data_ptr(), v_buffer.data_ptr(), o.data_ptr()
     a.o_lse = o_lse.data_ptr() if o_lse is not None else None
     a.dtype = _DTYPES[q.dtype]
@@ -137,7 +157,7 @@ def _cached_args(tensors, rest, path, o_lse):
     stream = torch.cuda.current_stream(q.device).cuda_stream
     (pn, po, pq, pk, sm_scale, logit_cap) = rest
     key = (tuple(map(id, tensors)), pn[0], pn[1], po[0], po[1], pq[0], pq[1], pk[0], pk[1], sm_scale, logit_cap,
-           path, id(o_lse), stream)
+           path, id(o_lse), stream, id(row_ranges_of(tensors[7])))
     ptrs = tuple([t.data_ptr() for t in tensors])
     hit = _ARG_CACHE.get(key)
     if hit is not None and hit[1] == ptrs:
@@ -145,7 +165,7 @@ def _cached_args(tensors, rest, path, o_lse):
     a = build_args(*tensors, pn, po, pq, pk, sm_scale, logit_cap, path=path, o_lse=o_lse, stream=stream)
     if len(_ARG_CACHE) >= _ARG_CACHE_MAX:
         _ARG_CACHE.clear()
-    _ARG_CACHE[key] = (a, ptrs, tensors, o_lse)
+    _ARG_CACHE[key] = (a, ptrs, tensors, o_lse, row_ranges_of(tensors[7]))
     return a
 
 

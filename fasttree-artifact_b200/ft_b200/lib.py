@@ -22,7 +22,8 @@ FT_DEV_BAD_KV_INDEX, FT_DEV_BAD_Q_INDEX, FT_DEV_BAD_ROW_INDEX, FT_DEV_WAIT_TIMEO
 EXPORTS = ["ft_version", "ft_decode_args_size", "ft_last_error", "ft_decode", "ft_stage1", "ft_stage2",
            "ft_decode_static_scratch", "ft_bump_kv_lens",
            "ft_read_device_status", "ft_launch_count", "ft_stage1_path_name",
-           "ft_plan_b200_build", "ft_plan_b200_build_direct", "ft_plan_get_info", "ft_plan_copy_tables", "ft_plan_free"]
+           "ft_plan_b200_build", "ft_plan_b200_build_direct", "ft_plan_get_info", "ft_plan_copy_tables", "ft_plan_copy_row_ranges",
+           "ft_plan_free"]
 
 
 class FastTreeError(RuntimeError):
@@ -38,7 +39,8 @@ class B200ModelStruct(ctypes.Structure):
     _fields_ = [("num_sms", ctypes.c_int32), ("ctas_per_sm", ctypes.c_int32), ("waves", ctypes.c_double),
                 ("tile_tokens", ctypes.c_int32), ("rows_per_cta", ctypes.c_int32), ("min_chunk", ctypes.c_int32),
                 ("nominal_split", ctypes.c_int32), ("ridge_flop_per_byte", ctypes.c_double),
-                ("task_overhead_bytes", ctypes.c_int32), ("elem_bytes", ctypes.c_int32)]
+                ("task_overhead_bytes", ctypes.c_int32), ("elem_bytes", ctypes.c_int32),
+                ("group_member_tokens", ctypes.c_int32), ("group_min_members", ctypes.c_int32)]
 
 
 class PlanInfo(ctypes.Structure):
@@ -47,7 +49,7 @@ class PlanInfo(ctypes.Structure):
                 ("batch", ctypes.c_int64), ("nodes", ctypes.c_int64), ("virtual_nodes", ctypes.c_int64),
                 ("phase_node_nums", ctypes.c_int32 * 2), ("phase_node_offsets", ctypes.c_int32 * 2),
                 ("q_tile", ctypes.c_int32), ("small_tile", ctypes.c_int32), ("tile_tokens", ctypes.c_int32),
-                ("reserved", ctypes.c_int32), ("target_bytes", ctypes.c_double)]
+                ("has_row_ranges", ctypes.c_int32), ("target_bytes", ctypes.c_double)]
 
 
 class DecodeArgs(ctypes.Structure):
@@ -76,6 +78,7 @@ class DecodeArgs(ctypes.Structure):
         ("mid_lse_stride0", ctypes.c_int64),
         ("sm_scale", ctypes.c_float), ("logit_cap", ctypes.c_float),
         ("stream", ctypes.c_void_p),
+        ("vnode_q_kv_ranges", ctypes.c_void_p),
     ]
 
 
@@ -136,6 +139,8 @@ def load():
         lib.ft_plan_get_info.restype = ctypes.c_int
         lib.ft_plan_copy_tables.argtypes = [ctypes.c_void_p] + [i32p] * 10
         lib.ft_plan_copy_tables.restype = ctypes.c_int
+        lib.ft_plan_copy_row_ranges.argtypes = [ctypes.c_void_p, i32p]
+        lib.ft_plan_copy_row_ranges.restype = ctypes.c_int
         lib.ft_plan_free.argtypes = [ctypes.c_void_p]
         lib.ft_plan_free.restype = None
         _lib = lib

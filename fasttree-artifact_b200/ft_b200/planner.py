@@ -20,6 +20,7 @@ The emitted table family is the reference's (fasttree.py:282-296):
 ``req_to_vnode_entries/offs/lens`` (entries are partial-ROW ids),
 ``phase_node_nums/offsets``.
 """
+import math
 from collections import deque
 from dataclasses import dataclass, field, replace
 
@@ -35,6 +36,7 @@ class VirtualNode:
     requests: np.ndarray   # request ids, in partial-row order
     q_tile: int            # requests per task
     kv_split: int          # tokens per task
+    row_ranges: list = None  # group of short nodes: per request the (begin, end) tokens of the chunk it attends to
 
 
 @dataclass
@@ -51,6 +53,7 @@ class Plan:
     phase_node_nums: list
     phase_node_offsets: list
     node_assignments: list
+    vnode_q_kv_ranges: np.ndarray = None   # optional [partial rows, 2]: tokens of its chunk a partial row attends to
     phase_q_tile_sizes: list = field(default_factory=list)
     phase_kv_tile_sizes: list = field(default_factory=list)
     kv_split_sizes: list = field(default_factory=list)
@@ -82,6 +85,7 @@ def emit_tables(vnodes, batch_size, small_tile, order_key=None, order_out=None, 
     ``req_to_token``); no ``vnode_to_kv_entries`` array is built and
     ``vnode_to_kv_offs`` are those offsets."""
     kv_chunks, kv_offs, kv_lens, q_chunks, q_offs, q_lens = [], [], [], [], [], []
+    range_chunks, any_ranges = [], False
     kv_total = q_total = 0
     for vn in vnodes:
         reqs = np.asarray(vn.requests, dtype=np.int32)
@@ -114,6 +118,15 @@ def emit_tables(vnodes, batch_size, small_tile, order_key=None, order_out=None, 
         q_offs.append((q_base[:, None] + t_off[None, :]).reshape(-1))
         q_lens.append(np.tile(t_len, n_kv))
         q_chunks.append(np.tile(reqs, n_kv))
+        if vn.row_ranges is not None:
+            if n_kv != 1 or n_q != 1:
+                raise ValueError("a group of short nodes must be one task")
+            range_chunks.append(np.asarray(vn.row_ranges, dtype=np.int32).reshape(nreq, 2))
+            any_ranges = True
+        else:                                  # every row of chunk c sees the whole chunk
+            full = np.zeros((n_kv, nreq, 2), dtype=np.int32)
+            full[:, :, 1] = c_len[:, None]
+            range_chunks.append(full.reshape(-1, 2))
         kv_total += length
         q_total += n_kv * nreq
 
@@ -149,6 +162,7 @@ def emit_tables(vnodes, batch_size, small_tile, order_key=None, order_out=None, 
         vnode_to_q_offs=q_offs[perm].astype(np.int32), vnode_to_q_lens=q_lens[perm].astype(np.int32),
         req_to_vnode_entries=np.concatenate([order, pad]),
         req_to_vnode_offs=r2v_offs, req_to_vnode_lens=r2v_lens,
+        vnode_q_kv_ranges=np.ascontiguousarray(np.concatenate(range_chunks)) if any_ranges else None,
         phase_node_nums=[int(big.size), int(small.size)],
         phase_node_offsets=[0, int(big.size)],
     )
@@ -297,6 +311,8 @@ class B200Model:
     ridge_flop_per_byte: float = 90.0   # warp-MMA flops that cost as much time as one streamed byte
     task_overhead_bytes: int = 16384    # fixed cost of one more CTA, in streamed-byte equivalents
     elem_bytes: int = 2
+    group_member_tokens: int = 128      # nodes up to this long (and few enough rows for the few-row kernels) may be grouped; 0: never
+    group_min_members: int = 6          # a group must hold at least this many nodes to beat one task per node
 
 
 def _task_cost(n_req, length, group, head_dim, m):
@@ -385,12 +401,65 @@ def plan_b200(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, p
     m = b200_model_for(params, head_dim, model)
     vnodes, assign, q_tile, small_tile, target = b200_virtual_nodes(
         tree, num_qo_heads, num_kv_heads, head_dim, m, lambda a, i: _chain_ranges(tree, kv_ptrs, a, i))
+    if head_dim == 128 and m.elem_bytes == 2:      # the kernels that honour row ranges exist for this shape
+        vnodes = b200_group_short_nodes(vnodes, q_tile, small_tile, m,
+                                        int(math.floor(target / (2 * head_dim * m.elem_bytes))))
     tabs = emit_tables(vnodes, batch_size, small_tile=small_tile, order_key=b200_task_order)
     params.set_q_tile_sizes([q_tile, small_tile])
     params.set_kv_tile_sizes([m.tile_tokens, m.tile_tokens])
     return Plan(node_assignments=assign, phase_q_tile_sizes=[q_tile, small_tile],
                 phase_kv_tile_sizes=[m.tile_tokens, m.tile_tokens], kv_split_sizes=[],
                 info={"planner": "b200", "target_bytes": float(target), "vnodes": len(vnodes)}, **tabs)
+
+
+def b200_group_short_nodes(vnodes, q_tile, small_tile, m, target_tokens):
+    """Packs short virtual nodes with pairwise disjoint request sets into groups
+    that run as ONE many-row task: the members' KV is concatenated, their requests
+    are concatenated, and each request attends only to its own member's tokens
+    (``row_ranges``).  A tree of many short nodes otherwise becomes thousands of
+    partly filled 64-token tiles, each a task with its own start-up and epilogue.
+
+    Candidates are the virtual nodes with at most ``small_tile`` requests and at
+    most ``group_member_tokens`` tokens, taken in order; a group is closed when
+    the next candidate would exceed ``q_tile`` requests or the token cap (the
+    per-task target, between 4 and 16 tiles), or shares a request with it.  Groups
+    with fewer than ``group_min_members`` members, or not more requests than
+    ``small_tile``, are dissolved.  Result: the other virtual nodes in their
+    order, then groups and dissolved candidates in the order they were closed."""
+    if m.group_member_tokens <= 0:
+        return vnodes
+    tile = m.tile_tokens
+    cap = min(max(target_tokens // tile * tile, 4 * tile), 16 * tile)
+    kept, tail = [], []
+    cur, cur_reqs, cur_tokens, cur_n = [], set(), 0, 0
+
+    def close():
+        if len(cur) >= m.group_min_members and cur_n > small_tile:
+            ranges, row_ranges, start = [], [], 0
+            for vn, length in cur:
+                ranges.extend(vn.kv_ranges)
+                row_ranges.extend([(start, start + length)] * len(vn.requests))
+                start += length
+            tail.append(VirtualNode(ranges, np.concatenate([vn.requests for vn, _ in cur]), q_tile=q_tile,
+                                    kv_split=-(-start // tile) * tile, row_ranges=row_ranges))
+        else:
+            tail.extend(vn for vn, _ in cur)
+
+    for vn in vnodes:
+        length = sum(e - b for b, e in vn.kv_ranges)
+        n = len(vn.requests)
+        if n <= small_tile and length <= m.group_member_tokens:
+            if cur and (cur_n + n > q_tile or cur_tokens + length > cap or any(int(r) in cur_reqs for r in vn.requests)):
+                close()
+                cur, cur_reqs, cur_tokens, cur_n = [], set(), 0, 0
+            cur.append((vn, length))
+            cur_reqs.update(int(r) for r in vn.requests)
+            cur_tokens += length
+            cur_n += n
+        else:
+            kept.append(vn)
+    close()
+    return kept + tail
 
 
 def _tree_arrays(tree):
@@ -427,6 +496,9 @@ def _native_tables(build, direct):
             req_to_vnode_offs=np.empty(info.batch, dtype=np.int32), req_to_vnode_lens=np.empty(info.batch, dtype=np.int32))
         assign = np.empty(info.nodes, dtype=np.int32)
         _lib.check(L.ft_plan_copy_tables(handle, *(as32(t) for t in tabs.values()), as32(assign)))
+        if info.has_row_ranges:
+            tabs["vnode_q_kv_ranges"] = np.empty((info.partial_rows, 2), dtype=np.int32)
+            _lib.check(L.ft_plan_copy_row_ranges(handle, as32(tabs["vnode_q_kv_ranges"])))
     finally:
         L.ft_plan_free(handle)
     if direct:
@@ -439,7 +511,8 @@ def _native_tables(build, direct):
 def _model_struct(m):
     from . import lib as _lib
     return _lib.B200ModelStruct(m.num_sms, m.ctas_per_sm, m.waves, m.tile_tokens, m.rows_per_cta, m.min_chunk,
-                                m.nominal_split, m.ridge_flop_per_byte, m.task_overhead_bytes, m.elem_bytes)
+                                m.nominal_split, m.ridge_flop_per_byte, m.task_overhead_bytes, m.elem_bytes,
+                                m.group_member_tokens, m.group_min_members)
 
 
 def plan_b200_native(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, params, model=None):

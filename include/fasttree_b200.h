@@ -107,6 +107,16 @@ typedef struct ft_decode_args {
   float sm_scale;
   float logit_cap;                    /* accepted and ignored, as in the reference (fasttree.py:603) */
   void* stream;                       /* cudaStream_t                               */
+  /* optional extension of the plan format (no counterpart in the reference) ---- */
+  const int32_t* vnode_q_kv_ranges;   /* [num_partial_rows][2] or NULL: partial row r attends only to tokens
+                                         [begin, end) of its vnode's KV chunk (positions relative to the chunk's
+                                         start, clipped to the chunk).  This lets one vnode hold several short
+                                         nodes with disjoint request sets (their KV concatenated, each request
+                                         seeing only its own node's tokens).  NULL = every row sees the whole
+                                         chunk, as in the reference.  Honoured by the many-row kernels (tcgen05,
+                                         wide mma.sync) and by the generic kernel; the few-row kernels do not
+                                         read it, so rows of vnodes with <= 16 query rows must cover their whole
+                                         chunk (the planner of this library only narrows rows of many-row vnodes). */
 } ft_decode_args;
 
 /* Library version (major*10000 + minor*100 + patch). */
@@ -190,6 +200,9 @@ typedef struct ft_b200_model { /* machine constants of the cost model; NULL in f
   double ridge_flop_per_byte;  /* flops that cost as much time as one streamed byte: 90 (360 at head_dim 128) */
   int32_t task_overhead_bytes; /* fixed cost of one more CTA in streamed-byte equivalents: 16384 */
   int32_t elem_bytes;          /* 2 */
+  int32_t group_member_tokens; /* nodes up to this long, with few enough requests for the few-row kernels, may be
+                                  packed into groups that run as one many-row task: 128; 0 = never */
+  int32_t group_min_members;   /* smallest group worth forming: 6 */
 } ft_b200_model;
 
 typedef struct ft_plan_info {
@@ -204,7 +217,7 @@ typedef struct ft_plan_info {
   int32_t q_tile;       /* requests per task in phase 0 / 1: the tile sizes to pass as phase_q_tile_sizes */
   int32_t small_tile;
   int32_t tile_tokens;
-  int32_t reserved;
+  int32_t has_row_ranges; /* 1: the plan holds groups of short nodes and ft_plan_copy_row_ranges has a table to give */
   double target_bytes;  /* streamed bytes one task was sized for */
 } ft_plan_info;
 
@@ -230,6 +243,10 @@ int ft_plan_copy_tables(const ft_plan* plan, int32_t* vnode_to_kv_entries, int32
                         int32_t* vnode_to_kv_lens, int32_t* vnode_to_q_entries, int32_t* vnode_to_q_offs,
                         int32_t* vnode_to_q_lens, int32_t* req_to_vnode_entries, int32_t* req_to_vnode_offs,
                         int32_t* req_to_vnode_lens, int32_t* node_assignments);
+/* The optional tenth table, vnode_q_kv_ranges of ft_decode_args ([partial_rows][2] int32): only when
+ * ft_plan_info.has_row_ranges is 1 (ft_plan_b200_build at head_dim 128 with 16-bit elements, when short nodes were
+ * packed into groups); FT_ERR_INVALID_ARGUMENT otherwise. */
+int ft_plan_copy_row_ranges(const ft_plan* plan, int32_t* vnode_q_kv_ranges);
 void ft_plan_free(ft_plan* plan);
 
 #ifdef __cplusplus

@@ -67,12 +67,16 @@ def per_leaf_attention(nodes, kv_ptrs, q, k_tree, v_tree, scale, requests=None):
 
 
 def stage1_partials(q, k_buf, v_buf, kv_entries, kv_offs, kv_lens, q_entries, q_offs, q_lens,
-                    scale, round_p_to=None):
+                    scale, round_p_to=None, q_ranges=None):
     """Per-vnode partial attention.  Index tables are 1-D integer arrays in the
     reference's format.  Returns (mid_o [R,Hq,D], mid_lse [R,Hq]) fp32; rows no
     vnode covers stay NaN.  ``round_p_to`` optionally rounds the un-normalised
     probabilities to a storage dtype before the PV product, which is what the
-    reference does with ``exp_logics.to(v.type)`` (fasttree.py:391)."""
+    reference does with ``exp_logics.to(v.type)`` (fasttree.py:391).
+    ``q_ranges`` ([R,2] integers, optional; an extension of the engine's own plan
+    format with no counterpart in the reference) restricts partial row r to the
+    tokens ``[begin, end)`` of its vnode's chunk; a row left with no token gets a
+    zero partial and an LSE of -inf."""
     kv_entries = np.asarray(kv_entries).reshape(-1)
     q_entries = np.asarray(q_entries)
     rows_total = len(q_entries)
@@ -91,14 +95,21 @@ def stage1_partials(q, k_buf, v_buf, kv_entries, kv_offs, kv_lens, q_entries, q_
         reqs = torch.as_tensor(q_entries[qo:qo + ql].astype(np.int64))
         qq = q.index_select(0, reqs).float().view(ql, hkv, group, d)
         s = torch.einsum("rhgd,lhd->rhgl", qq, k) * scale
+        if q_ranges is not None:
+            rng = torch.as_tensor(np.asarray(q_ranges).reshape(-1, 2)[qo:qo + ql].astype(np.int64))
+            pos = torch.arange(kl).view(1, kl)
+            seen = (pos >= rng[:, :1]) & (pos < rng[:, 1:])                      # [ql, kl]
+            s = s.masked_fill(~seen.view(ql, 1, 1, kl), float("-inf"))
         m = s.max(dim=-1, keepdim=True).values
+        m = torch.where(torch.isinf(m), torch.zeros_like(m), m)                  # rows that see no token
         p = torch.exp(s - m)
         den = p.sum(dim=-1, keepdim=True)
         if round_p_to is not None:
             p = p.to(round_p_to).float()
-        o = torch.einsum("rhgl,lhd->rhgd", p, v) / den
+        o = torch.einsum("rhgl,lhd->rhgd", p, v) / den.clamp_min(1e-38)
+        lse = torch.where(den > 0, torch.log(den) + m, torch.full_like(den, float("-inf")))
         mid_o[qo:qo + ql] = o.reshape(ql, hq, d)
-        mid_lse[qo:qo + ql] = (torch.log(den) + m).reshape(ql, hq)
+        mid_lse[qo:qo + ql] = lse.reshape(ql, hq)
     return mid_o, mid_lse
 
 
@@ -127,5 +138,6 @@ def stage2_merge(mid_o, mid_lse, r2v_entries, r2v_offs, r2v_lens):
 def tree_decode(q, k_buf, v_buf, plan, scale):
     """Stage 1 followed by stage 2 on an :class:`OraclePlan`-like object."""
     mid_o, mid_lse = stage1_partials(q, k_buf, v_buf, plan.kv_entries, plan.kv_offs, plan.kv_lens,
-                                     plan.q_entries, plan.q_offs, plan.q_lens, scale)
+                                     plan.q_entries, plan.q_offs, plan.q_lens, scale,
+                                     q_ranges=getattr(plan, "q_ranges", None))
     return stage2_merge(mid_o, mid_lse, plan.r2v_entries, plan.r2v_offs, plan.r2v_lens)

@@ -114,6 +114,9 @@ EDGE_TREES = [
     ([1, 2, 4], [40, 30, 20], 16, 16, 64),            # MHA, head_dim 64
     ([1, 2], [700, 20], 128, 1, 128),                 # G=128: one request spans two 64-row blocks
     ([1, 600], [10, 33], 32, 32, 128),                # 19200 one-tile tasks: the persistent kernel walks > 48 per CTA
+    ([1, 40], [70, 20], 32, 8, 128),                  # B200 plan: 40 short leaves -> groups of <= 32 requests, ragged ranges
+    ([1, 4, 64], [100, 50, 12], 32, 32, 128),         # B200 plan: MHA, groups of 21 twelve-token leaves
+    ([1, 3, 24], [30, 129, 31], 16, 4, 128),          # B200 plan: members that straddle tile boundaries
 ]
 
 
@@ -136,9 +139,31 @@ def test_edge_shapes_against_oracle(spec, dtype):
             np.testing.assert_allclose(run.o_lse.cpu().numpy(), truth_lse.numpy(), rtol=1e-4, atol=2e-5)
             # stage-1 partials against the oracle's per-vnode restatement on the very same plan
             tabs = [t.cpu().numpy() for t in run.aux[:6]]
-            mid_o, mid_lse = ref_attention.stage1_partials(c["q"], c["k"], c["v"], *tabs, scale)
+            ranges = engine.row_ranges_of(run.aux[3])     # B200 plans that group short nodes
+            mid_o, mid_lse = ref_attention.stage1_partials(
+                c["q"], c["k"], c["v"], *tabs, scale, q_ranges=None if ranges is None else ranges.cpu().numpy())
             np.testing.assert_allclose(run.mid_lse.cpu().numpy(), mid_lse.numpy(), rtol=1e-4, atol=2e-5)
             assert (run.mid_o.cpu() - mid_o).abs().max().item() <= tol
+
+
+@pytest.mark.parametrize("spec", [t for t in EDGE_TREES if t[0] in ([1, 40], [1, 4, 64], [1, 3, 24])],
+                         ids=lambda s: "n%s" % "-".join(map(str, s[0])))
+def test_short_nodes_run_as_groups_with_row_ranges(spec):
+    """The B200 plan of these trees packs the short leaves into many-row tasks whose rows carry token ranges;
+    every kernel family must give the path-concatenated attention on that plan."""
+    sizes, lens, hq, hkv, d = spec
+    c = adhoc(sizes, lens, hq, hkv, d, torch.float16, seed=11, q_scale=0.5)
+    grouped = gpu_utils.EngineRun(c["nodes"], c["ptrs"], c["batch"], c["q"], c["k"], c["v"], hq, hkv, d, c["tsq"])
+    ranges = engine.row_ranges_of(grouped.aux[3])
+    assert ranges is not None and tuple(ranges.shape) == (grouped.aux[3].numel(), 2)
+    n_big = grouped.aux[11][0]
+    assert n_big > 0 and int((ranges[:, 0] > 0).sum()) > 0          # some rows start inside their chunk
+    scale = 1.0 / d ** 0.5
+    truth, _ = ref_attention.per_leaf_attention(c["nodes"], c["ptrs"], c["q"], c["k"], c["v"], scale)
+    for path in paths_for(c):
+        out = grouped.decode(path=path)
+        assert lib.read_device_status() == 0
+        assert (out - truth).abs().max().item() <= atol_for(torch.float16), path
 
 
 def test_scattered_pool_rows_and_2d_index_table():

@@ -65,6 +65,8 @@ def check_plan_covers_every_path_once(tree, ptrs, batch, plan):
     """Every request must see each token of its root->leaf path in exactly one
     of its partial rows, and nothing else."""
     kv_entries = plan.vnode_to_kv_entries
+    ranges = plan.vnode_q_kv_ranges          # groups of short nodes: a row sees only [begin, end) of its chunk
+    n_big = plan.phase_node_nums[0]
     row_tokens = {}
     for vn in range(plan.num_vnodes):
         ko, kl = int(plan.vnode_to_kv_offs[vn]), int(plan.vnode_to_kv_lens[vn])
@@ -74,7 +76,14 @@ def check_plan_covers_every_path_once(tree, ptrs, batch, plan):
         assert toks.min() >= 0
         for row in range(qo, qo + ql):
             assert row not in row_tokens, "two vnodes write the same partial row"
-            row_tokens[row] = toks
+            if ranges is None:
+                row_tokens[row] = toks
+            else:
+                b, e = int(ranges[row, 0]), int(ranges[row, 1])
+                assert 0 <= b < e <= kl
+                if vn >= n_big:                  # the few-row kernels do not look at the ranges
+                    assert (b, e) == (0, kl)
+                row_tokens[row] = toks[b:e]
     assert len(row_tokens) == plan.num_partial_rows
     paths = {}
     for nd in tree:
@@ -135,6 +144,9 @@ def test_b200_plan_on_random_trees(seed):
 def _same_plan(a, b):
     for x, y, name in zip(a.tables(), b.tables(), cases.TABLES):
         np.testing.assert_array_equal(x, y, err_msg=name)
+    assert (a.vnode_q_kv_ranges is None) == (b.vnode_q_kv_ranges is None)
+    if a.vnode_q_kv_ranges is not None:
+        np.testing.assert_array_equal(a.vnode_q_kv_ranges, b.vnode_q_kv_ranges)
     assert list(a.node_assignments) == list(b.node_assignments)
     assert list(a.phase_node_nums) == list(b.phase_node_nums)
     assert list(a.phase_node_offsets) == list(b.phase_node_offsets)
@@ -241,3 +253,60 @@ def test_validate_tree_rejects_bad_trees():
     nodes[0].num_children = 2
     with pytest.raises(ValueError):
         validate_tree(nodes)
+
+
+GROUP_TREES = {
+    # tree                                                         heads      groups expected
+    "cfg3": (([1, 16, 256], [2048, 512, 64]), (32, 8), True),
+    "deep_short": (([1, 2, 4, 8, 16, 32, 64], [16] * 7), (32, 32), True),
+    "ragged_members": (([1, 3, 24], [30, 129, 31]), (16, 4), True),
+    "long_leaves": (([1, 64], [4096, 256]), (32, 8), False),          # members longer than the limit
+    "too_few": (([1, 5], [300, 20]), (8, 8), False),                  # fewer members than a group needs
+}
+
+
+@pytest.mark.parametrize("name", sorted(GROUP_TREES))
+@pytest.mark.parametrize("native", [False, True], ids=["python", "native"])
+def test_groups_of_short_nodes(name, native):
+    """Short nodes with disjoint requests are packed into many-row tasks whose rows carry token ranges; the
+    grouped plan still covers every path once, the few-row tasks keep whole-chunk ranges, and the oracle's
+    two-stage evaluation of the grouped plan reproduces path-concatenated attention."""
+    import torch
+    from oracle import ref_attention
+    (sizes, lens), (hq, hkv), expect = GROUP_TREES[name]
+    onodes = ref_inputs.layered_tree(sizes, lens)
+    tree, batch, ptrs = product_tree(onodes)
+    p = make_params(hq, hkv, [16, 4], planner_name="b200")
+    p.native_planner = native
+    plan = fasttree.build_plan(tree, ptrs, batch, hq, hkv, 128, [1024, 128], [132, 528], [132, 132], p)
+    assert (plan.vnode_q_kv_ranges is not None) == expect
+    check_plan_covers_every_path_once(tree, ptrs, batch, plan)
+    if not expect:
+        return
+    assert plan.vnode_q_kv_ranges.shape == (plan.num_partial_rows, 2) and plan.vnode_q_kv_ranges.dtype == np.int32
+    # the same tree with grouping switched off has more tasks and the same partial rows
+    q = make_params(hq, hkv, [16, 4], planner_name="b200")
+    q.native_planner = native
+    from dataclasses import replace
+    q.b200_model = replace(planner.b200_model_for(q, 128), group_member_tokens=0)
+    flat = fasttree.build_plan(tree, ptrs, batch, hq, hkv, 128, [1024, 128], [132, 528], [132, 132], q)
+    assert flat.vnode_q_kv_ranges is None
+    assert flat.num_vnodes > plan.num_vnodes and flat.num_partial_rows == plan.num_partial_rows
+    if sum(s * l for s, l in zip(sizes, lens)) > 20000:
+        return                                     # the arithmetic check below is for the small trees
+    qq, k, v, _, _ = ref_inputs.draw_qkv(onodes, hq, hkv, 128, torch.float32, 5, 0.5)
+    scale = 1.0 / 128 ** 0.5
+    mid_o, mid_lse = ref_attention.stage1_partials(qq, k, v, *plan.tables()[:6], scale, q_ranges=plan.vnode_q_kv_ranges)
+    out, lse = ref_attention.stage2_merge(mid_o, mid_lse, *plan.tables()[6:9])
+    truth, truth_lse = ref_attention.per_leaf_attention(onodes, ptrs, qq, k, v, scale)
+    np.testing.assert_allclose(out.numpy(), truth.numpy(), rtol=1e-5, atol=2e-6)
+    np.testing.assert_allclose(lse.numpy(), truth_lse.numpy(), rtol=1e-5, atol=1e-5)
+
+
+def test_no_groups_outside_head_dim_128():
+    tree, batch, ptrs = product_tree(ref_inputs.layered_tree([1, 16, 256], [64, 32, 16]))
+    for native in (False, True):
+        p = make_params(32, 8, [16, 4], planner_name="b200")
+        p.native_planner = native
+        plan = fasttree.build_plan(tree, ptrs, batch, 32, 8, 64, [1024, 128], [132, 528], [132, 132], p)
+        assert plan.vnode_q_kv_ranges is None
