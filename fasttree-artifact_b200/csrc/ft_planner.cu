@@ -255,15 +255,17 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
 
     // ---- groups of short nodes (table-building mode, head_dim 128, 16-bit elements: the shape whose kernels honour
     // per-row token ranges).  Candidates - at most small_tile requests, at most group_member_tokens tokens - are
-    // taken in order; a group is closed when the next candidate would exceed q_tile requests or the token cap (the
-    // per-task target, between 4 and 16 tiles) or shares a request with it; groups with fewer than
+    // taken in order; a group is closed when the next candidate would exceed q_tile requests or 16 tiles of tokens,
+    // would exceed the per-task token target (at least 4 tiles) once the group has more than small_tile requests,
+    // or shares a request with it; groups with fewer than
     // group_min_members members, or not more requests than small_tile, are dissolved.  Result: the other virtual
     // nodes in their order, then groups and dissolved candidates in the order they were closed.
     bool any_groups = false;
     if (direct == nullptr && head_dim == 128 && m.elem_bytes == 2 && m.group_member_tokens > 0) {
       const int64_t tile = m.tile_tokens;
       const int64_t target_tokens = (int64_t)std::floor(target / (double)row_bytes);
-      const int64_t cap = std::min(std::max(target_tokens / tile * tile, 4 * tile), 16 * tile);
+      const int64_t hard_cap = 16 * tile;
+      const int64_t cap = std::min(std::max(target_tokens / tile * tile, 4 * tile), hard_cap);
       std::vector<Spec> kept, tail;
       std::vector<Spec> cur;
       std::vector<uint8_t> in_group((size_t)std::max(batch, 1), 0);
@@ -295,7 +297,9 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
         if (nreq <= small_tile && s.length <= m.group_member_tokens) {
           bool shared = false;
           for (int32_t r : s.reqs) shared = shared || in_group[r] != 0;
-          if (!cur.empty() && (cur_n + nreq > q_tile || cur_tokens + s.length > cap || shared)) close();
+          if (!cur.empty() && (cur_n + nreq > q_tile || cur_tokens + s.length > hard_cap ||
+                               (cur_tokens + s.length > cap && cur_n > small_tile) || shared))
+            close();
           for (int32_t r : s.reqs) in_group[r] = 1;
           cur_tokens += s.length;
           cur_n += nreq;

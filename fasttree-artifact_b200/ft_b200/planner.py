@@ -421,15 +421,17 @@ def b200_group_short_nodes(vnodes, q_tile, small_tile, m, target_tokens):
 
     Candidates are the virtual nodes with at most ``small_tile`` requests and at
     most ``group_member_tokens`` tokens, taken in order; a group is closed when
-    the next candidate would exceed ``q_tile`` requests or the token cap (the
-    per-task target, between 4 and 16 tiles), or shares a request with it.  Groups
+    the next candidate would exceed ``q_tile`` requests or 16 tiles of tokens,
+    would exceed the per-task token target (at least 4 tiles) once the group has
+    more than ``small_tile`` requests, or shares a request with it.  Groups
     with fewer than ``group_min_members`` members, or not more requests than
     ``small_tile``, are dissolved.  Result: the other virtual nodes in their
     order, then groups and dissolved candidates in the order they were closed."""
     if m.group_member_tokens <= 0:
         return vnodes
     tile = m.tile_tokens
-    cap = min(max(target_tokens // tile * tile, 4 * tile), 16 * tile)
+    hard_cap = 16 * tile
+    cap = min(max(target_tokens // tile * tile, 4 * tile), hard_cap)
     kept, tail = [], []
     cur, cur_reqs, cur_tokens, cur_n = [], set(), 0, 0
 
@@ -449,7 +451,9 @@ def b200_group_short_nodes(vnodes, q_tile, small_tile, m, target_tokens):
         length = sum(e - b for b, e in vn.kv_ranges)
         n = len(vn.requests)
         if n <= small_tile and length <= m.group_member_tokens:
-            if cur and (cur_n + n > q_tile or cur_tokens + length > cap or any(int(r) in cur_reqs for r in vn.requests)):
+            if cur and (cur_n + n > q_tile or cur_tokens + length > hard_cap
+                        or (cur_tokens + length > cap and cur_n > small_tile)
+                        or any(int(r) in cur_reqs for r in vn.requests)):
                 close()
                 cur, cur_reqs, cur_tokens, cur_n = [], set(), 0, 0
             cur.append((vn, length))
