@@ -183,7 +183,8 @@ def test_native_splitter_matches_on_random_trees_and_models(seed):
                                                             len_lo=1, len_hi=40 * (1 + seed)))
     hq, hkv = [(32, 8), (8, 8), (16, 1), (64, 8)][seed % 4]
     model = replace(planner.B200Model(), waves=float(rng.choice([0.5, 1.0, 2.0, 3.0])), min_chunk=int(rng.choice([64, 128, 256])),
-                    rows_per_cta=int(rng.choice([64, 128])), ridge_flop_per_byte=float(rng.choice([90.0, 360.0])))
+                    rows_per_cta=int(rng.choice([64, 128])), ridge_flop_per_byte=float(rng.choice([90.0, 360.0])),
+                    group_member_tokens=int(rng.choice([0, 48, 128, 256])), group_min_members=int(rng.choice([2, 6, 10])))
     pa, pb = make_params(hq, hkv, [16, 4], planner_name="b200"), make_params(hq, hkv, [16, 4], planner_name="b200")
     spec = planner.plan_b200(tree, ptrs, batch, hq, hkv, 128, pa, model=model)
     native = planner.plan_b200_native(tree, ptrs, batch, hq, hkv, 128, pb, model=model)
@@ -199,6 +200,19 @@ def test_native_splitter_rejects_bad_trees():
         planner.plan_b200_native(tree, ptrs[:-1], batch, 8, 8, 128, p)
     with pytest.raises(lib.FastTreeError):                      # a request id outside the batch
         planner.plan_b200_native(tree, ptrs, batch - 1, 8, 8, 128, p)
+    import ctypes
+    L, handle = lib.load(), ctypes.c_void_p()                  # a plan without groups has no row-range table to give
+    parent, seqlen, req_offs, req_ids = planner._tree_arrays(tree)
+    i32p, i64p = ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int64)
+    kv = np.asarray(ptrs, dtype=np.int64)
+    assert L.ft_plan_b200_build(parent.ctypes.data_as(i32p), seqlen.ctypes.data_as(i32p), len(tree),
+                                req_offs.ctypes.data_as(i64p), req_ids.ctypes.data_as(i32p), kv.ctypes.data_as(i64p),
+                                batch, 8, 8, 128, None, ctypes.byref(handle)) == 0
+    info = lib.PlanInfo()
+    assert L.ft_plan_get_info(handle, ctypes.byref(info)) == 0 and info.has_row_ranges == 0
+    out = np.zeros(2 * max(int(info.partial_rows), 1), dtype=np.int32)
+    assert L.ft_plan_copy_row_ranges(handle, out.ctypes.data_as(i32p)) == -1
+    L.ft_plan_free(handle)
     tree[1].parent = 2                                         # parent after child
     with pytest.raises(lib.FastTreeError):
         planner.plan_b200_native(tree, ptrs, batch, 8, 8, 128, p)
