@@ -421,7 +421,10 @@ int launch_stage2(const ft::Stage2Params& p, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  FT_CUDA_OK(cudaLaunchKernelEx(&cfg, ft::stage2_merge_kernel<T>, p));
+  if (p.head_dim <= 128)
+    FT_CUDA_OK(cudaLaunchKernelEx(&cfg, ft::stage2_merge_kernel<T, 1>, p));
+  else
+    FT_CUDA_OK(cudaLaunchKernelEx(&cfg, ft::stage2_merge_kernel<T, 2>, p));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return FT_OK;
 }
@@ -519,6 +522,13 @@ int ft_stage2(const ft_decode_args* a) {
   p.batch = a->batch;
   p.heads = a->num_qo_heads;
   p.head_dim = a->head_dim;
+  {
+    const int64_t esz = a->dtype == FT_F32 ? 4 : 2, vec = 4 * esz;  // bytes of one 4-element store
+    p.o_vec = (reinterpret_cast<uintptr_t>(a->o) % vec == 0 && (a->o_stride0 * esz) % vec == 0 &&
+               (a->o_stride1 * esz) % vec == 0)
+                  ? 1
+                  : 0;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
   switch (a->dtype) {
     case FT_F16: return launch_stage2<__half>(p, st);

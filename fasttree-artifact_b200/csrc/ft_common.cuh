@@ -90,6 +90,7 @@ struct Stage2Params {
   int32_t batch;
   int32_t heads;
   int32_t head_dim;
+  int32_t o_vec;  // 1: o rows are aligned for 4-element vector stores
 };
 
 // Programmatic dependent launch: stage 1 lets the next kernel of the stream be scheduled while its own CTAs are

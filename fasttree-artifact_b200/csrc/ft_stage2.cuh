@@ -13,9 +13,10 @@
 
 namespace ft {
 
-template <typename T>
-__global__ void __launch_bounds__(128) stage2_merge_kernel(Stage2Params p) {
-  constexpr int MAXC = 2;  // float4 chunks per lane: head_dim <= 256
+// MAXC: float4 chunks per lane (1: head_dim <= 128, 2: head_dim <= 256); the narrower variant needs half the
+// registers for the rows in flight, which is what bounds the warps per SM here.
+template <typename T, int MAXC>
+__global__ void __launch_bounds__(128, MAXC == 1 ? 9 : 6) stage2_merge_kernel(Stage2Params p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t pair = (int64_t)blockIdx.x * 4 + warp;
   if (pair >= (int64_t)p.batch * p.heads) return;
@@ -99,10 +100,17 @@ __global__ void __launch_bounds__(128) stage2_merge_kernel(Stage2Params p) {
   for (int c = 0; c < MAXC; ++c) {
     const int ch = lane + 32 * c;
     if (ch < chunks) {
-      dst[4 * ch + 0] = from_float<T>(acc[c].x * inv);
-      dst[4 * ch + 1] = from_float<T>(acc[c].y * inv);
-      dst[4 * ch + 2] = from_float<T>(acc[c].z * inv);
-      dst[4 * ch + 3] = from_float<T>(acc[c].w * inv);
+      alignas(16) T out[4] = {from_float<T>(acc[c].x * inv), from_float<T>(acc[c].y * inv), from_float<T>(acc[c].z * inv),
+                  from_float<T>(acc[c].w * inv)};
+      if (p.o_vec) {  // four elements in one store when the output rows allow it
+        if constexpr (sizeof(T) == 2)
+          *reinterpret_cast<uint2*>(dst + 4 * ch) = *reinterpret_cast<const uint2*>(out);
+        else
+          *reinterpret_cast<float4*>(dst + 4 * ch) = *reinterpret_cast<const float4*>(out);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) dst[4 * ch + e] = out[e];
+      }
     }
   }
   if (p.o_lse != nullptr && lane == 0)
