@@ -27,6 +27,7 @@ from dataclasses import dataclass, field, replace
 import numpy as np
 
 PAD_ENTRIES = 32  # the reference appends 32 x -1 to both index lists (fasttree.py:261-262)
+GROUP_MAX_TILES = 16  # a group of short nodes never spans more KV tiles than this (same constant in csrc/ft_planner.cu)
 
 
 @dataclass
@@ -430,7 +431,7 @@ def b200_group_short_nodes(vnodes, q_tile, small_tile, m, target_tokens):
     if m.group_member_tokens <= 0:
         return vnodes
     tile = m.tile_tokens
-    hard_cap = 16 * tile
+    hard_cap = GROUP_MAX_TILES * tile
     cap = min(max(target_tokens // tile * tile, 4 * tile), hard_cap)
     kept, tail = [], []
     cur, cur_reqs, cur_tokens, cur_n = [], set(), 0, 0
