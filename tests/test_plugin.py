@@ -21,7 +21,10 @@ KEYS = ["vnode_to_kv_offs", "vnode_to_kv_lens", "vnode_to_q_offs", "vnode_to_q_l
 
 def make_md(hq, hkv, planner):
     return metadata.FastTreeMetadata(hq, hkv, 128, "cpu", max_vnodes=4096, max_vnode_to_q_entries=8192,
-                                     max_batch_size=256, planner=planner)
+                                     max_batch_size=512, planner=planner)
+
+
+ALL_BURSTS = sorted(plugin_cases.CASES) + sorted(plugin_cases.TRAFFIC_SHAPES)
 
 
 @pytest.mark.parametrize("name", sorted(plugin_cases.CASES))
@@ -69,7 +72,7 @@ def check_cover(batch, rows, md, extra_prompt):
         assert kv_offs[v] + kv_lens[v] == end and q_lens[v] == 1 and q_entries[q_offs[v]] == r
 
 
-@pytest.mark.parametrize("name", sorted(plugin_cases.CASES))
+@pytest.mark.parametrize("name", ALL_BURSTS)
 @pytest.mark.parametrize("planner,extra", [("reference", 0), ("b200", 0), ("b200", 5)])
 def test_plans_cover_every_position_once(name, planner, extra):
     batch, rows, hq, hkv = plugin_cases.build(name, extra_prompt=extra)
@@ -78,7 +81,7 @@ def test_plans_cover_every_position_once(name, planner, extra):
     check_cover(batch, rows, md, extra)
 
 
-@pytest.mark.parametrize("name", sorted(plugin_cases.CASES))
+@pytest.mark.parametrize("name", ALL_BURSTS)
 @pytest.mark.parametrize("extra", [0, 5])
 def test_native_schedule_matches_the_python_specification(name, extra):
     """ft_plan_b200_build_direct against b200_virtual_nodes + emit_tables on the same burst."""

@@ -36,14 +36,23 @@ def reference_attention(batch, rows, q, layer, step, scale):
 @pytest.mark.parametrize("planner,extra", [("reference", 0), ("b200", 0), ("b200", 3)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
 def test_decode_burst_through_the_hook(name, planner, extra, dtype):
+    run_burst(name, planner, extra, dtype, steps=3)
+
+
+@pytest.mark.parametrize("name", sorted(plugin_cases.TRAFFIC_SHAPES))
+def test_serving_traffic_shapes_through_the_hook(name):
+    """The tree shapes of the reference's four serving benchmarks (synthetic token counts), two decode steps."""
+    run_burst(name, "b200", 2, torch.float16, steps=2)
+
+
+def run_burst(name, planner, extra, dtype, steps):
     from sglang.srt.layers.radix_attention import RadixAttention
     from sglang.srt.model_executor.forward_batch_info import InputMetadata
 
-    steps = 3
     batch, rows, hq, hkv = plugin_cases.build(name, device="cuda", dtype=dtype, extra_prompt=extra, steps=steps)
     d = 128
     md = metadata.FastTreeMetadata(hq, hkv, d, "cuda", max_vnodes=4096, max_vnode_to_q_entries=8192,
-                                   max_batch_size=256, planner=planner)
+                                   max_batch_size=512, planner=planner)
     plugin._replace_fwd_batch_info()
     plugin._replace_radix_attn()
     attn = RadixAttention(hq, d, 1.0 / d ** 0.5, hkv, 0)
