@@ -166,6 +166,31 @@ def test_short_nodes_run_as_groups_with_row_ranges(spec):
         assert (out - truth).abs().max().item() <= atol_for(torch.float16), path
 
 
+@pytest.mark.parametrize("seed", range(10))
+def test_random_trees_of_short_nodes(seed):
+    """Irregular trees whose nodes are mostly short enough to be grouped (random depth, fan-out, node lengths,
+    head configuration and 16-bit type per seed), every kernel family, against path-concatenated attention."""
+    rng = np.random.default_rng(1000 + seed)
+    levels = int(rng.integers(2, 6))
+    hi = int(rng.choice([8, 20, 70, 130, 300]))
+    nodes = ref_inputs.random_tree(levels, seed, max_children=int(rng.choice([4, 12, 40])),
+                                   lam=float(rng.choice([1.5, 3.0, 6.0])), len_lo=1, len_hi=hi)
+    if len(nodes) > 3000:
+        pytest.skip("tree too large for a quick test")
+    hq, hkv = [(32, 8), (32, 32), (16, 1), (64, 8), (8, 2)][seed % 5]
+    dtype = [torch.float16, torch.bfloat16][seed % 2]
+    q, k, v, ptrs, batch = ref_inputs.draw_qkv(nodes, hq, hkv, 128, dtype, seed, 0.5)
+    run = gpu_utils.EngineRun(nodes, ptrs, batch, q, k, v, hq, hkv, 128, cases.q_tiles_for_group(hq // hkv))
+    scale = 1.0 / 128 ** 0.5
+    truth, truth_lse = ref_attention.per_leaf_attention(nodes, ptrs, q, k, v, scale)
+    tol = atol_for(dtype) + (float(truth.abs().max()) * 2 ** -8 if dtype == torch.bfloat16 else 0.0)
+    for path in ("auto", "tcgen05", "mma", "mma_wide", "stream", "generic"):
+        out = run.decode(path=path)
+        assert lib.read_device_status() == 0
+        assert (out - truth).abs().max().item() <= tol, path
+        np.testing.assert_allclose(run.o_lse.cpu().numpy(), truth_lse.numpy(), rtol=1e-4, atol=2e-5)
+
+
 def test_scattered_pool_rows_and_2d_index_table():
     """Serving-style addressing: K/V rows live at arbitrary pool slots and the
     row-id list is a 2-D int32 table (req_to_token) addressed by flat offsets."""
