@@ -494,6 +494,68 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           mbar_arrive_on_cp_async(bar(C::Q_FULL));  // one arrival per thread once its copies have landed
           cp_async_wait<0>();
         }
+        if (warp == 6) {
+          // ============================================================== V loader (this warp, once Q is on its way)
+          // Row ids live in registers, two per lane and one tile ahead, so this role shares nothing with the K
+          // loader: same dense test (64 consecutive pool rows -> two TMA boxes), same gather otherwise.
+          const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)kvh * p.v_s1;
+          auto fetch_ids = [&](int t, int (&dst)[2]) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int pos = t * C::TILE + lane + 32 * h;
+              dst[h] = pos < id_lim ? __ldg(p.kv_entries + kv_off + pos) : -1;
+            }
+          };
+          int cur[2] = {-1, -1}, nxt[2] = {-1, -1};
+          if (ntiles > 0) fetch_ids(0, cur);
+          for (int t = 0; t < ntiles && !dead; ++t) {
+            if (t + 1 < ntiles) fetch_ids(t + 1, nxt);
+            const int g = g0 + t, b = g & 1;
+            bool dense = false;
+            int first_row = 0;
+            if (tp.has_tma && (t + 1) * C::TILE <= id_lim) {
+              first_row = __shfl_sync(0xffffffffu, cur[0], 0);
+              const bool mine = cur[0] == first_row + lane && cur[1] == first_row + lane + 32;
+              dense = __all_sync(0xffffffffu, mine) && first_row >= 0 && (uint32_t)(first_row + C::TILE) <= row_lim;
+            }
+            if (!tc_wait(bar(C::V_EMPTY + b), ((uint32_t)(g >> 1) & 1u) ^ 1u, abort_flag)) {
+              give_up();
+              break;
+            }
+            const uint32_t buf = v_buf(g), full = bar(C::V_FULL + b);
+            if (dense) {
+              if (lane == 0) {
+                mbar_arrive_expect_tx(full, 16384);
+                tma_load_3d(buf, &tp.v_map, 0, kvh, first_row, full);
+                tma_load_3d(buf + 8192, &tp.v_map, 64, kvh, first_row, full);
+              } else {
+                mbar_arrive(full);
+              }
+            } else {
+              const int c = lane & 15;
+              bool bad = false, stored = false;
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+#pragma unroll 4
+                for (int i = 0; i < 16; ++i) {
+                  const int r = (lane >> 4) + 2 * i + 32 * h, pos = t * C::TILE + r;  // row r: slot h of lane r & 31
+                  const int id = __shfl_sync(0xffffffffu, cur[h], r & 31);
+                  const uint32_t row = pos < id_lim ? (uint32_t)id : 0xffffffffu;
+                  const bool ok = row < row_lim;  // padding (0xffffffff), negative and too-large ids all fail this test
+                  bad |= !ok && pos < id_lim;
+                  stored |= !ok;
+                  cp_async16(buf + tc_swz(r, c, 8192), vbase + (int64_t)(ok ? row : 0u) * p.v_s0 + c * 8, ok);
+                }
+              }
+              if (bad) flag_error(FT_DEV_BAD_KV_INDEX);
+              if (stored) proxy_fence();  // the zero rows were plain shared stores
+              mbar_arrive_on_cp_async(full);
+            }
+            cur[0] = nxt[0];
+            cur[1] = nxt[1];
+          }
+          cp_async_wait<0>();
+        }
       } else if (warp == 5) {
         // ================================================================ loader
         const int* ring = reinterpret_cast<const int*>(smem + C::IDX_OFF);
@@ -534,48 +596,33 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           mbar_arrive_on_cp_async(full);
         };
         const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)kvh * p.k_s1;
-        const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)kvh * p.v_s1;
         if (ntiles > 0) issue_ids(0);
         cp_async_commit();
         if (ntiles > 1) issue_ids(1);
         cp_async_commit();
-        // Step s loads K of tile s and V of tile s-1: K runs one tile ahead, so that a V buffer still held by
-        // the P.V of two tiles back never keeps the next K load (and with it the next S) waiting.
-        bool dense_prev = false;
-        int first_prev = 0;
-        for (int s = 0; s <= ntiles && !dead; ++s) {
+        // K only: the V tiles have a loader warp of their own (below), so a tile whose rows must be gathered one
+        // by one costs each of the two warps half of the copies, and K never waits behind a V buffer.
+        for (int s = 0; s < ntiles && !dead; ++s) {
+          const int g = g0 + s, b = g & 1;
+          cp_async_wait<1>();  // ids of tile s have landed (this lane's copies)
+          __syncwarp();
+          if (s == 0 && lane == 0) FT_TL_MARK(5);
+          // dense tile: 64 valid, consecutive row ids inside the buffer -> TMA
+          const int* ids = ring + (s % C::IDX_SLOTS) * C::TILE;
           bool dense = false;
           int first_row = 0;
-          if (s < ntiles) {
-            const int g = g0 + s, b = g & 1;
-            cp_async_wait<1>();  // ids of tile s have landed (this lane's copies)
-            __syncwarp();
-            if (s == 0 && lane == 0) FT_TL_MARK(5);
-            // dense tile: 64 valid, consecutive row ids inside the buffer -> TMA
-            const int* ids = ring + (s % C::IDX_SLOTS) * C::TILE;
-            if (tp.has_tma && (s + 1) * C::TILE <= id_lim) {
-              first_row = ids[0];
-              const bool mine = ids[lane] == first_row + lane && ids[lane + 32] == first_row + lane + 32;
-              dense = __all_sync(0xffffffffu, mine) && first_row >= 0 && (uint32_t)(first_row + C::TILE) <= row_lim;
-            }
-            if (!tc_wait(bar(C::K_EMPTY + b), ((uint32_t)(g >> 1) & 1u) ^ 1u, abort_flag)) {
-              give_up();
-              break;
-            }
-            load_tile(s, k_buf(g), bar(C::K_FULL + b), &tp.k_map, kbase, p.k_s0, dense, first_row);
+          if (tp.has_tma && (s + 1) * C::TILE <= id_lim) {
+            first_row = ids[0];
+            const bool mine = ids[lane] == first_row + lane && ids[lane + 32] == first_row + lane + 32;
+            dense = __all_sync(0xffffffffu, mine) && first_row >= 0 && (uint32_t)(first_row + C::TILE) <= row_lim;
           }
-          if (s > 0) {
-            const int g = g0 + s - 1, b = g & 1;
-            if (!tc_wait(bar(C::V_EMPTY + b), ((uint32_t)(g >> 1) & 1u) ^ 1u, abort_flag)) {
-              give_up();
-              break;
-            }
-            load_tile(s - 1, v_buf(g), bar(C::V_FULL + b), &tp.v_map, vbase, p.v_s0, dense_prev, first_prev);
+          if (!tc_wait(bar(C::K_EMPTY + b), ((uint32_t)(g >> 1) & 1u) ^ 1u, abort_flag)) {
+            give_up();
+            break;
           }
-          if (s + 2 < ntiles) issue_ids(s + 2);  // into the slot of tile s-1, whose ids were last used just above
+          load_tile(s, k_buf(g), bar(C::K_FULL + b), &tp.k_map, kbase, p.k_s0, dense, first_row);
+          if (s + 2 < ntiles) issue_ids(s + 2);  // into the slot of tile s-1, whose ids were last used a step ago
           cp_async_commit();
-          dense_prev = dense;
-          first_prev = first_row;
         }
         cp_async_wait<0>();
       } else {
