@@ -22,17 +22,20 @@
 //   warp 4     MMA issue (one elected lane): S_t is issued before the softmax of
 //              tile t-1 has finished (two S buffers in TMEM), P.V of tile t-1
 //              as soon as its P is written.
-//   warp 5     K/V loads.  A tile whose 64 row ids are consecutive is fetched
-//              with four tiled TMA copies (cp.async.bulk.tensor, 128-byte
+//   warp 5     K loads.  A tile whose 64 row ids are consecutive is fetched
+//              with two tiled TMA copies (cp.async.bulk.tensor, 128-byte
 //              swizzle, no multicast) straight into the operand layout; any
 //              other tile (scattered pool slots, the ragged last tile) is
-//              gathered with 16-byte cp.async copies.  K loads run one tile
-//              ahead of V loads; row ids reach a small shared ring with
-//              cp.async two tiles ahead.
-//   warps 6-7  Q gather (by request id), concurrent with the first K/V loads:
+//              gathered with 16-byte cp.async copies.  Row ids reach a small
+//              shared ring with cp.async two tiles ahead.
+//   warps 6-7  Q gather (by request id), concurrent with the first K loads:
 //              when G is a power of two, two TMA boxes for the whole tile if the
 //              request ids are consecutive, else one box per request (its G
 //              adjacent heads); 16-byte cp.async copies otherwise.
+//   warp 6     then loads the V tiles the same way as warp 5 loads K, with the
+//              row ids in registers (two per lane, one tile ahead), so the two
+//              loaders share nothing and a gathered tile costs each of them
+//              half of the copies.
 // The two warpgroups trade registers at start-up (setmaxnreg): the kernel
 // launches at 128 registers per thread, so that a CTA takes exactly two
 // equal-sized warps per scheduler partition and two CTAs always fit on an SM
