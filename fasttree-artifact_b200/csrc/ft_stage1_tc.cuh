@@ -33,11 +33,9 @@
 //              request ids are consecutive, else one box per request (its G
 //              adjacent heads); 16-byte cp.async copies otherwise.
 //   warp 6     then loads the V tiles the same way as warp 5 loads K, with the
-//              row ids in registers (two per lane, one tile ahead), so the
-//              loaders share nothing.
-//   warp 7     then helps with K: of a tile that has to be gathered it copies
-//              rows 32..63 (warp 5 rows 0..31), from its own register copy of
-//              the ids; a gathered tile thus costs three warps a third each.
+//              row ids in registers (two per lane, one tile ahead), so the two
+//              loaders share nothing and a gathered tile costs each of them
+//              half of the copies.
 // The two warpgroups trade registers at start-up (setmaxnreg): the kernel
 // launches at 128 registers per thread, so that a CTA takes exactly two
 // equal-sized warps per scheduler partition and two CTAs always fit on an SM
@@ -216,7 +214,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
   }
   if (tid == 0) {
     for (int b = 0; b < 2; ++b) {
-      mbar_init(bar(C::K_FULL + b), 64);   // the lanes of the two K loaders (warps 5 and 7)
+      mbar_init(bar(C::K_FULL + b), 32);   // the loader's lanes
       mbar_init(bar(C::V_FULL + b), 32);
       mbar_init(bar(C::K_EMPTY + b), 1);   // tcgen05.commit
       mbar_init(bar(C::V_EMPTY + b), 1);
@@ -421,18 +419,6 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
     for (int row0 = 0; row0 < rows; row0 += C::ROWS) {
       if (warp >= 6) {
         // ================================================================ Q gather (64 threads)
-        // These two warps load K/V tiles afterwards (warp 6: V, warp 7: half of every gathered K tile) and keep the
-        // row ids for that in registers, two per lane; the first tile's ids are requested before the Q gather so
-        // that they are there when it ends.
-        auto fetch_ids = [&](int t, int (&dst)[2]) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int pos = t * C::TILE + lane + 32 * h;
-            dst[h] = pos < id_lim ? __ldg(p.kv_entries + kv_off + pos) : -1;
-          }
-        };
-        int cur[2] = {-1, -1}, nxt[2] = {-1, -1};
-        if (ntiles > 0) fetch_ids(0, cur);
         // request ids of this pass's slots -> the (still unused) P buffer, then the rows themselves
         const int qt = tid - 192, ld_c = qt & 15, ld_r = qt >> 4;
         const int row_end = min(rows, row0 + C::ROWS);
@@ -511,56 +497,20 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           mbar_arrive_on_cp_async(bar(C::Q_FULL));  // one arrival per thread once its copies have landed
           cp_async_wait<0>();
         }
-        if (warp == 7) {
-          // ============================================================== second K loader
-          // Makes the same dense test as warp 5 from its own copy of the row ids; on a tile that has to be gathered
-          // it copies rows 32..63 (warp 5: rows 0..31), on a TMA tile it only arrives.
-          const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)kvh * p.k_s1;
-          for (int t = 0; t < ntiles && !dead; ++t) {
-            if (t + 1 < ntiles) fetch_ids(t + 1, nxt);
-            const int g = g0 + t, b = g & 1;
-            bool dense = false;
-            if (tp.has_tma && (t + 1) * C::TILE <= id_lim) {
-              const int first_row = __shfl_sync(0xffffffffu, cur[0], 0);
-              const bool mine = cur[0] == first_row + lane && cur[1] == first_row + lane + 32;
-              dense = __all_sync(0xffffffffu, mine) && first_row >= 0 && (uint32_t)(first_row + C::TILE) <= row_lim;
-            }
-            // Both K loaders wait for the buffer and arrive on every tile, TMA tiles included: the full barrier
-            // needs both, so neither can run ahead of the other by more than one use of a buffer.
-            if (!tc_wait(bar(C::K_EMPTY + b), ((uint32_t)(g >> 1) & 1u) ^ 1u, abort_flag)) {
-              give_up();
-              break;
-            }
-            const uint32_t buf = k_buf(g), full = bar(C::K_FULL + b);
-            if (dense) {
-              mbar_arrive(full);
-            } else {
-              const int c = lane & 15;
-              bool bad = false, stored = false;
-#pragma unroll 4
-              for (int i = 0; i < 16; ++i) {
-                const int r = (lane >> 4) + 2 * i + 32, pos = t * C::TILE + r;  // row r: slot 1 of lane r & 31
-                const int id = __shfl_sync(0xffffffffu, cur[1], r & 31);
-                const uint32_t row = pos < id_lim ? (uint32_t)id : 0xffffffffu;
-                const bool ok = row < row_lim;
-                bad |= !ok && pos < id_lim;
-                stored |= !ok;
-                cp_async16(buf + tc_swz(r, c, 8192), kbase + (int64_t)(ok ? row : 0u) * p.k_s0 + c * 8, ok);
-              }
-              if (bad) flag_error(FT_DEV_BAD_KV_INDEX);
-              if (stored) proxy_fence();
-              mbar_arrive_on_cp_async(full);
-            }
-            cur[0] = nxt[0];
-            cur[1] = nxt[1];
-          }
-          cp_async_wait<0>();
-        }
         if (warp == 6) {
           // ============================================================== V loader (this warp, once Q is on its way)
           // Row ids live in registers, two per lane and one tile ahead, so this role shares nothing with the K
-          // loaders: same dense test (64 consecutive pool rows -> two TMA boxes), same gather otherwise.
+          // loader: same dense test (64 consecutive pool rows -> two TMA boxes), same gather otherwise.
           const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)kvh * p.v_s1;
+          auto fetch_ids = [&](int t, int (&dst)[2]) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int pos = t * C::TILE + lane + 32 * h;
+              dst[h] = pos < id_lim ? __ldg(p.kv_entries + kv_off + pos) : -1;
+            }
+          };
+          int cur[2] = {-1, -1}, nxt[2] = {-1, -1};
+          if (ntiles > 0) fetch_ids(0, cur);
           for (int t = 0; t < ntiles && !dead; ++t) {
             if (t + 1 < ntiles) fetch_ids(t + 1, nxt);
             const int g = g0 + t, b = g & 1;
@@ -636,7 +586,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           const int c = lane & 15;
           bool bad = false, stored = false;
 #pragma unroll 4
-          for (int i = 0; i < 16; ++i) {  // rows 0..31; warp 7 gathers rows 32..63 of the same tile
+          for (int i = 0; i < 32; ++i) {
             const int r = (lane >> 4) + 2 * i, pos = t * C::TILE + r;
             const uint32_t row = pos < id_lim ? (uint32_t)ids[r] : 0xffffffffu;
             const bool ok = row < row_lim;  // padding (0xffffffff), negative and too-large ids all fail this test
