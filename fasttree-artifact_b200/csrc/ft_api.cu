@@ -22,6 +22,46 @@ namespace {
 
 thread_local char g_err[512] = "";
 std::atomic<int64_t> g_launches{0};
+thread_local int64_t t_launches = 0;  // launches issued by this host thread
+
+void count_launch() {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  ++t_launches;
+}
+
+// ft_stage1_path_name walks the same selection code as ft_stage1 with launches switched off and collects the
+// names of the kernels that would have been launched.
+thread_local bool g_dry_run = false;
+thread_local char g_kernel_names[160] = "";
+
+bool dry_run(const char* kernel) {
+  if (!g_dry_run) return false;
+  const size_t used = strlen(g_kernel_names);
+  snprintf(g_kernel_names + used, sizeof(g_kernel_names) - used, "%s%s", used ? "+" : "", kernel);
+  return true;
+}
+
+// Largest dynamic shared memory of a kernel, raised once per device.  Several host threads may make their first
+// call at the same time: the flag is atomic and setting the attribute twice is harmless.
+struct OncePerDevice {
+  std::atomic<bool> done[64];
+  OncePerDevice() {
+    for (auto& d : done) d.store(false, std::memory_order_relaxed);
+  }
+};
+
+template <typename Kernel>
+cudaError_t raise_smem_limit(OncePerDevice& once, Kernel kernel, int bytes, int* device_out = nullptr) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (device_out != nullptr) *device_out = dev;
+  const bool tracked = dev >= 0 && dev < 64;
+  if (tracked && once.done[dev].load(std::memory_order_acquire)) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && tracked) once.done[dev].store(true, std::memory_order_release);
+  return e;
+}
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -148,68 +188,54 @@ ft::Stage1Params stage1_params(const ft_decode_args* a) {
 template <typename T, int D>
 int launch_mma(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
   using C = ft::MmaCfg<D>;
-  static bool configured[64] = {};
-  int dev = 0;
-  FT_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    FT_CUDA_OK(cudaFuncSetAttribute(ft::stage1_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    C::SMEM_BYTES));
-    if (dev >= 0 && dev < 64) configured[dev] = true;
-  }
+  if (dry_run("stage1_mma_kernel")) return FT_OK;
+  static OncePerDevice once;
+  FT_CUDA_OK(raise_smem_limit(once, ft::stage1_mma_kernel<T, D>, C::SMEM_BYTES));
   const unsigned grid = (unsigned)p.node_count * (unsigned)hkv;
   ft::stage1_mma_kernel<T, D><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(p);
   FT_CUDA_OK(cudaGetLastError());
-  g_launches.fetch_add(1, std::memory_order_relaxed);
+  count_launch();
   return FT_OK;
 }
 
 template <typename T, int D>
 int launch_narrow(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
   using C = ft::NarrowCfg<D, 2>;
-  static bool configured[64] = {};
-  int dev = 0;
-  FT_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    FT_CUDA_OK(cudaFuncSetAttribute(ft::stage1_narrow_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    C::SMEM_BYTES));
-    if (dev >= 0 && dev < 64) configured[dev] = true;
-  }
+  if (dry_run("stage1_narrow_kernel")) return FT_OK;
+  static OncePerDevice once;
+  FT_CUDA_OK(raise_smem_limit(once, ft::stage1_narrow_kernel<T, D>, C::SMEM_BYTES));
   const unsigned grid = (unsigned)p.node_count * (unsigned)hkv;
   ft::stage1_narrow_kernel<T, D><<<grid, 128, C::SMEM_BYTES, st>>>(p);
   FT_CUDA_OK(cudaGetLastError());
-  g_launches.fetch_add(1, std::memory_order_relaxed);
+  count_launch();
   return FT_OK;
 }
 
 int sm_count(int dev) {
-  static int sms[64] = {};
+  static std::atomic<int> sms[64];
   if (dev < 0 || dev >= 64) return 148;
-  if (sms[dev] == 0) {
-    int n = 0;
+  int n = sms[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    sms[dev] = n;
+    sms[dev].store(n, std::memory_order_relaxed);
   }
-  return sms[dev];
+  return n;
 }
 
 // Persistent few-row kernel: two CTAs per SM, each walking its share of the tasks.
 template <typename T, int D>
 int launch_stream(const ft::TcParams& tp, int hkv, cudaStream_t st) {
   using C = ft::StreamCfg<D>;
-  static bool configured[64] = {};
+  if (dry_run("stage1_stream_kernel")) return FT_OK;
+  static OncePerDevice once;
   int dev = 0;
-  FT_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    FT_CUDA_OK(cudaFuncSetAttribute(ft::stage1_stream_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    C::SMEM_BYTES));
-    if (dev >= 0 && dev < 64) configured[dev] = true;
-  }
+  FT_CUDA_OK(raise_smem_limit(once, ft::stage1_stream_kernel<T, D>, C::SMEM_BYTES, &dev));
   const int64_t tasks = (int64_t)tp.p.node_count * hkv;
   const int64_t slots = 2LL * sm_count(dev);
   const unsigned grid = (unsigned)(tasks < slots ? tasks : slots);
   ft::stage1_stream_kernel<T, D><<<grid, 128, C::SMEM_BYTES, st>>>(tp);
   FT_CUDA_OK(cudaGetLastError());
-  g_launches.fetch_add(1, std::memory_order_relaxed);
+  count_launch();
   return FT_OK;
 }
 
@@ -242,23 +268,34 @@ struct MapKey {
 };
 
 // Descriptor of a [rows, heads, head_dim] 16-bit tensor (element strides s0, s1), box 64 (head_dim) x box_heads x
-// box_rows, 128-byte swizzle.  Descriptors are cached by buffer identity; encoding one costs about a microsecond.
+// box_rows, 128-byte swizzle.  Descriptors are cached by buffer identity (encoding one costs about a microsecond)
+// in a hash table of 1024 slots, probed linearly over 8 slots; a full neighbourhood evicts its first slot.  A
+// serving process holds two descriptors per layer's K/V buffer plus two per query shape - a few hundred at most.
 bool tensor_map_3d(CUtensorMap* out, const void* base, int dtype, int head_dim, int64_t rows, int heads, int64_t s0,
                    int64_t s1, int box_heads, int box_rows) {
-  constexpr int SLOTS = 128;
+  constexpr int SLOTS = 1024, PROBES = 8;
   static std::mutex mu;
   static MapKey keys[SLOTS];
   static CUtensorMap maps[SLOTS];
-  static int used = 0, next = 0;
+  static bool used[SLOTS] = {};
   int device = -1;
   if (cudaGetDevice(&device) != cudaSuccess) return false;  // the same address can name different memory on two devices
   const MapKey key{base, rows, s0, s1, heads, dtype + 16 * head_dim, box_heads * 1024 + box_rows, device};
+  uint64_t h = reinterpret_cast<uintptr_t>(base) >> 8;
+  h = (h ^ (uint64_t)key.box_heads * 0x9E3779B97F4A7C15ull ^ (uint64_t)(device + 1) * 0xC2B2AE3D27D4EB4Full ^
+       (uint64_t)rows * 0x165667B19E3779F9ull) * 0xFF51AFD7ED558CCDull;
+  const int home = (int)(h >> 40) & (SLOTS - 1);
   std::lock_guard<std::mutex> lock(mu);
-  for (int i = 0; i < used; ++i)
-    if (keys[i] == key) {
-      *out = maps[i];
+  int slot = -1;
+  for (int i = 0; i < PROBES; ++i) {
+    const int j = (home + i) & (SLOTS - 1);
+    if (used[j] && keys[j] == key) {
+      *out = maps[j];
       return true;
     }
+    if (!used[j] && slot < 0) slot = j;
+  }
+  if (slot < 0) slot = home;
   EncodeTiledFn enc = encode_tiled_fn();
   if (enc == nullptr || rows <= 0 || rows > 0x7fffffffLL || heads <= 0) return false;
   const cuuint64_t dims[3] = {(cuuint64_t)head_dim, (cuuint64_t)heads, (cuuint64_t)rows};
@@ -271,9 +308,9 @@ bool tensor_map_3d(CUtensorMap* out, const void* base, int dtype, int head_dim, 
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) return false;
-  const int slot = used < SLOTS ? used++ : (next++ % SLOTS);
   keys[slot] = key;
   maps[slot] = m;
+  used[slot] = true;
   *out = m;
   return true;
 }
@@ -302,17 +339,13 @@ ft::TcParams tc_params(const ft::Stage1Params& p, const ft_decode_args* a) {
 template <typename T>
 int launch_tc(const ft::TcParams& p, int hkv, cudaStream_t st) {
   using C = ft::TcCfg;
-  static bool configured[64] = {};
-  int dev = 0;
-  FT_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    FT_CUDA_OK(cudaFuncSetAttribute(ft::stage1_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    if (dev >= 0 && dev < 64) configured[dev] = true;
-  }
+  if (dry_run("stage1_tc_kernel")) return FT_OK;
+  static OncePerDevice once;
+  FT_CUDA_OK(raise_smem_limit(once, ft::stage1_tc_kernel<T>, C::SMEM_BYTES));
   const unsigned grid = (unsigned)p.p.node_count * (unsigned)hkv;
   ft::stage1_tc_kernel<T><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(p);
   FT_CUDA_OK(cudaGetLastError());
-  g_launches.fetch_add(1, std::memory_order_relaxed);
+  count_launch();
   return FT_OK;
 }
 
@@ -322,13 +355,10 @@ int launch_fused(ft::TcParams p, int hkv, cudaStream_t st) {
                                                                                 : ft::StreamCfg<128>::SMEM_BYTES;
   constexpr int smem = smem_a > ft::NarrowCfg<128, 2>::SMEM_BYTES ? smem_a : ft::NarrowCfg<128, 2>::SMEM_BYTES;
   static_assert(smem <= 115712, "two CTAs must fit in one SM's shared memory");
-  static bool configured[64] = {};
+  if (dry_run("stage1_fused_kernel")) return FT_OK;
+  static OncePerDevice once;
   int dev = 0;
-  FT_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    FT_CUDA_OK(cudaFuncSetAttribute(ft::stage1_fused_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    if (dev >= 0 && dev < 64) configured[dev] = true;
-  }
+  FT_CUDA_OK(raise_smem_limit(once, ft::stage1_fused_kernel<T>, smem, &dev));
   // Few-row tasks: a full set of persistent workers when each would get several tasks and the many-row CTAs
   // do not fill the device more than once (the task pipeline then hides the per-task start-up; the workers
   // take the slots the many-row CTAs leave and, as those finish, theirs too); one CTA per task otherwise (the
@@ -348,7 +378,7 @@ int launch_fused(ft::TcParams p, int hkv, cudaStream_t st) {
   p.p.lead_wide = (int)lead;
   ft::stage1_fused_kernel<T><<<(unsigned)(wide + few_ctas), ft::TcCfg::THREADS, smem, st>>>(p);
   FT_CUDA_OK(cudaGetLastError());
-  g_launches.fetch_add(1, std::memory_order_relaxed);
+  count_launch();
   return FT_OK;
 }
 
@@ -374,10 +404,11 @@ int launch_tensor(const ft::Stage1Params& p, const ft_decode_args* a, int hkv, c
 
 template <typename T>
 int launch_generic(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
+  if (dry_run("stage1_generic_kernel")) return FT_OK;
   dim3 grid(p.node_count, hkv);
   ft::stage1_generic_kernel<T><<<grid, 128, 0, st>>>(p);
   FT_CUDA_OK(cudaGetLastError());
-  g_launches.fetch_add(1, std::memory_order_relaxed);
+  count_launch();
   return FT_OK;
 }
 
@@ -403,8 +434,12 @@ int launch_stage1_range(const ft_decode_args* a, int path, int offset, int count
   }
 }
 
+// after_stage1: this launch directly follows a stage-1 launch of the same call on the same stream.  Only then may
+// the kernel be scheduled early (programmatic dependent launch): it reads the request tables before it waits for
+// the preceding kernel, which is safe after stage 1 (that kernel never writes them) but not after an arbitrary
+// kernel of the caller's that may still be building those tables.
 template <typename T>
-int launch_stage2(const ft::Stage2Params& p, cudaStream_t st) {
+int launch_stage2(const ft::Stage2Params& p, cudaStream_t st, bool after_stage1) {
   const int64_t pairs = (int64_t)p.batch * p.heads;
   if (pairs == 0) return FT_OK;
   const int64_t blocks = (pairs + 3) / 4;
@@ -420,12 +455,12 @@ int launch_stage2(const ft::Stage2Params& p, cudaStream_t st) {
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = after_stage1 ? 1 : 0;
   if (p.head_dim <= 128)
     FT_CUDA_OK(cudaLaunchKernelEx(&cfg, ft::stage2_merge_kernel<T, 1>, p));
   else
     FT_CUDA_OK(cudaLaunchKernelEx(&cfg, ft::stage2_merge_kernel<T, 2>, p));
-  g_launches.fetch_add(1, std::memory_order_relaxed);
+  count_launch();
   return FT_OK;
 }
 
@@ -450,18 +485,12 @@ const char* ft_last_error(void) { return g_err; }
 int64_t ft_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 const char* ft_stage1_path_name(const ft_decode_args* args) {
-  int rc = check_common(args);
+  g_kernel_names[0] = '\0';
+  g_dry_run = true;
+  const int rc = ft_stage1(args);
+  g_dry_run = false;
   if (rc != FT_OK) return nullptr;
-  const int path = pick_path(args);
-  if (path < 0) return nullptr;
-  switch (path) {
-    case FT_PATH_AUTO: return args->head_dim == 128 ? "narrow+tcgen05" : "narrow+mma";
-    case FT_PATH_MMA: return "narrow+mma";
-    case FT_PATH_MMA_WIDE: return "mma_wide";
-    case FT_PATH_TCGEN05: return "tcgen05";
-    case FT_PATH_STREAM: return args->head_dim == 128 ? "stream+tcgen05" : "stream+mma";
-    default: return "generic";
-  }
+  return g_kernel_names;
 }
 
 int ft_stage1(const ft_decode_args* a) {
@@ -499,7 +528,8 @@ int ft_stage1(const ft_decode_args* a) {
   return launch_stage1_range(a, path, o1, n1, rows1);
 }
 
-int ft_stage2(const ft_decode_args* a) {
+namespace {
+int stage2_impl(const ft_decode_args* a, bool after_stage1) {
   int rc = check_common(a);
   if (rc != FT_OK) return rc;
   if (a->o == nullptr) return fail(FT_ERR_INVALID_ARGUMENT, "o is NULL");
@@ -531,16 +561,42 @@ int ft_stage2(const ft_decode_args* a) {
   }
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
   switch (a->dtype) {
-    case FT_F16: return launch_stage2<__half>(p, st);
-    case FT_BF16: return launch_stage2<__nv_bfloat16>(p, st);
-    default: return launch_stage2<float>(p, st);
+    case FT_F16: return launch_stage2<__half>(p, st, after_stage1);
+    case FT_BF16: return launch_stage2<__nv_bfloat16>(p, st, after_stage1);
+    default: return launch_stage2<float>(p, st, after_stage1);
   }
 }
+}  // namespace
+
+int ft_stage2(const ft_decode_args* a) { return stage2_impl(a, false); }
 
 int ft_decode(const ft_decode_args* a) {
+  const int64_t before = t_launches;
   int rc = ft_stage1(a);
   if (rc != FT_OK) return rc;
-  return ft_stage2(a);
+  // a plan without vnodes launches no stage 1: stage 2 then follows whatever the caller enqueued before
+  const bool launched = t_launches != before;
+  return stage2_impl(a, launched);
+}
+
+int ft_decode_host_io(const ft_decode_args* a, const void* q_host, void* o_host, int wait) {
+  if (a == nullptr) return fail(FT_ERR_INVALID_ARGUMENT, "args is NULL");
+  if (q_host == nullptr || o_host == nullptr) return fail(FT_ERR_INVALID_ARGUMENT, "q_host / o_host is NULL");
+  if (a->q == nullptr || a->o == nullptr) return fail(FT_ERR_INVALID_ARGUMENT, "q / o (device staging buffers) is NULL");
+  if (a->batch < 0 || a->num_qo_heads <= 0 || a->head_dim <= 0)
+    return fail(FT_ERR_INVALID_ARGUMENT, "batch / num_qo_heads / head_dim must be positive");
+  const int64_t row = (int64_t)a->num_qo_heads * a->head_dim;
+  if (a->q_stride1 != a->head_dim || a->q_stride0 != row || a->o_stride1 != a->head_dim || a->o_stride0 != row)
+    return fail(FT_ERR_UNSUPPORTED, "ft_decode_host_io needs packed [batch, heads, head_dim] device q and o");
+  const size_t esz = a->dtype == FT_F32 ? 4 : 2;
+  const size_t bytes = (size_t)a->batch * (size_t)row * esz;
+  cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+  if (bytes > 0) FT_CUDA_OK(cudaMemcpyAsync(const_cast<void*>(a->q), q_host, bytes, cudaMemcpyHostToDevice, st));
+  const int rc = ft_decode(a);
+  if (rc != FT_OK) return rc;
+  if (bytes > 0) FT_CUDA_OK(cudaMemcpyAsync(o_host, a->o, bytes, cudaMemcpyDeviceToHost, st));
+  if (wait) FT_CUDA_OK(cudaStreamSynchronize(st));
+  return FT_OK;
 }
 
 // ---- ft_decode_static_scratch: partial-result scratch in a fixed device array owned by the library ----------
@@ -588,7 +644,51 @@ int ft_bump_kv_lens(int32_t* vnode_to_kv_lens, const int32_t* last_vnodes, int32
     return fail(FT_ERR_INVALID_ARGUMENT, "vnode_to_kv_lens / last_vnodes is NULL");
   bump_kv_lens_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(vnode_to_kv_lens, last_vnodes, n);
   FT_CUDA_OK(cudaGetLastError());
-  g_launches.fetch_add(1, std::memory_order_relaxed);
+  count_launch();
+  return FT_OK;
+}
+
+namespace {
+// One warp waits on an mbarrier that nothing ever arrives at, through the same bounded waits the stage-1 kernels
+// use.  No copy, no MMA and no tensor memory is involved, so a wait that runs out leaves nothing in flight.
+__global__ void bounded_wait_selftest_kernel(int limit, int* result) {
+  __shared__ __align__(8) unsigned long long barrier_word;
+  __shared__ int abort_word;
+  const uint32_t bar = ft::smem_u32(&barrier_word);
+  if (threadIdx.x == 0) {
+    ft::mbar_init(bar, 1);
+    abort_word = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+  // (1) the plain bounded wait of the persistent workers: gives up after `limit` probes
+  const bool plain = ft::mbar_wait(bar, 0, limit);
+  // (2) the tcgen05 kernel's wait: same limit semantics (its own constant), and it leaves early once a sibling
+  // role has raised the CTA's abort flag - raised here by lane 0 before the call
+  if (threadIdx.x == 0) abort_word = 1;
+  __syncthreads();
+  const bool aborted = ft::tc_wait(bar, 0, &abort_word);
+  if (threadIdx.x == 0) {
+    if (!plain || !aborted) ft::flag_error(FT_DEV_WAIT_TIMEOUT);  // what the kernels do when a wait runs out
+    result[0] = plain ? 1 : 0;
+    result[1] = aborted ? 1 : 0;
+  }
+}
+}  // namespace
+
+int ft_selftest_bounded_wait(int limit, int* result_host, void* stream) {
+  if (result_host == nullptr) return fail(FT_ERR_INVALID_ARGUMENT, "result_host is NULL");
+  if (limit < 1 || limit > (1 << 20)) return fail(FT_ERR_INVALID_ARGUMENT, "limit must be in [1, 2^20] probes");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int* dev = nullptr;
+  FT_CUDA_OK(cudaMalloc(&dev, 2 * sizeof(int)));
+  bounded_wait_selftest_kernel<<<1, 32, 0, st>>>(limit, dev);
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaMemcpyAsync(result_host, dev, 2 * sizeof(int), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  cudaFree(dev);
+  if (e != cudaSuccess) return fail(FT_ERR_CUDA, "bounded-wait self-test failed: %s", cudaGetErrorString(e));
+  count_launch();
   return FT_OK;
 }
 

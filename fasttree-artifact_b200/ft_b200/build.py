@@ -23,19 +23,37 @@ def _nvcc():
     return exe
 
 
+STAMP_PATH = LIB_PATH + ".srchash"
+
+
+def _source_digest():
+    """SHA-256 over the names and contents of every file the library is built from.  Content, not time stamps:
+    a copy of the tree (another machine, a container snapshot) keeps no usable modification times."""
+    import hashlib
+    h = hashlib.sha256()
+    for folder in (CSRC, INCLUDE):
+        for name in sorted(os.listdir(folder)):
+            if name.endswith((".cu", ".cuh", ".h")):
+                h.update(name.encode())
+                with open(os.path.join(folder, name), "rb") as fh:
+                    h.update(fh.read())
+    h.update(os.environ.get("FT_B200_NVCC_FLAGS", "").encode())
+    return h.hexdigest()
+
+
 def _stale():
-    if not os.path.exists(LIB_PATH):
+    """True when the library is missing or was built from other sources than the ones in the tree."""
+    if not os.path.exists(LIB_PATH) or not os.path.exists(STAMP_PATH):
         return True
-    built = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + \
-           [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE)]
-    return any(os.path.getmtime(d) > built for d in deps)
+    with open(STAMP_PATH) as fh:
+        return fh.read().strip() != _source_digest()
 
 
 def build_library(force=False, verbose=False):
     """Compile every CUDA source for sm_100a into one shared library."""
     if not force and not _stale():
         return LIB_PATH
+    digest = _source_digest()
     cmd = [_nvcc(), "-shared", "-Xcompiler", "-fPIC", "-O3", "-std=c++17", "-lineinfo",
            "-gencode", "arch=compute_100a,code=sm_100a",
            "-I", INCLUDE, "-I", CSRC, "-o", LIB_PATH]
@@ -49,6 +67,8 @@ def build_library(force=False, verbose=False):
         print(res.stdout)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout)
+    with open(STAMP_PATH, "w") as fh:
+        fh.write(digest + "\n")
     return LIB_PATH
 
 

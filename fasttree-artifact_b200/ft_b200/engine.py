@@ -41,25 +41,68 @@ def _pair(name, x):
     return int(x[0]), int(x[1])
 
 
-def attach_row_ranges(vnode_to_q_entries, ranges):
+ROW_RANGE_MAGIC = 0x46545252          # "FTRR": trailer of a vnode_to_q_entries table that carries row ranges
+
+_RANGE_CACHE = {}
+_RANGE_CACHE_MAX = 64
+
+
+def pack_row_ranges(q_entries, ranges):
     """The B200 plan format's optional tenth table - per partial row the tokens
     ``[begin, end)`` of its vnode's KV chunk that the row attends to (int32
-    ``[rows, 2]``) - has no slot in the reference's 13-entry tuple, so it rides on
-    the ``vnode_to_q_entries`` tensor object it is parallel to."""
-    vnode_to_q_entries.ft_row_ranges = ranges
-    return vnode_to_q_entries
+    ``[rows, 2]``) - has no slot in the reference's 13-entry tuple.  It travels
+    INSIDE the ``vnode_to_q_entries`` table it is parallel to:
+
+        [ R request ids | 2R range entries | ROW_RANGE_MAGIC, R ]
+
+    so that clone(), .to(), .contiguous(), pickling or rebuilding the tuple keep it.
+    Takes and returns numpy int32 arrays."""
+    import numpy as np
+    rows = int(q_entries.shape[0])
+    if ranges.shape != (rows, 2):
+        raise ValueError("the row-range table needs two entries per partial row")
+    tail = np.array([ROW_RANGE_MAGIC, rows], dtype=np.int32)
+    return np.ascontiguousarray(np.concatenate([q_entries.astype(np.int32), ranges.astype(np.int32).ravel(), tail]))
+
+
+def split_q_entries(vnode_to_q_entries):
+    """``(rows, ranges)`` of a vnode_to_q_entries table: the number of partial rows it
+    names and a ``[rows, 2]`` view of the row ranges packed behind them (None for
+    a table in the reference's format).  Recognising the trailer reads two
+    integers back from the device; the answer is remembered per (storage,
+    length, version) of the tensor, so a steady decode loop does not repeat it.
+    The first call on a new table therefore synchronises with the device and
+    must not fall inside a CUDA graph capture."""
+    t = vnode_to_q_entries
+    n = t.numel()
+    if n < 5 or (n - 2) % 3 != 0:
+        return n, None
+    key = (t.data_ptr(), n, t._version, t.device.index)
+    hit = _RANGE_CACHE.get(key)
+    if hit is None:
+        magic, rows = t.view(-1)[-2:].tolist()
+        hit = rows if (magic == ROW_RANGE_MAGIC and 3 * rows + 2 == n) else -1
+        if len(_RANGE_CACHE) >= _RANGE_CACHE_MAX:
+            _RANGE_CACHE.clear()
+        _RANGE_CACHE[key] = hit
+    if hit < 0:
+        return n, None
+    return hit, t.view(-1)[hit:3 * hit].view(hit, 2)
 
 
 def row_ranges_of(vnode_to_q_entries):
-    return getattr(vnode_to_q_entries, "ft_row_ranges", None)
+    return split_q_entries(vnode_to_q_entries)[1]
 
 
 def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, vnode_to_kv_lens,
                vnode_to_q_entries, vnode_to_q_offs, vnode_to_q_lens, req_to_vnode_entries,
                req_to_vnode_offs, req_to_vnode_lens, mid_o, mid_lse, phase_node_nums, phase_node_offsets,
                phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap=-1, path="auto", o_lse=None,
-               stream=None):
-    """Validate the tensors and fill a :class:`DecodeArgs` struct."""
+               stream=None, row_ranges="detect"):
+    """Validate the tensors and fill a :class:`DecodeArgs` struct.  ``row_ranges``:
+    ``"detect"`` looks for ranges packed into ``vnode_to_q_entries`` (see
+    :func:`pack_row_ranges`), ``None`` says the plan has none (no look-up, no
+    device read), a tensor gives the table explicitly."""
     for name, t in (("q", q), ("k_buffer", k_buffer), ("v_buffer", v_buffer), ("o", o),
                     ("mid_o", mid_o), ("mid_lse", mid_lse)):
         _require_cuda(name, t)
@@ -108,10 +151,16 @@ def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, 
     if path not in _lib.PATHS:
         raise ValueError(f"path must be one of {sorted(_lib.PATHS)}")
 
-    ranges = row_ranges_of(vnode_to_q_entries)
+    q_rows = vnode_to_q_entries.numel()
+    if isinstance(row_ranges, str):
+        if row_ranges != "detect":
+            raise ValueError("row_ranges must be 'detect', None or an int32 tensor")
+        q_rows, ranges = split_q_entries(vnode_to_q_entries)
+    else:
+        ranges = row_ranges
     if ranges is not None:
         _table("row ranges", ranges)
-        if ranges.numel() < 2 * vnode_to_q_entries.numel():
+        if ranges.numel() < 2 * q_rows:
             raise ValueError("the row-range table needs two entries per partial row")
 
     a = _lib.DecodeArgs()
@@ -131,7 +180,7 @@ def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, 
      a.vnode_to_q_offs, a.vnode_to_q_lens, a.req_to_vnode_entries, a.req_to_vnode_offs,
      a.req_to_vnode_lens) = [t.data_ptr() for t in tabs]
     a.kv_entries_len = vnode_to_kv_entries.numel()
-    a.num_partial_rows = min(mid_o.shape[0], mid_lse.shape[0], vnode_to_q_entries.numel())
+    a.num_partial_rows = min(mid_o.shape[0], mid_lse.shape[0], q_rows)
     a.phase_node_nums[0], a.phase_node_nums[1] = n0, n1
     a.phase_node_offsets[0], a.phase_node_offsets[1] = f0, f1
     a.phase_q_tile_sizes[0], a.phase_q_tile_sizes[1] = _pair("phase_q_tile_sizes", phase_q_tile_sizes)
@@ -145,38 +194,57 @@ def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, 
     return a
 
 
-def _cached_args(tensors, rest, path, o_lse):
+def _cached_args(tensors, rest, path, o_lse, row_ranges):
     """Argument structs are memoised so that a steady-state decode loop pays for
-    one dict lookup and a pointer check instead of rebuilding ~45 fields.  The key
-    is the identity of the tensor objects (kept alive by the cache entry, so an id
-    cannot be recycled) plus the scalar arguments; on a hit the data pointers are
-    compared with the cached ones, which catches storage that was re-allocated
-    behind the same tensor object.  Shapes and strides of a tensor object are
-    assumed not to change in place."""
-    q = tensors[0]
+    one dict lookup and a few pointer stores instead of rebuilding ~45 fields.
+    The key names only what persists across calls - the K/V buffers, the plan
+    tables and the partial buffers (by tensor identity; the entry keeps them
+    alive, so an id cannot be recycled) - plus the scalar arguments and the
+    layout of ``q`` / ``o``.  ``q``, ``o`` and ``o_lse`` are new tensor objects
+    on every layer and step of a serving loop: their addresses are written into
+    the cached struct on each call and the cache holds no reference to them.  On
+    a hit the data pointers of the persistent tensors are compared with the
+    cached ones, which catches storage re-allocated behind the same object."""
+    q, k_buffer, v_buffer, o = tensors[:4]
+    persistent = tensors[1:3] + tensors[4:]
     stream = torch.cuda.current_stream(q.device).cuda_stream
     (pn, po, pq, pk, sm_scale, logit_cap) = rest
-    key = (tuple(map(id, tensors)), pn[0], pn[1], po[0], po[1], pq[0], pq[1], pk[0], pk[1], sm_scale, logit_cap,
-           path, id(o_lse), stream, id(row_ranges_of(tensors[7])))
-    ptrs = tuple([t.data_ptr() for t in tensors])
+    is_detect = isinstance(row_ranges, str)
+    ranges_key = row_ranges if is_detect or row_ranges is None else id(row_ranges)
+    key = (tuple(map(id, persistent)), pn[0], pn[1], po[0], po[1], pq[0], pq[1], pk[0], pk[1], sm_scale, logit_cap,
+           path, stream, ranges_key, q.shape, q.stride(), q.dtype, o.shape, o.stride(), o.dtype, o_lse is None)
+    ptrs = tuple([t.data_ptr() for t in persistent])
     hit = _ARG_CACHE.get(key)
-    if hit is not None and hit[1] == ptrs:
-        return hit[0]
-    a = build_args(*tensors, pn, po, pq, pk, sm_scale, logit_cap, path=path, o_lse=o_lse, stream=stream)
-    if len(_ARG_CACHE) >= _ARG_CACHE_MAX:
-        _ARG_CACHE.clear()
-    _ARG_CACHE[key] = (a, ptrs, tensors, o_lse, row_ranges_of(tensors[7]))
+    if hit is not None and hit[1] == ptrs and (not is_detect or hit[3] == tensors[7]._version):
+        a = hit[0]
+        if not (q.is_cuda and o.is_cuda):
+            raise ValueError("q / o must live on a CUDA device; the engine has no CPU path")
+    else:
+        a = build_args(*tensors, pn, po, pq, pk, sm_scale, logit_cap, path=path, o_lse=o_lse, stream=stream,
+                       row_ranges=row_ranges)
+        if len(_ARG_CACHE) >= _ARG_CACHE_MAX:
+            _ARG_CACHE.clear()
+        keep = row_ranges if isinstance(row_ranges, torch.Tensor) else None
+        _ARG_CACHE[key] = (a, ptrs, persistent, tensors[7]._version, keep)
+    a.q, a.o = q.data_ptr(), o.data_ptr()
+    if o_lse is not None:
+        if (not o_lse.is_cuda or o_lse.dtype != torch.float32 or not o_lse.is_contiguous()
+                or o_lse.numel() < q.shape[0] * q.shape[1]):
+            raise ValueError("o_lse must be a contiguous float32 [batch, heads] CUDA tensor")
+        a.o_lse = o_lse.data_ptr()
+    else:
+        a.o_lse = None
     return a
 
 
 def _call(fn_name, q, k_buffer, v_buffer, o, kv_entries, kv_offs, kv_lens, q_entries, q_offs, q_lens,
           r2v_entries, r2v_offs, r2v_lens, mid_o, mid_lse, phase_node_nums, phase_node_offsets,
-          phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap, path, o_lse):
+          phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap, path, o_lse, row_ranges="detect"):
     tensors = (q, k_buffer, v_buffer, o, kv_entries, kv_offs, kv_lens, q_entries, q_offs, q_lens,
                r2v_entries, r2v_offs, r2v_lens, mid_o, mid_lse)
     rest = (phase_node_nums, phase_node_offsets, phase_q_tile_sizes, phase_kv_tile_sizes,
             float(sm_scale), float(logit_cap))
-    a = _cached_args(tensors, rest, path, o_lse)
+    a = _cached_args(tensors, rest, path, o_lse, row_ranges)
     lib = _lib.load()
     if q.device.index != torch.cuda.current_device():
         with torch.cuda.device(q.device):
@@ -186,18 +254,18 @@ def _call(fn_name, q, k_buffer, v_buffer, o, kv_entries, kv_offs, kv_lens, q_ent
     _lib.check(rc)
 
 
-def decode(*args, logit_cap=-1, path="auto", o_lse=None):
+def decode(*args, logit_cap=-1, path="auto", o_lse=None, row_ranges="detect"):
     """Stage 1 + stage 2.  Positional arguments are those of the reference's
     ``fasttree_decode`` up to and including ``sm_scale``."""
-    _call("ft_decode", *args, logit_cap, path, o_lse)
+    _call("ft_decode", *args, logit_cap, path, o_lse, row_ranges)
 
 
-def stage1(*args, logit_cap=-1, path="auto"):
-    _call("ft_stage1", *args, logit_cap, path, None)
+def stage1(*args, logit_cap=-1, path="auto", row_ranges="detect"):
+    _call("ft_stage1", *args, logit_cap, path, None, row_ranges)
 
 
 def stage2(*args, logit_cap=-1, o_lse=None):
-    _call("ft_stage2", *args, logit_cap, "auto", o_lse)
+    _call("ft_stage2", *args, logit_cap, "auto", o_lse, None)
 
 
 def stage1_path_name(*args, logit_cap=-1, path="auto"):

@@ -20,7 +20,7 @@ FT_STATIC_SCRATCH_BYTES = 16 << 20      # capacity of the array behind ft_decode
 FT_DEV_BAD_KV_INDEX, FT_DEV_BAD_Q_INDEX, FT_DEV_BAD_ROW_INDEX, FT_DEV_WAIT_TIMEOUT = 1, 2, 4, 8
 
 EXPORTS = ["ft_version", "ft_decode_args_size", "ft_last_error", "ft_decode", "ft_stage1", "ft_stage2",
-           "ft_decode_static_scratch", "ft_bump_kv_lens",
+           "ft_decode_static_scratch", "ft_decode_host_io", "ft_selftest_bounded_wait", "ft_bump_kv_lens",
            "ft_read_device_status", "ft_launch_count", "ft_stage1_path_name",
            "ft_plan_b200_build", "ft_plan_b200_build_direct", "ft_plan_get_info", "ft_plan_copy_tables", "ft_plan_copy_row_ranges",
            "ft_plan_free"]
@@ -91,7 +91,9 @@ def library_path():
 
 
 def load():
-    """Load (building first if the sources are newer) and declare the C ABI."""
+    """Load the library and declare the C ABI.  It is built first when it is missing or older than any of its
+    sources (and nvcc is there to build it); a stale library that cannot be rebuilt is an error, not a silent
+    run of old kernels."""
     global _lib
     if _lib is not None:
         return _lib
@@ -99,11 +101,12 @@ def load():
         if _lib is not None:
             return _lib
         path = _build.LIB_PATH
-        if not os.path.exists(path) or os.environ.get("FT_B200_REBUILD") == "1":
+        if _build._stale() or os.environ.get("FT_B200_REBUILD") == "1":
             try:
                 _build.build_library(force=True)
             except Exception as exc:  # no nvcc, or the compile failed
-                raise FastTreeError(-3, f"libfasttree_b200.so is missing and could not be built: {exc}") from exc
+                state = "missing" if not os.path.exists(path) else "older than its sources"
+                raise FastTreeError(-3, f"libfasttree_b200.so is {state} and could not be built: {exc}") from exc
         try:
             lib = ctypes.CDLL(path)
         except OSError as exc:
@@ -119,6 +122,10 @@ def load():
             fn = getattr(lib, name)
             fn.argtypes = [argp]
             fn.restype = ctypes.c_int
+        lib.ft_decode_host_io.argtypes = [argp, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
+        lib.ft_decode_host_io.restype = ctypes.c_int
+        lib.ft_selftest_bounded_wait.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_void_p]
+        lib.ft_selftest_bounded_wait.restype = ctypes.c_int
         lib.ft_bump_kv_lens.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]
         lib.ft_bump_kv_lens.restype = ctypes.c_int
         lib.ft_read_device_status.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]

@@ -93,11 +93,12 @@ def fasttree_preparation(tree_info, KV_ptrs, batch_size, num_qo_heads, num_kv_he
     dev = torch.device(device)
     if dev.type != "cuda":
         raise ValueError("fasttree_preparation uploads to a CUDA device; the engine has no CPU path")
-    tabs = tuple(torch.from_numpy(t).to(dev) for t in plan.tables())
+    host = list(plan.tables())
     if plan.vnode_q_kv_ranges is not None:
         # groups of short nodes (B200 splitter only): the per-row token ranges have no slot in the reference's
-        # tuple and travel on the vnode_to_q_entries tensor they are parallel to
-        _engine.attach_row_ranges(tabs[3], torch.from_numpy(plan.vnode_q_kv_ranges).to(dev))
+        # tuple and travel inside the vnode_to_q_entries table, behind the request ids (engine.pack_row_ranges)
+        host[3] = _engine.pack_row_ranges(host[3], plan.vnode_q_kv_ranges)
+    tabs = tuple(torch.from_numpy(t).to(dev) for t in host)
     rows = plan.num_partial_rows
     mid_o = torch.empty((rows, num_qo_heads, head_dim), dtype=torch.float32, device=dev)
     mid_lse = torch.empty((rows, num_qo_heads), dtype=torch.float32, device=dev)

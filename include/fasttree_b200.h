@@ -139,8 +139,19 @@ int ft_decode(const ft_decode_args* args);
 int ft_stage1(const ft_decode_args* args);
 
 /* Log-sum-exp merge of each request's partial rows into o (and o_lse).
- * Replaces _fasttree_decode_stage2 (kernel_bench/fasttree.py:549-579). */
+ * Replaces _fasttree_decode_stage2 (kernel_bench/fasttree.py:549-579).
+ * Called on its own it is an ordinary launch, ordered after everything enqueued on the stream before it;
+ * inside ft_decode it is launched as a programmatic dependent of stage 1. */
 int ft_stage2(const ft_decode_args* args);
+
+/* ft_decode fed from and drained to pinned host memory in one call: q_host ([batch, heads, head_dim], packed) is
+ * copied to args->q, the decode runs, args->o is copied to o_host, all on args->stream with one cudaMemcpyAsync
+ * per buffer; wait != 0 also synchronises the stream before returning.  args->q and args->o are device staging
+ * buffers and must be packed.  This is the call pattern of a decode loop whose sampler runs on the host: the
+ * reference's harness does the same with two torch copies around fasttree_decode
+ * (kernel_bench/benchmark.py:88-128 keeps Q and the output on the device; its SGLang host reads the logits back
+ * once per step). */
+int ft_decode_host_io(const ft_decode_args* args, const void* q_host, void* o_host, int wait);
 
 /* ft_decode for callers that cannot provide (or allocate) the mid_o / mid_lse scratch.  It has no counterpart
  * in the reference, whose planner and plugin always allocate those buffers with torch
@@ -153,7 +164,7 @@ int ft_stage2(const ft_decode_args* args);
  * everything else is as in ft_decode.  The call allocates nothing: no cudaMalloc, no cudaFree, no allocating
  * library routine.
  *
- * Limit: num_partial_rows * num_qo_heads * (head_dim + 1) * 4 bytes must fit in the array (e.g. 1015 partial
+ * Limit: num_partial_rows * num_qo_heads * (head_dim + 1) * 4 bytes must fit in the array (e.g. 1016 partial
  * rows at 32 heads x 128); larger plans get FT_ERR_TOO_LARGE and must use ft_decode.
  * Set-up: the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
  * device current); make that first call before any stream capture begins.
@@ -174,11 +185,20 @@ int ft_bump_kv_lens(int32_t* vnode_to_kv_lens, const int32_t* last_vnodes, int32
  * instead of faulting. */
 int ft_read_device_status(void* stream, int32_t* flags);
 
+/* Runs one warp through the bounded mbarrier waits of the stage-1 kernels on a barrier nothing arrives at
+ * (limit = probes before the plain wait gives up, 1 .. 2^20) and synchronises.  result_host[0] / [1] receive what
+ * the plain wait and the abortable wait returned (0 = gave up, the expected answer); the kernel then raises
+ * FT_DEV_WAIT_TIMEOUT in the device status word, as a stage-1 kernel whose wait ran out does.  No copy engine, tensor
+ * core or tensor memory is used.  A health check for the failure-detection path; no counterpart in the reference. */
+int ft_selftest_bounded_wait(int limit, int* result_host, void* stream);
+
 /* Number of kernels this library has launched from the calling process. */
 int64_t ft_launch_count(void);
 
-/* Name of the stage-1 kernel family ft_stage1 would use for these arguments
- * ("generic", "mma", "tcgen05"), or NULL with ft_last_error() set. */
+/* Names of the kernels ft_stage1 would launch for these arguments, joined by '+' when there are two launches
+ * (e.g. "stage1_fused_kernel", "stage1_tc_kernel+stage1_narrow_kernel"): the names a profiler shows.  Nothing is
+ * launched.  NULL with ft_last_error() set when the arguments are rejected.  The text belongs to the calling
+ * thread and is valid until its next call. */
 const char* ft_stage1_path_name(const ft_decode_args* args);
 
 /* ---- host-side planner -------------------------------------------------------------------------------------

@@ -139,7 +139,8 @@ def test_edge_shapes_against_oracle(spec, dtype):
             np.testing.assert_allclose(run.o_lse.cpu().numpy(), truth_lse.numpy(), rtol=1e-4, atol=2e-5)
             # stage-1 partials against the oracle's per-vnode restatement on the very same plan
             tabs = [t.cpu().numpy() for t in run.aux[:6]]
-            ranges = engine.row_ranges_of(run.aux[3])     # B200 plans that group short nodes
+            rows, ranges = engine.split_q_entries(run.aux[3])     # B200 plans that group short nodes carry ranges
+            tabs[3] = tabs[3][:rows]
             mid_o, mid_lse = ref_attention.stage1_partials(
                 c["q"], c["k"], c["v"], *tabs, scale, q_ranges=None if ranges is None else ranges.cpu().numpy())
             np.testing.assert_allclose(run.mid_lse.cpu().numpy(), mid_lse.numpy(), rtol=1e-4, atol=2e-5)
@@ -154,8 +155,8 @@ def test_short_nodes_run_as_groups_with_row_ranges(spec):
     sizes, lens, hq, hkv, d = spec
     c = adhoc(sizes, lens, hq, hkv, d, torch.float16, seed=11, q_scale=0.5)
     grouped = gpu_utils.EngineRun(c["nodes"], c["ptrs"], c["batch"], c["q"], c["k"], c["v"], hq, hkv, d, c["tsq"])
-    ranges = engine.row_ranges_of(grouped.aux[3])
-    assert ranges is not None and tuple(ranges.shape) == (grouped.aux[3].numel(), 2)
+    rows, ranges = engine.split_q_entries(grouped.aux[3])
+    assert ranges is not None and tuple(ranges.shape) == (rows, 2) and rows == grouped.mid_o.shape[0]
     n_big = grouped.aux[11][0]
     assert n_big > 0 and int((ranges[:, 0] > 0).sum()) > 0          # some rows start inside their chunk
     scale = 1.0 / d ** 0.5
@@ -164,6 +165,39 @@ def test_short_nodes_run_as_groups_with_row_ranges(spec):
         out = grouped.decode(path=path)
         assert lib.read_device_status() == 0
         assert (out - truth).abs().max().item() <= atol_for(torch.float16), path
+    # the ranges live inside the vnode_to_q_entries table: a cloned / rebuilt tuple decodes to the same bits
+    cloned = tuple(t.clone() if isinstance(t, torch.Tensor) else list(t) for t in grouped.aux)
+    o2 = torch.full_like(grouped.o, float("nan"))
+    fasttree.fasttree_decode(grouped.q, grouped.k, grouped.v, o2, *cloned, grouped.tiles[0], grouped.tiles[1],
+                             grouped.scale)
+    torch.cuda.synchronize()
+    assert torch.equal(o2.float().cpu(), grouped.decode(path="auto"))
+
+
+def test_argument_cache_keeps_no_query_tensors():
+    """A serving loop hands the engine new q / o tensor objects on every layer and step.  The memoised argument
+    structs are keyed on the persistent tensors only: 1000 calls with fresh q / o leave one entry and keep none
+    of the q storages alive."""
+    import gc
+    import weakref
+    c = cases.build_decode_case("mini3_fp16")
+    run = gpu_utils.EngineRun(c["nodes"], c["ptrs"], c["batch"], c["q"], c["k"], c["v"], c["hq"], c["hkv"],
+                              c["d"], c["tsq"], planner="b200")
+    want = run.decode(path="auto")
+    engine._ARG_CACHE.clear()
+    refs = []
+    for i in range(1000):
+        q = run.q.clone()
+        o = torch.empty_like(q)
+        engine.decode(q, run.k, run.v, o, *run.aux, run.tiles[0], run.tiles[1], run.scale)
+        if i % 100 == 0:
+            refs.append(weakref.ref(q))
+            torch.cuda.synchronize()
+            assert torch.equal(o.float().cpu(), want)
+    assert len(engine._ARG_CACHE) == 1
+    del q, o
+    gc.collect()
+    assert all(r() is None for r in refs)
 
 
 @pytest.mark.parametrize("seed", range(10))
