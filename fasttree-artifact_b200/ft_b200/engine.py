@@ -7,6 +7,7 @@ nothing is allocated per call.  Bad arguments raise ``FastTreeError`` /
 ``ValueError`` instead of silently producing garbage.
 """
 import ctypes
+import weakref
 
 import torch
 
@@ -43,8 +44,7 @@ def _pair(name, x):
 
 ROW_RANGE_MAGIC = 0x46545252          # "FTRR": trailer of a vnode_to_q_entries table that carries row ranges
 
-_RANGE_CACHE = {}
-_RANGE_CACHE_MAX = 64
+_RANGE_CACHE = {}     # id(tensor) -> (weak reference to it, (version, data_ptr, numel), rows or -1)
 
 
 def pack_row_ranges(q_entries, ranges):
@@ -69,22 +69,24 @@ def split_q_entries(vnode_to_q_entries):
     """``(rows, ranges)`` of a vnode_to_q_entries table: the number of partial rows it
     names and a ``[rows, 2]`` view of the row ranges packed behind them (None for
     a table in the reference's format).  Recognising the trailer reads two
-    integers back from the device; the answer is remembered per (storage,
-    length, version) of the tensor, so a steady decode loop does not repeat it.
+    integers back from the device; the answer is remembered per tensor object
+    (weakly, and re-read when the tensor was written to in place or re-allocated), so
+    a steady decode loop does not repeat it.
     The first call on a new table therefore synchronises with the device and
     must not fall inside a CUDA graph capture."""
     t = vnode_to_q_entries
     n = t.numel()
     if n < 5 or (n - 2) % 3 != 0:
         return n, None
-    key = (t.data_ptr(), n, t._version, t.device.index)
-    hit = _RANGE_CACHE.get(key)
-    if hit is None:
+    state = (t._version, t.data_ptr(), n)
+    ident = id(t)
+    known = _RANGE_CACHE.get(ident)
+    if known is not None and known[0]() is t and known[1] == state:
+        hit = known[2]
+    else:
         magic, rows = t.view(-1)[-2:].tolist()
         hit = rows if (magic == ROW_RANGE_MAGIC and 3 * rows + 2 == n) else -1
-        if len(_RANGE_CACHE) >= _RANGE_CACHE_MAX:
-            _RANGE_CACHE.clear()
-        _RANGE_CACHE[key] = hit
+        _RANGE_CACHE[ident] = (weakref.ref(t, lambda _r, k=ident: _RANGE_CACHE.pop(k, None)), state, hit)
     if hit < 0:
         return n, None
     return hit, t.view(-1)[hit:3 * hit].view(hit, 2)
@@ -266,6 +268,33 @@ def stage1(*args, logit_cap=-1, path="auto", row_ranges="detect"):
 
 def stage2(*args, logit_cap=-1, o_lse=None):
     _call("ft_stage2", *args, logit_cap, "auto", o_lse, None)
+
+
+def decode_host_io(q_host, o_host, q_dev, k_buffer, v_buffer, o_dev, *rest, logit_cap=-1, path="auto",
+                   row_ranges="detect", wait=True):
+    """One decode step fed from and drained to pinned host memory through ONE C-ABI call
+    (``ft_decode_host_io``): ``q_host`` -> ``q_dev`` (one cudaMemcpyAsync), stage 1 + stage 2, ``o_dev`` ->
+    ``o_host`` (one cudaMemcpyAsync), all on torch's current stream; ``wait`` synchronises that stream before
+    returning, so ``o_host`` is valid.  ``q_dev`` / ``o_dev`` are caller-owned packed device staging tensors,
+    ``rest`` are the plan tables, scratch, phase lists, tile lists and ``sm_scale`` as in :func:`decode`."""
+    for name, t in (("q_host", q_host), ("o_host", o_host)):
+        if not isinstance(t, torch.Tensor) or t.is_cuda or not t.is_pinned() or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous pinned host tensor")
+    if q_host.shape != q_dev.shape or o_host.shape != o_dev.shape or q_host.dtype != q_dev.dtype \
+            or o_host.dtype != o_dev.dtype:
+        raise ValueError("host and device staging tensors must agree in shape and dtype")
+    if not q_dev.is_contiguous() or not o_dev.is_contiguous():
+        raise ValueError("the device staging tensors must be packed")
+    tensors = (q_dev, k_buffer, v_buffer, o_dev) + tuple(rest[:11])
+    pn, po, pq, pk, sm_scale = rest[11:16]
+    a = _cached_args(tensors, (pn, po, pq, pk, float(sm_scale), float(logit_cap)), path, None, row_ranges)
+    lib = _lib.load()
+    if q_dev.device.index != torch.cuda.current_device():
+        with torch.cuda.device(q_dev.device):
+            rc = lib.ft_decode_host_io(ctypes.byref(a), q_host.data_ptr(), o_host.data_ptr(), 1 if wait else 0)
+    else:
+        rc = lib.ft_decode_host_io(ctypes.byref(a), q_host.data_ptr(), o_host.data_ptr(), 1 if wait else 0)
+    _lib.check(rc)
 
 
 def stage1_path_name(*args, logit_cap=-1, path="auto"):

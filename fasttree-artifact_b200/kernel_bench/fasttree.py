@@ -117,3 +117,22 @@ def fasttree_decode(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_o
                    vnode_to_q_entries, vnode_to_q_offs, vnode_to_q_lens, req_to_vnode_entries,
                    req_to_vnode_offs, req_to_vnode_lens, mid_o, mid_lse, phase_node_nums, phase_node_offsets,
                    phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap=logit_cap)
+
+
+_STAGING = {}
+
+
+def fasttree_decode_host_io(q, k_buffer, v_buffer, o, *aux_and_tiles, logit_cap=-1):
+    """:func:`fasttree_decode` with ``q`` and ``o`` in pinned HOST memory (same positional arguments otherwise):
+    the query is copied to the device, the step runs, the output is copied back and the stream is synchronised,
+    all inside one call of the shared library (``ft_decode_host_io``) - the pattern of a decode loop whose
+    sampler lives on the host.  The device staging buffers are kept per (shape, dtype, device) and reused, so a
+    steady loop allocates nothing.  No counterpart in the reference, whose harness keeps Q and the output on the
+    device (kernel_bench/benchmark.py:88-128)."""
+    dev = k_buffer.device
+    key = (tuple(q.shape), q.dtype, dev)
+    stage = _STAGING.get(key)
+    if stage is None:
+        stage = (torch.empty(q.shape, dtype=q.dtype, device=dev), torch.empty(o.shape, dtype=o.dtype, device=dev))
+        _STAGING[key] = stage
+    _engine.decode_host_io(q, o, stage[0], k_buffer, v_buffer, stage[1], *aux_and_tiles, logit_cap=logit_cap)

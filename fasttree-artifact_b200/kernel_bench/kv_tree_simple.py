@@ -40,6 +40,31 @@ def retrive_from_file(filepath):
     return nodes
 
 
+def tree_from_rows(rows):
+    """Nodes from ``[parent, id, seqlen, out_degree]`` rows (what tree_generation.generate_tree returns and
+    what a tree file holds)."""
+    return [KVTreeNode(int(p), int(i), int(s), int(d)) for p, i, s, d in rows]
+
+
+def assign_requests(nodes):
+    """Leaves, in id order, get request ids 0, 1, 2, ...; each id is recorded on the leaf and on all its
+    ancestors (what the reference does while drawing the inputs, kernel_bench/flash_attn_wrap.py:24-33).
+    Returns ``(batch_size, KV_ptrs)`` where node i owns rows ``[KV_ptrs[i], KV_ptrs[i+1])`` of the flat tree
+    tensors (:13,22)."""
+    for nd in nodes:
+        nd.requests = []
+    batch, ptrs = 0, [0]
+    for nd in nodes:
+        ptrs.append(ptrs[-1] + nd.seqlen)
+        if nd.num_children == 0:
+            cur = nd.id
+            while cur != -1:
+                nodes[cur].requests.append(batch)
+                cur = nodes[cur].parent
+            batch += 1
+    return batch, ptrs
+
+
 def validate_tree(nodes):
     """Checks the invariants the planner relies on; raises ValueError."""
     deg = [0] * len(nodes)

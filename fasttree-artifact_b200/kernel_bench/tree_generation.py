@@ -25,6 +25,27 @@ def generate_tree(layer_sizes, layer_lengths):
     return rows
 
 
+def generate_random_tree(levels, seed, max_children=32, lam=3.0, len_lo=16, len_hi=2048):
+    """Irregular tree with ``levels`` node-levels in the same row format (no counterpart in the reference, whose
+    generator is layered only).  Nodes get breadth-first ids; for each node in that order a context length
+    ~ Uniform{len_lo..len_hi} is drawn and, unless it sits on the last level, a child count
+    ``min(max_children, 1 + Poisson(lam))``, from ``numpy.random.default_rng(seed)``."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    rows, depth = [[-1, 0, 0, 0]], [0]
+    head = 0
+    while head < len(rows):
+        rows[head][2] = int(rng.integers(len_lo, len_hi + 1))
+        if depth[head] < levels - 1:
+            kids = int(min(max_children, 1 + rng.poisson(lam)))
+            rows[head][3] = kids
+            for _ in range(kids):
+                rows.append([head, len(rows), 0, 0])
+                depth.append(depth[head] + 1)
+        head += 1
+    return rows
+
+
 def save_tree(nodes, output_path):
     with open(output_path, "w", encoding="utf-8") as fh:
         fh.write(f"{len(nodes)}\n")
@@ -37,10 +58,17 @@ def _csv_ints(text):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description="Generate a tree based on layer sizes and sequence lengths.")
-    ap.add_argument("-n", "--layer_sizes", type=str, required=True, help="node count per level, e.g. 1,2,4")
-    ap.add_argument("-l", "--layer_lengths", type=str, required=True, help="context length per level, e.g. 128,64,64")
+    ap.add_argument("-n", "--layer_sizes", type=str, help="node count per level, e.g. 1,2,4")
+    ap.add_argument("-l", "--layer_lengths", type=str, help="context length per level, e.g. 128,64,64")
     ap.add_argument("-o", "--output_file", type=str, required=True)
+    ap.add_argument("--random_levels", type=int, default=0, help="write a seeded irregular tree of this many levels instead")
+    ap.add_argument("--seed", type=int, default=0)
     args = ap.parse_args(argv)
+    if args.random_levels > 0:
+        save_tree(generate_random_tree(args.random_levels, args.seed), args.output_file)
+        return
+    if not args.layer_sizes or not args.layer_lengths:
+        ap.error("-n/--layer_sizes and -l/--layer_lengths are required for a layered tree")
     save_tree(generate_tree(_csv_ints(args.layer_sizes), _csv_ints(args.layer_lengths)), args.output_file)
 
 

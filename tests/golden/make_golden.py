@@ -1,8 +1,8 @@
 #!/usr/bin/env python
 """Regenerate the golden fixtures in this directory from the reference's own code.
 
-Needs a checkout of PanZaifeng/FastTree-Artifact (``--reference``, default
-/root/reference); it is imported read-only and never copied.  The reference's
+Needs a checkout of PanZaifeng/FastTree-Artifact (``--reference DIR`` or the
+environment variable FASTTREE_REFERENCE_DIR); it is imported read-only and never copied.  The reference's
 planner and Triton kernels (kernel_bench/fasttree.py) run on the CPU: Triton is
 put in interpreter mode and the module's ``torch`` global is replaced by a
 forwarding object whose ``device(...)`` always answers ``cpu`` (the planner
@@ -18,7 +18,7 @@ Outputs (all small, committed):
                         reference kernels on seeded inputs (inputs are
                         reproduced from the seed; their SHA-256 is stored).
 
-Usage:  python tests/golden/make_golden.py [--reference DIR] [--with-cfg2]
+Usage:  python tests/golden/make_golden.py --reference DIR [--with-cfg2]
 """
 import argparse
 import contextlib
@@ -234,7 +234,8 @@ def save_decode(name, rec, keep_mid=True):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("FASTTREE_REFERENCE_DIR"), required="FASTTREE_REFERENCE_DIR" not in os.environ,
+                    help="checkout of PanZaifeng/FastTree-Artifact (or set FASTTREE_REFERENCE_DIR)")
     ap.add_argument("--with-cfg2", action="store_true", help="also the full-size fp16 case (minutes)")
     ap.add_argument("--skip-planner", action="store_true")
     args = ap.parse_args()

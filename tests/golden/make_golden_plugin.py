@@ -30,7 +30,8 @@ import plugin_cases  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("FASTTREE_REFERENCE_DIR"), required="FASTTREE_REFERENCE_DIR" not in os.environ,
+                    help="checkout of PanZaifeng/FastTree-Artifact (or set FASTTREE_REFERENCE_DIR)")
     args = ap.parse_args()
     sglang_standin.install()
     ref_pkg = os.path.join(args.reference, "sglang_v0.2.13_bench", "fasttree_sglang_plugin_v0_2_13")

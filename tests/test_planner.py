@@ -324,3 +324,23 @@ def test_no_groups_outside_head_dim_128():
         p.native_planner = native
         plan = fasttree.build_plan(tree, ptrs, batch, 32, 8, 64, [1024, 128], [132, 528], [132, 132], p)
         assert plan.vnode_q_kv_ranges is None
+
+
+def test_product_tree_builders_match_the_oracle():
+    """The benchmark builds its trees with the shipped generator; the oracle's restatement must describe the
+    same trees (layered and seeded irregular), request assignment and row ranges."""
+    import kv_tree_simple
+    import tree_generation
+    for levels, seed in ((3, 0), (4, 0), (4, 2), (5, 1)):
+        mine = kv_tree_simple.tree_from_rows(tree_generation.generate_random_tree(levels, seed))
+        theirs = ref_inputs.random_tree(levels, seed)
+        batch, ptrs = kv_tree_simple.assign_requests(mine)
+        assert batch == ref_inputs.assign_requests(theirs) and ptrs == ref_inputs.kv_prefix_sums(theirs)
+        assert [(n.parent, n.id, n.seqlen, n.num_children, n.requests) for n in mine] == \
+               [(n.parent, n.id, n.seqlen, n.num_children, n.requests) for n in theirs]
+    mine = kv_tree_simple.tree_from_rows(tree_generation.generate_tree([1, 16, 256], [2048, 512, 64]))
+    theirs = ref_inputs.layered_tree([1, 16, 256], [2048, 512, 64])
+    kv_tree_simple.assign_requests(mine)
+    ref_inputs.assign_requests(theirs)
+    assert [(n.parent, n.seqlen, n.num_children, n.requests) for n in mine] == \
+           [(n.parent, n.seqlen, n.num_children, n.requests) for n in theirs]
