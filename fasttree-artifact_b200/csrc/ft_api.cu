@@ -16,6 +16,7 @@
 #include "ft_stage1_narrow.cuh"
 #include "ft_stage1_stream.cuh"
 #include "ft_stage1_tc.cuh"
+#include "ft_stage1_persist.cuh"
 #include "ft_stage2.cuh"
 
 namespace {
@@ -136,10 +137,11 @@ const char* mma_obstacle(const ft_decode_args* a) {
 int pick_path(const ft_decode_args* a) {
   if (a->path == FT_PATH_GENERIC) return FT_PATH_GENERIC;
   const char* why = mma_obstacle(a);
-  if (a->path == FT_PATH_MMA || a->path == FT_PATH_TCGEN05 || a->path == FT_PATH_MMA_WIDE || a->path == FT_PATH_STREAM) {
+  if (a->path == FT_PATH_MMA || a->path == FT_PATH_TCGEN05 || a->path == FT_PATH_MMA_WIDE || a->path == FT_PATH_STREAM ||
+      a->path == FT_PATH_PERSIST) {
     if (why != nullptr) return fail(FT_ERR_UNSUPPORTED, "tensor-core path unavailable: %s", why);
-    if (a->path == FT_PATH_TCGEN05 && a->head_dim != 128)
-      return fail(FT_ERR_UNSUPPORTED, "the tcgen05 kernel needs head_dim 128, got %d", a->head_dim);
+    if ((a->path == FT_PATH_TCGEN05 || a->path == FT_PATH_PERSIST) && a->head_dim != 128)
+      return fail(FT_ERR_UNSUPPORTED, "the tcgen05 kernels need head_dim 128, got %d", a->head_dim);
     return a->path;
   }
   if (a->path != FT_PATH_AUTO) return fail(FT_ERR_INVALID_ARGUMENT, "unknown path %d", a->path);
@@ -349,6 +351,38 @@ int launch_tc(const ft::TcParams& p, int hkv, cudaStream_t st) {
   return FT_OK;
 }
 
+// Claim counters of the persistent kernel: 64 pairs used round-robin by successive launches (each launch leaves
+// its pair at zero when its last CTA finishes, so a pair is reusable as soon as that launch is over; launches
+// 64 apart do not overlap in practice).
+static __device__ unsigned int g_sched_counters[64][2];
+
+template <typename T>
+int launch_persist(ft::TcParams p, int hkv, cudaStream_t st) {
+  using C = ft::PsCfg;
+  if (dry_run("stage1_persist_kernel")) return FT_OK;
+  static OncePerDevice once;
+  int dev = 0;
+  FT_CUDA_OK(raise_smem_limit(once, ft::stage1_persist_kernel<T>, C::SMEM_BYTES, &dev));
+  if (dev < 0 || dev >= 64) return fail(FT_ERR_UNSUPPORTED, "device ordinal %d outside 0..63", dev);
+  static std::atomic<unsigned int*> counters_of_device[64];
+  unsigned int* base = counters_of_device[dev].load(std::memory_order_acquire);
+  if (base == nullptr) {
+    FT_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&base), g_sched_counters));
+    counters_of_device[dev].store(base, std::memory_order_release);
+  }
+  static std::atomic<unsigned int> next_pair{0};
+  p.sched = base + 2 * (next_pair.fetch_add(1, std::memory_order_relaxed) % 64u);
+  const int64_t tasks = (int64_t)p.p.node_count * hkv;
+  if (tasks <= 0) return FT_OK;
+  if (tasks > 0x7fffffffLL) return fail(FT_ERR_TOO_LARGE, "vnodes x kv heads exceeds the task limit");
+  const int64_t slots = 2LL * sm_count(dev);  // two resident CTAs per SM
+  const unsigned grid = (unsigned)(tasks < slots ? tasks : slots);
+  ft::stage1_persist_kernel<T><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(p);
+  FT_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return FT_OK;
+}
+
 template <typename T>
 int launch_fused(ft::TcParams p, int hkv, cudaStream_t st) {
   constexpr int smem_a = ft::TcCfg::SMEM_BYTES > ft::StreamCfg<128>::SMEM_BYTES ? ft::TcCfg::SMEM_BYTES
@@ -509,6 +543,22 @@ int ft_stage1(const ft_decode_args* a) {
   const int rows0 = (int)(r0 < (1 << 30) ? r0 : (1 << 30)), rows1 = (int)(r1 < (1 << 30) ? r1 : (1 << 30));
   const bool same_kernel = path == FT_PATH_GENERIC || path == FT_PATH_MMA_WIDE || path == FT_PATH_TCGEN05 ||
                            ((rows0 > 16) == (rows1 > 16));
+  // the persistent kernel takes every task of the launch, whatever its row count
+  if (path == FT_PATH_PERSIST) {
+    cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+    const bool joined = n0 > 0 && n1 > 0 && o1 == o0 + n0;
+    for (int ph = 0; ph < (joined ? 1 : 2); ++ph) {
+      ft::Stage1Params p = stage1_params(a);
+      p.node_offset = ph == 0 ? o0 : o1;
+      p.node_count = joined ? n0 + n1 : (ph == 0 ? n0 : n1);
+      if (p.node_count <= 0) continue;
+      const ft::TcParams tp = tc_params(p, a);
+      rc = a->dtype == FT_F16 ? launch_persist<__half>(tp, a->num_kv_heads, st)
+                              : launch_persist<__nv_bfloat16>(tp, a->num_kv_heads, st);
+      if (rc != FT_OK) return rc;
+    }
+    return FT_OK;
+  }
   // head_dim 128, many-row phase followed directly by the few-row phase: one grid with both kernel bodies
   if (path == FT_PATH_AUTO && a->head_dim == 128 && n0 > 0 && n1 > 0 && o1 == o0 + n0 && rows0 > 16 && rows1 <= 16) {
     ft::Stage1Params p = stage1_params(a);
@@ -701,6 +751,17 @@ int ft_debug_timeline(unsigned long long* out, int n) {
   return FT_OK;
 }
 #endif
+
+int ft_read_wait_diagnostics(int32_t* out8) {
+  if (out8 == nullptr) return fail(FT_ERR_INVALID_ARGUMENT, "out8 is NULL");
+  FT_CUDA_OK(cudaDeviceSynchronize());
+  FT_CUDA_OK(cudaMemcpyFromSymbol(out8, ft::g_wait_diag, 8 * sizeof(int)));
+  if (out8[0] != 0) {
+    const int zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    FT_CUDA_OK(cudaMemcpyToSymbol(ft::g_wait_diag, zero, sizeof(zero)));
+  }
+  return FT_OK;
+}
 
 int ft_read_device_status(void* stream, int32_t* flags) {
   if (flags == nullptr) return fail(FT_ERR_INVALID_ARGUMENT, "flags is NULL");

@@ -18,6 +18,7 @@ struct alignas(64) TcParams {
   Stage1Params p;
   int has_tma;
   int q_box_rows;     // 0: gather Q with cp.async (group size not a power of two <= 128, or no descriptor)
+  unsigned int* sched;  // persistent kernel: {tasks claimed beyond the first per CTA, CTAs finished}, zero between launches
 };
 
 __device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }

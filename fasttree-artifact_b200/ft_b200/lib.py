@@ -11,16 +11,16 @@ import threading
 from . import build as _build
 
 FT_F16, FT_BF16, FT_F32 = 0, 1, 2
-FT_PATH_AUTO, FT_PATH_GENERIC, FT_PATH_MMA, FT_PATH_TCGEN05, FT_PATH_MMA_WIDE, FT_PATH_STREAM = 0, 1, 2, 3, 4, 5
+FT_PATH_AUTO, FT_PATH_GENERIC, FT_PATH_MMA, FT_PATH_TCGEN05, FT_PATH_MMA_WIDE, FT_PATH_STREAM, FT_PATH_PERSIST = 0, 1, 2, 3, 4, 5, 6
 PATHS = {"auto": FT_PATH_AUTO, "generic": FT_PATH_GENERIC, "mma": FT_PATH_MMA, "tcgen05": FT_PATH_TCGEN05,
-         "mma_wide": FT_PATH_MMA_WIDE, "stream": FT_PATH_STREAM}
+         "mma_wide": FT_PATH_MMA_WIDE, "stream": FT_PATH_STREAM, "persist": FT_PATH_PERSIST}
 
 FT_STATIC_SCRATCH_BYTES = 16 << 20      # capacity of the array behind ft_decode_static_scratch
 
 FT_DEV_BAD_KV_INDEX, FT_DEV_BAD_Q_INDEX, FT_DEV_BAD_ROW_INDEX, FT_DEV_WAIT_TIMEOUT = 1, 2, 4, 8
 
 EXPORTS = ["ft_version", "ft_decode_args_size", "ft_last_error", "ft_decode", "ft_stage1", "ft_stage2",
-           "ft_decode_static_scratch", "ft_decode_host_io", "ft_selftest_bounded_wait", "ft_bump_kv_lens",
+           "ft_decode_static_scratch", "ft_decode_host_io", "ft_selftest_bounded_wait", "ft_read_wait_diagnostics", "ft_bump_kv_lens",
            "ft_read_device_status", "ft_launch_count", "ft_stage1_path_name",
            "ft_plan_b200_build", "ft_plan_b200_build_direct", "ft_plan_get_info", "ft_plan_copy_tables", "ft_plan_copy_row_ranges",
            "ft_plan_free"]
@@ -100,8 +100,8 @@ def load():
     with _lock:
         if _lib is not None:
             return _lib
-        path = _build.LIB_PATH
-        if _build._stale() or os.environ.get("FT_B200_REBUILD") == "1":
+        path = os.environ.get("FT_B200_LIBRARY") or _build.LIB_PATH      # a prebuilt library elsewhere, if named
+        if path == _build.LIB_PATH and (_build._stale() or os.environ.get("FT_B200_REBUILD") == "1"):
             try:
                 _build.build_library(force=True)
             except Exception as exc:  # no nvcc, or the compile failed
@@ -157,6 +157,12 @@ def load():
 def check(rc):
     if rc != 0:
         raise FastTreeError(rc, load().ft_last_error().decode("utf-8", "replace"))
+
+
+def read_wait_diagnostics():
+    out = (ctypes.c_int32 * 8)()
+    check(load().ft_read_wait_diagnostics(out))
+    return list(out)
 
 
 def launch_count():

@@ -37,7 +37,8 @@ enum ft_path {
                           narrow (swapped-operand) kernel for <= 16 query rows per task, else the wide one */
   FT_PATH_TCGEN05 = 3, /* tcgen05/TMEM kernel for 128-row tasks, 16-bit types, head_dim 128 */
   FT_PATH_MMA_WIDE = 4, /* the wide mma.sync kernel for every task (ablation / cross-check) */
-  FT_PATH_STREAM = 5    /* like AUTO, but few-row phases run the persistent kernel that pipelines across tasks */
+  FT_PATH_STREAM = 5,   /* like AUTO, but few-row phases run the persistent kernel that pipelines across tasks */
+  FT_PATH_PERSIST = 6   /* one persistent tcgen05 kernel (a CTA per SM) for every task: 16-bit types, head_dim 128 */
 };
 
 /* Status codes. */
@@ -191,6 +192,12 @@ int ft_read_device_status(void* stream, int32_t* flags);
  * FT_DEV_WAIT_TIMEOUT in the device status word, as a stage-1 kernel whose wait ran out does.  No copy engine, tensor
  * core or tensor memory is used.  A health check for the failure-detection path; no counterpart in the reference. */
 int ft_selftest_bounded_wait(int limit, int* result_host, void* stream);
+
+/* Which bounded wait of the persistent stage-1 kernel gave up first since the last call (after
+ * FT_DEV_WAIT_TIMEOUT): out8 = {wait id (0: none), block, warp, task sequence number, tile counter, 0, 0, 0};
+ * the ids are listed next to the kernel (csrc/ft_stage1_persist.cuh).  Synchronises the device and clears the
+ * record.  A diagnostic aid; no counterpart in the reference. */
+int ft_read_wait_diagnostics(int32_t* out8);
 
 /* Number of kernels this library has launched from the calling process. */
 int64_t ft_launch_count(void);

@@ -32,7 +32,7 @@ def paths_for(c):
     fast = c["dtype"] != torch.float32 and c["d"] in (64, 128)
     if not fast:
         return ["generic"]
-    return ["generic", "mma", "mma_wide", "stream"] + (["tcgen05", "auto"] if c["d"] == 128 else [])
+    return ["generic", "mma", "mma_wide", "stream"] + (["tcgen05", "persist", "auto"] if c["d"] == 128 else [])
 
 
 SMALL = [n for n in cases.DECODE_CASES if n != "cfg2_fp16"]
@@ -67,7 +67,7 @@ def test_bf16_case(planner):
     fp32 up-cast of the same bf16 tensors."""
     c = cases.build_decode_case("mini3_bf16_as_fp32")
     assert c["dtype"] == torch.bfloat16
-    for path in ("generic", "mma", "mma_wide", "stream", "tcgen05", "auto"):
+    for path in ("generic", "mma", "mma_wide", "stream", "tcgen05", "persist", "auto"):
         _, out = gpu_utils.run_case(c, planner=planner, path=path)
         # the output itself is rounded to bf16 (8 bits of mantissa): allow one bf16 ulp of the largest value
         bound = ATOL16 + float(np.abs(c["gold"]["o"]).max()) * 2 ** -8
@@ -218,14 +218,14 @@ def test_random_trees_of_short_nodes(seed):
     scale = 1.0 / 128 ** 0.5
     truth, truth_lse = ref_attention.per_leaf_attention(nodes, ptrs, q, k, v, scale)
     tol = atol_for(dtype) + (float(truth.abs().max()) * 2 ** -8 if dtype == torch.bfloat16 else 0.0)
-    for path in ("auto", "tcgen05", "mma", "mma_wide", "stream", "generic"):
+    for path in ("auto", "tcgen05", "persist", "mma", "mma_wide", "stream", "generic"):
         out = run.decode(path=path)
         assert lib.read_device_status() == 0
         assert (out - truth).abs().max().item() <= tol, path
         np.testing.assert_allclose(run.o_lse.cpu().numpy(), truth_lse.numpy(), rtol=1e-4, atol=2e-5)
 
 
-ALL_PATHS = ("mma", "mma_wide", "generic", "tcgen05", "stream", "auto")
+ALL_PATHS = ("mma", "mma_wide", "generic", "tcgen05", "persist", "stream", "auto")
 
 
 def wide_case():
