@@ -138,6 +138,7 @@ template <typename T>
 __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const __grid_constant__ TcParams tp) {
   using C = PsCfg;
   allow_dependent_launch();
+  FT_TL_BEGIN();
   extern __shared__ __align__(1024) uint8_t smem[];
   const Stage1Params& p = tp.p;
   const uint32_t sm = smem_u32(smem);
@@ -200,6 +201,16 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = usable ? *tmem_slot : 0u;
+  if (tid == 0) FT_TL_MARK(0);
+#ifdef FT_TIMELINE
+  long long tl_s = 0, tl_epi = 0, tl_task = 0, tl_pv = 0, tl_c = 0;
+  int tl_tasks = 0, tl_tiles = 0;
+#define PS_TL_T0() tl_c = (long long)timeline_now()
+#define PS_TL_ADD(acc) acc += (long long)timeline_now() - tl_c
+#else
+#define PS_TL_T0() do { } while (0)
+#define PS_TL_ADD(acc) do { } while (0)
+#endif
 
   bool dead = !usable;
   auto give_up = [&](int wait_id, int seq_, int counter) {
@@ -291,10 +302,12 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
     auto pv_done = [&](int tile) { return warp_wait(bar(C::PV_DONE + (tile & 1)), (uint32_t)(tile >> 1) & 1u); };
     for (int seq = 0; !dead; ++seq) {
       PsTask t;
+      PS_TL_T0();
       if (!read_task(seq, t, true)) {
         give_up(1, seq, gx);
         break;
       }
+      PS_TL_ADD(tl_task);
       if (t.vn < 0) break;
       const int rows = min(t.q_len * G - t.row0, 128);
       const int kv_len = t.kv_len;
@@ -317,10 +330,16 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
       float m_used = -INFINITY, l_run = 0.f;
       for (int j = 0; j < ntiles && !dead; ++j, ++gx) {
         const int b = gx & 1;
+        PS_TL_T0();
         if (!warp_wait(bar(C::S_FULL + b), (uint32_t)(gx >> 1) & 1u)) {
           give_up(2, seq, gx);
           break;
         }
+        PS_TL_ADD(tl_s);
+#ifdef FT_TIMELINE
+        if (gx == 0 && tid == 0) FT_TL_MARK(3);
+        ++tl_tiles;
+#endif
         tc_fence_after();
         const uint32_t s_col = t_lane + b * C::TILE;
         float corr = 1.f;
@@ -366,10 +385,12 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
         // t - 2 is long done, but every thread looks at every phase of the two P.V barriers in turn so that their
         // parities keep their meaning.  O is only touched when the running offset has to grow, and then P.V of
         // tile t - 1 must be done too.
+        PS_TL_T0();
         if (gx >= 2 && !pv_done(gx - 2)) {
           give_up(3, seq, gx);
           break;
         }
+        PS_TL_ADD(tl_pv);
         if (j > 0 && __any_sync(0xffffffffu, grow)) {
           if (!pv_done(gx - 1)) {
             give_up(3, seq, gx);
@@ -391,6 +412,7 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
         mbar_arrive(bar(C::P_FULL + b));
       }
       // ---- epilogue: wait for the last two P.V (in order), normalise, write this thread's partial row
+      PS_TL_T0();
       if (!dead && gx >= 2 && !pv_done(gx - 2)) give_up(4, seq, gx);
       if (!dead && gx >= 1 && !pv_done(gx - 1)) give_up(4, seq, gx);
       if (!dead) {
@@ -417,7 +439,24 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
         // task before its last P.V completes)
         mbar_arrive(bar(C::TASK_EMPTY + seq % C::TR));
       }
+      PS_TL_ADD(tl_epi);
+#ifdef FT_TIMELINE
+      if (tl_tasks == 0 && tid == 0) FT_TL_MARK(4);
+      ++tl_tasks;
+#endif
     }
+#ifdef FT_TIMELINE
+    if (tid == 0 && blockIdx.x < FT_TIMELINE_CTAS) {
+      unsigned long long* rec = g_timeline + 16 * blockIdx.x;
+      rec[9] = tl_tasks;
+      rec[10] = tl_tiles;
+      rec[11] = tl_s;
+      rec[12] = tl_epi;
+      rec[13] = tl_task;
+      rec[14] = tl_pv;
+      rec[15] = timeline_now();
+    }
+#endif
   } else {
     reg_shrink<C::REGS_OTHER>();
     if (warp == 4) {
@@ -469,6 +508,9 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
               give_up(8, seq, gx);
               break;
             }
+#ifdef FT_TIMELINE
+            if (gx == 0) FT_TL_MARK(2);
+#endif
             // S buffer b still holds P of tile gx - 2 until that tile's P.V has COMPLETED: MMAs of different
             // shapes are not ordered against each other, so issue order alone does not protect it
             if (gx >= 2 && !ps_wait(bar(C::PV_DONE + b), (uint32_t)((gx - 2) >> 1) & 1u, abort_flag)) {
@@ -591,6 +633,9 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
                 break;
               }
               load_tile(&tp.k_map, base, p.k_s0, t.kvh, tt, id_lim, cur, sm + C::K_OFF + sk * 16384, bar(C::K_FULL + sk));
+#ifdef FT_TIMELINE
+              if (g == 0 && lane == 0) FT_TL_MARK(1);
+#endif
               if (last_pass && !next_known) {  // the claim has had a tile's time to come back: fetch that task's metadata
                 b_next = __shfl_sync(0xffffffffu, b_next, 0);
                 meta_next = meta_load(b_next);
@@ -773,6 +818,7 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(C::TMEM_COLS) : "memory");
   }
+  FT_TL_END(3);
   if (tid == 0) {
     __threadfence();
     const unsigned int done = atomicAdd(tp.sched + 1, 1u);
