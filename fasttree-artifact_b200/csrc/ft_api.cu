@@ -109,7 +109,7 @@ int check_stage1(const ft_decode_args* a) {
   for (int ph = 0; ph < 2; ++ph)
     if (a->phase_node_nums[ph] < 0 || a->phase_node_offsets[ph] < 0)
       return fail(FT_ERR_INVALID_ARGUMENT, "phase %d: negative vnode count or offset", ph);
-  if (a->phase_node_nums[0] + a->phase_node_nums[1] > 0) {
+  if (a->phase_node_nums[0] + a->phase_node_nums[1] > 0 || a->device_phase_info != nullptr) {
     if (!a->vnode_to_kv_entries || !a->vnode_to_kv_offs || !a->vnode_to_kv_lens || !a->vnode_to_q_entries ||
         !a->vnode_to_q_offs || !a->vnode_to_q_lens)
       return fail(FT_ERR_INVALID_ARGUMENT, "a vnode table pointer is NULL");
@@ -135,8 +135,16 @@ const char* mma_obstacle(const ft_decode_args* a) {
 }
 
 int pick_path(const ft_decode_args* a) {
-  if (a->path == FT_PATH_GENERIC) return FT_PATH_GENERIC;
   const char* why = mma_obstacle(a);
+  if (a->device_phase_info != nullptr) {  // only the persistent kernel has a grid that does not depend on the plan
+    if (a->path != FT_PATH_AUTO && a->path != FT_PATH_PERSIST)
+      return fail(FT_ERR_UNSUPPORTED, "device_phase_info needs path AUTO or PERSIST, got %d", a->path);
+    if (why != nullptr || a->head_dim != 128)
+      return fail(FT_ERR_UNSUPPORTED, "device_phase_info needs the persistent kernel: 16-bit types, head_dim 128, aligned buffers%s%s",
+                  why ? "; " : "", why ? why : "");
+    return FT_PATH_PERSIST;
+  }
+  if (a->path == FT_PATH_GENERIC) return FT_PATH_GENERIC;
   if (a->path == FT_PATH_MMA || a->path == FT_PATH_TCGEN05 || a->path == FT_PATH_MMA_WIDE || a->path == FT_PATH_STREAM ||
       a->path == FT_PATH_PERSIST) {
     if (why != nullptr) return fail(FT_ERR_UNSUPPORTED, "tensor-core path unavailable: %s", why);
@@ -160,6 +168,7 @@ ft::Stage1Params stage1_params(const ft_decode_args* a) {
   p.q_offs = a->vnode_to_q_offs;
   p.q_lens = a->vnode_to_q_lens;
   p.q_ranges = a->vnode_q_kv_ranges;
+  p.dev_phase = a->device_phase_info;
   p.mid_o = a->mid_o;
   p.mid_lse = a->mid_lse;
   p.q_s0 = a->q_stride0;
@@ -372,10 +381,11 @@ int launch_persist(ft::TcParams p, int hkv, cudaStream_t st) {
   }
   static std::atomic<unsigned int> next_pair{0};
   p.sched = base + 2 * (next_pair.fetch_add(1, std::memory_order_relaxed) % 64u);
-  const int64_t tasks = (int64_t)p.p.node_count * hkv;
+  const int64_t slots = 2LL * sm_count(dev);  // two resident CTAs per SM
+  int64_t tasks = (int64_t)p.p.node_count * hkv;
+  if (p.p.dev_phase != nullptr) tasks = slots;  // the task count is only known on the device: a full grid
   if (tasks <= 0) return FT_OK;
   if (tasks > 0x7fffffffLL) return fail(FT_ERR_TOO_LARGE, "vnodes x kv heads exceeds the task limit");
-  const int64_t slots = 2LL * sm_count(dev);  // two resident CTAs per SM
   const unsigned grid = (unsigned)(tasks < slots ? tasks : slots);
   ft::stage1_persist_kernel<T><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(p);
   FT_CUDA_OK(cudaGetLastError());
@@ -544,6 +554,13 @@ int ft_stage1(const ft_decode_args* a) {
   const bool same_kernel = path == FT_PATH_GENERIC || path == FT_PATH_MMA_WIDE || path == FT_PATH_TCGEN05 ||
                            ((rows0 > 16) == (rows1 > 16));
   // the persistent kernel takes every task of the launch, whatever its row count
+  if (path == FT_PATH_PERSIST && a->device_phase_info != nullptr) {
+    ft::Stage1Params p = stage1_params(a);  // node_offset / node_count come from the device array
+    const ft::TcParams tp = tc_params(p, a);
+    cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+    return a->dtype == FT_F16 ? launch_persist<__half>(tp, a->num_kv_heads, st)
+                              : launch_persist<__nv_bfloat16>(tp, a->num_kv_heads, st);
+  }
   if (path == FT_PATH_PERSIST) {
     cudaStream_t st = static_cast<cudaStream_t>(a->stream);
     const bool joined = n0 > 0 && n1 > 0 && o1 == o0 + n0;
@@ -629,6 +646,18 @@ int ft_decode(const ft_decode_args* a) {
   return stage2_impl(a, launched);
 }
 
+namespace {
+// Host-to-device copy done by the SMs: 16 bytes per thread from mapped pinned host memory.  For the few hundred
+// KiB of a decode step's query this is several microseconds quicker than a copy-engine transfer, whose set-up
+// and completion hand-shake dominate at that size.
+__global__ void __launch_bounds__(256) host_to_device_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, size_t n16,
+                                                             unsigned char* dst_tail, const unsigned char* src_tail, int tail) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n16) dst[i] = src[i];
+  if (i < (size_t)tail) dst_tail[i] = src_tail[i];
+}
+}  // namespace
+
 int ft_decode_host_io(const ft_decode_args* a, const void* q_host, void* o_host, int wait) {
   if (a == nullptr) return fail(FT_ERR_INVALID_ARGUMENT, "args is NULL");
   if (q_host == nullptr || o_host == nullptr) return fail(FT_ERR_INVALID_ARGUMENT, "q_host / o_host is NULL");
@@ -641,10 +670,36 @@ int ft_decode_host_io(const ft_decode_args* a, const void* q_host, void* o_host,
   const size_t esz = a->dtype == FT_F32 ? 4 : 2;
   const size_t bytes = (size_t)a->batch * (size_t)row * esz;
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
-  if (bytes > 0) FT_CUDA_OK(cudaMemcpyAsync(const_cast<void*>(a->q), q_host, bytes, cudaMemcpyHostToDevice, st));
-  const int rc = ft_decode(a);
+  if (bytes == 0) return ft_decode(a);
+  // Pinned host memory is mapped into the device's address space: the query is then fetched by a small kernel and
+  // stage 2 writes the output rows straight into o_host over PCIe, so no copy-engine transfer sits on the step's
+  // critical path.  Memory that is not mapped (pageable, or registered without the mapped flag) takes the copy
+  // engine, one cudaMemcpyAsync per buffer.
+  void *q_map = nullptr, *o_map = nullptr;
+  const bool mapped = cudaHostGetDevicePointer(&q_map, const_cast<void*>(q_host), 0) == cudaSuccess &&
+                      cudaHostGetDevicePointer(&o_map, o_host, 0) == cudaSuccess && aligned16(q_map) && aligned16(a->q) &&
+                      aligned16(o_map);
+  if (!mapped) {
+    (void)cudaGetLastError();  // the failed query left an error behind
+    FT_CUDA_OK(cudaMemcpyAsync(const_cast<void*>(a->q), q_host, bytes, cudaMemcpyHostToDevice, st));
+    const int rc = ft_decode(a);
+    if (rc != FT_OK) return rc;
+    FT_CUDA_OK(cudaMemcpyAsync(o_host, a->o, bytes, cudaMemcpyDeviceToHost, st));
+    if (wait) FT_CUDA_OK(cudaStreamSynchronize(st));
+    return FT_OK;
+  }
+  const size_t n16 = bytes / 16;
+  const int tail = (int)(bytes % 16);
+  const unsigned blocks = (unsigned)((n16 + (tail ? 1 : 0) + 255) / 256);
+  host_to_device_kernel<<<blocks, 256, 0, st>>>(static_cast<uint4*>(const_cast<void*>(a->q)), static_cast<const uint4*>(q_map), n16,
+                                                static_cast<unsigned char*>(const_cast<void*>(a->q)) + 16 * n16,
+                                                static_cast<const unsigned char*>(q_map) + 16 * n16, tail);
+  FT_CUDA_OK(cudaGetLastError());
+  count_launch();
+  ft_decode_args b = *a;
+  b.o = o_map;  // stage 2 writes the merged rows into host memory; the device staging buffer args->o is not used
+  const int rc = ft_decode(&b);
   if (rc != FT_OK) return rc;
-  if (bytes > 0) FT_CUDA_OK(cudaMemcpyAsync(o_host, a->o, bytes, cudaMemcpyDeviceToHost, st));
   if (wait) FT_CUDA_OK(cudaStreamSynchronize(st));
   return FT_OK;
 }

@@ -59,6 +59,7 @@ struct Stage1Params {
   const int32_t* q_offs;
   const int32_t* q_lens;
   const int32_t* q_ranges;  // optional [num_partial_rows][2]: the chunk tokens [begin, end) a partial row attends to
+  const int32_t* dev_phase; // optional device array {n0, n1, o0, o1}: the persistent kernel reads its vnode range here
   float* mid_o;
   float* mid_lse;
   int64_t q_s0, q_s1, k_s0, k_s1, v_s0, v_s1, mo_s0, mo_s1, ml_s0;

@@ -150,7 +150,18 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = p.group, H = p.num_kv_heads;
-  const int total_tasks = p.node_count * H;
+  // the launch's vnode range: host arguments, or read from the device so that the launch outlives the plan
+  int node_offset = p.node_offset, node_count = p.node_count;
+  if (p.dev_phase != nullptr) {
+    const int n0 = max(__ldg(p.dev_phase + 0), 0), n1 = max(__ldg(p.dev_phase + 1), 0);
+    node_offset = max(__ldg(p.dev_phase + 2), 0);
+    node_count = n0 + n1;
+    if (n0 > 0 && n1 > 0 && __ldg(p.dev_phase + 3) != node_offset + n0) {  // the phases must be adjacent
+      if (threadIdx.x == 0) flag_error(FT_DEV_BAD_ROW_INDEX);
+      node_count = n0;
+    }
+  }
+  const int total_tasks = (int)min((long long)node_count * H, 0x7fffffffLL);
   const float scale2 = p.sm_scale * 1.4426950408889634f;
   const uint32_t row_lim = (uint32_t)(p.kv_rows < 0x7fffffffLL ? p.kv_rows : 0x7fffffffLL);
 
@@ -543,7 +554,7 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
       auto meta_load = [&](int b_) {  // lanes 0-3: q_off, q_len, kv_off, kv_len of the task's vnode
         int v = 0;
         if (b_ < total_tasks && lane < 4) {
-          const int vn = p.node_offset + b_ / H;
+          const int vn = node_offset + b_ / H;
           const int32_t* tab = lane == 0 ? p.q_offs : lane == 1 ? p.q_lens : lane == 2 ? p.kv_offs : p.kv_lens;
           v = __ldg(tab + vn);
         }
@@ -573,7 +584,7 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
         int meta_next = 0;
         bool next_known = false;
         PsTask t;
-        t.vn = p.node_offset + b / H;
+        t.vn = node_offset + b / H;
         t.kvh = b - (b / H) * H;
         t.q_off = __shfl_sync(0xffffffffu, meta, 0);
         t.q_len = __shfl_sync(0xffffffffu, meta, 1);

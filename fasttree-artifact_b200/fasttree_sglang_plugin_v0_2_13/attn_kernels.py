@@ -10,8 +10,10 @@ from ft_b200 import engine as _engine
 def fasttree_decode(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, vnode_to_kv_lens,
                     vnode_to_q_entries, vnode_to_q_offs, vnode_to_q_lens, req_to_vnode_entries,
                     req_to_vnode_offs, req_to_vnode_lens, mid_o, mid_lse, phase_node_nums, phase_node_offsets,
-                    phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap=-1):
+                    phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap=-1, phase_info=None):
+    """``phase_info`` (beyond the reference's signature): a device copy of the phase split, see
+    ``FastTreeMetadata.graph_safe``."""
     _engine.decode(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, vnode_to_kv_lens,
                    vnode_to_q_entries, vnode_to_q_offs, vnode_to_q_lens, req_to_vnode_entries,
                    req_to_vnode_offs, req_to_vnode_lens, mid_o, mid_lse, phase_node_nums, phase_node_offsets,
-                   phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap=logit_cap, row_ranges=None)
+                   phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap=logit_cap, row_ranges=None, phase_info=phase_info)

@@ -26,6 +26,7 @@ class FastTreeMetadata:
         max_vnode_to_q_entries: int = 81920,
         max_batch_size: int = 8192,
         planner: str = "b200",
+        graph_safe: bool = False,
     ):
         if planner not in ("b200", "reference"):
             raise ValueError("planner must be 'b200' or 'reference'")
@@ -42,6 +43,10 @@ class FastTreeMetadata:
         self.para_threshs2 = para_threshs2
         self.planner = planner
         self.native_planner = True      # "b200": the library's native splitter (False: its Python specification)
+        # graph_safe: the decode call reads the phase split from the device (phase_info_dev) and runs the
+        # persistent stage-1 kernel, whose launch does not depend on the plan - a decode step captured in a CUDA
+        # graph then stays valid from burst to burst (16-bit KV, head_dim 128).  No counterpart in the reference.
+        self.graph_safe = bool(graph_safe)
         self.max_vnodes = max_vnodes
         self.max_vnode_to_q_entries = max_vnode_to_q_entries
         self.max_batch_size = max_batch_size
@@ -58,6 +63,7 @@ class FastTreeMetadata:
         self.req_to_vnode_offs = i32(max_batch_size)
         self.req_to_vnode_lens = i32(max_batch_size)
         self.req_last_vnodes_dev = i32(max_batch_size)      # device copy of req_last_vnodes for the per-step bump
+        self.phase_info_dev = torch.zeros(4, dtype=torch.int32, device=device)   # n0, n1, o0, o1 of the current plan
         self.mid_o = torch.empty((max_vnode_to_q_entries, num_qo_heads, head_dim), dtype=torch.float32, device=device)
         self.mid_lse = torch.empty((max_vnode_to_q_entries, num_qo_heads), dtype=torch.float32, device=device)
 

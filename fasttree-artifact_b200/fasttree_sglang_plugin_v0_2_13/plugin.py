@@ -15,6 +15,8 @@ unsharded ones, plugin.py:221-226); the NVTX ranges come from
 """
 from types import MethodType
 
+import os
+
 import torch
 
 from .attn_kernels import fasttree_decode
@@ -47,6 +49,7 @@ def _replace_radix_attn():
             md.mid_o, md.mid_lse,
             md.phase_node_nums, md.phase_node_offsets, md.phase_q_tile_sizes, md.phase_kv_tile_sizes,
             sm_scale=self.scaling, logit_cap=self.logit_cap,
+            phase_info=md.phase_info_dev if md.graph_safe else None,
         )
         return o
 
@@ -154,15 +157,19 @@ def _load_plugin_and_replace_tp_server_init(enable_fasttree=True, annotate_break
     def patched_init(self, gpu_id, tp_rank, server_args, nccl_port, model_overide_args):
         # patch inside the worker process, after it exists (CUDA must not be touched before the fork/spawn)
         _delayed_load_fasttree_plugin(enable_fasttree, annotate_breakdown)
-        if enable_fasttree:
-            server_args.disable_cuda_graph = True       # the schedule changes every burst
+        # The reference switches CUDA graphs off because its grids depend on the schedule, which changes every
+        # burst (plugin.py:209-211).  With FASTTREE_GRAPH_SAFE=1 the decode call takes its phase split from device
+        # memory and runs one plan-independent persistent grid, so the host's graph setting is left alone.
+        graph_safe = os.environ.get("FASTTREE_GRAPH_SAFE", "0") == "1"
+        if enable_fasttree and not graph_safe:
+            server_args.disable_cuda_graph = True
         original_init(self, gpu_id, tp_rank, server_args, nccl_port, model_overide_args)
         if enable_fasttree:
             cfg = self.model_config
             tp = max(1, int(getattr(server_args, "tp_size", 1) or 1))
             self.fasttree_metadata = FastTreeMetadata(
                 max(1, cfg.num_attention_heads // tp), max(1, cfg.num_key_value_heads // tp), cfg.head_dim,
-                torch.device("cuda", self.gpu_id))
+                torch.device("cuda", self.gpu_id), graph_safe=graph_safe)
 
     ModelTpServer.__init__ = patched_init
 

@@ -87,6 +87,7 @@ def _upload(md, tabs, last_vnodes):
     put(md.req_to_vnode_offs, tabs["req_to_vnode_offs"])
     put(md.req_to_vnode_lens, tabs["req_to_vnode_lens"])
     put(md.req_last_vnodes_dev, np.asarray(last_vnodes, dtype=np.int32))
+    put(md.phase_info_dev, np.asarray(list(tabs["phase_node_nums"]) + list(tabs["phase_node_offsets"]), dtype=np.int32))
     md.phase_node_nums = list(tabs["phase_node_nums"])
     md.phase_node_offsets = list(tabs["phase_node_offsets"])
     md.req_last_vnodes = [int(v) for v in last_vnodes]

@@ -100,8 +100,11 @@ def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, 
                vnode_to_q_entries, vnode_to_q_offs, vnode_to_q_lens, req_to_vnode_entries,
                req_to_vnode_offs, req_to_vnode_lens, mid_o, mid_lse, phase_node_nums, phase_node_offsets,
                phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap=-1, path="auto", o_lse=None,
-               stream=None, row_ranges="detect"):
-    """Validate the tensors and fill a :class:`DecodeArgs` struct.  ``row_ranges``:
+               stream=None, row_ranges="detect", phase_info=None):
+    """Validate the tensors and fill a :class:`DecodeArgs` struct.  ``phase_info``: an
+    int32 CUDA tensor ``[n0, n1, o0, o1]`` that stage 1 reads on the device in
+    place of ``phase_node_nums`` / ``phase_node_offsets`` (the launch then does not
+    depend on the plan and survives a re-plan inside a captured CUDA graph).  ``row_ranges``:
     ``"detect"`` looks for ranges packed into ``vnode_to_q_entries`` (see
     :func:`pack_row_ranges`), ``None`` says the plan has none (no look-up, no
     device read), a tensor gives the table explicitly."""
@@ -138,8 +141,12 @@ def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, 
     n0, n1 = _pair("phase_node_nums", phase_node_nums)
     f0, f1 = _pair("phase_node_offsets", phase_node_offsets)
     nv = vnode_to_kv_offs.numel()
+    if phase_info is not None:
+        _table("phase_info", phase_info)
+        if phase_info.numel() < 4:
+            raise ValueError("phase_info needs four entries: n0, n1, o0, o1")
     for cnt, off in ((n0, f0), (n1, f1)):
-        if cnt < 0 or off < 0 or off + cnt > nv:
+        if phase_info is None and (cnt < 0 or off < 0 or off + cnt > nv):
             raise ValueError("phase_node_nums / phase_node_offsets do not fit the vnode tables")
     if min(vnode_to_kv_lens.numel(), vnode_to_q_offs.numel(), vnode_to_q_lens.numel()) < nv:
         raise ValueError("vnode tables differ in length")
@@ -167,6 +174,7 @@ def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, 
 
     a = _lib.DecodeArgs()
     a.vnode_q_kv_ranges = ranges.data_ptr() if ranges is not None else None
+    a.device_phase_info = phase_info.data_ptr() if phase_info is not None else None
     a.q, a.k_buffer, a.v_buffer, a.o = q.data_ptr(), k_buffer.data_ptr(), v_buffer.data_ptr(), o.data_ptr()
     a.o_lse = o_lse.data_ptr() if o_lse is not None else None
     a.dtype = _DTYPES[q.dtype]
@@ -196,7 +204,7 @@ def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, 
     return a
 
 
-def _cached_args(tensors, rest, path, o_lse, row_ranges):
+def _cached_args(tensors, rest, path, o_lse, row_ranges, phase_info=None):
     """Argument structs are memoised so that a steady-state decode loop pays for
     one dict lookup and a few pointer stores instead of rebuilding ~45 fields.
     The key names only what persists across calls - the K/V buffers, the plan
@@ -214,7 +222,8 @@ def _cached_args(tensors, rest, path, o_lse, row_ranges):
     is_detect = isinstance(row_ranges, str)
     ranges_key = row_ranges if is_detect or row_ranges is None else id(row_ranges)
     key = (tuple(map(id, persistent)), pn[0], pn[1], po[0], po[1], pq[0], pq[1], pk[0], pk[1], sm_scale, logit_cap,
-           path, stream, ranges_key, q.shape, q.stride(), q.dtype, o.shape, o.stride(), o.dtype, o_lse is None)
+           path, stream, ranges_key, q.shape, q.stride(), q.dtype, o.shape, o.stride(), o.dtype, o_lse is None,
+           id(phase_info) if phase_info is not None else None)
     ptrs = tuple([t.data_ptr() for t in persistent])
     hit = _ARG_CACHE.get(key)
     if hit is not None and hit[1] == ptrs and (not is_detect or hit[3] == tensors[7]._version):
@@ -223,10 +232,10 @@ def _cached_args(tensors, rest, path, o_lse, row_ranges):
             raise ValueError("q / o must live on a CUDA device; the engine has no CPU path")
     else:
         a = build_args(*tensors, pn, po, pq, pk, sm_scale, logit_cap, path=path, o_lse=o_lse, stream=stream,
-                       row_ranges=row_ranges)
+                       row_ranges=row_ranges, phase_info=phase_info)
         if len(_ARG_CACHE) >= _ARG_CACHE_MAX:
             _ARG_CACHE.clear()
-        keep = row_ranges if isinstance(row_ranges, torch.Tensor) else None
+        keep = (row_ranges if isinstance(row_ranges, torch.Tensor) else None, phase_info)
         _ARG_CACHE[key] = (a, ptrs, persistent, tensors[7]._version, keep)
     a.q, a.o = q.data_ptr(), o.data_ptr()
     if o_lse is not None:
@@ -241,12 +250,13 @@ def _cached_args(tensors, rest, path, o_lse, row_ranges):
 
 def _call(fn_name, q, k_buffer, v_buffer, o, kv_entries, kv_offs, kv_lens, q_entries, q_offs, q_lens,
           r2v_entries, r2v_offs, r2v_lens, mid_o, mid_lse, phase_node_nums, phase_node_offsets,
-          phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap, path, o_lse, row_ranges="detect"):
+          phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap, path, o_lse, row_ranges="detect",
+          phase_info=None):
     tensors = (q, k_buffer, v_buffer, o, kv_entries, kv_offs, kv_lens, q_entries, q_offs, q_lens,
                r2v_entries, r2v_offs, r2v_lens, mid_o, mid_lse)
     rest = (phase_node_nums, phase_node_offsets, phase_q_tile_sizes, phase_kv_tile_sizes,
             float(sm_scale), float(logit_cap))
-    a = _cached_args(tensors, rest, path, o_lse, row_ranges)
+    a = _cached_args(tensors, rest, path, o_lse, row_ranges, phase_info)
     lib = _lib.load()
     if q.device.index != torch.cuda.current_device():
         with torch.cuda.device(q.device):
@@ -256,14 +266,14 @@ def _call(fn_name, q, k_buffer, v_buffer, o, kv_entries, kv_offs, kv_lens, q_ent
     _lib.check(rc)
 
 
-def decode(*args, logit_cap=-1, path="auto", o_lse=None, row_ranges="detect"):
+def decode(*args, logit_cap=-1, path="auto", o_lse=None, row_ranges="detect", phase_info=None):
     """Stage 1 + stage 2.  Positional arguments are those of the reference's
     ``fasttree_decode`` up to and including ``sm_scale``."""
-    _call("ft_decode", *args, logit_cap, path, o_lse, row_ranges)
+    _call("ft_decode", *args, logit_cap, path, o_lse, row_ranges, phase_info)
 
 
-def stage1(*args, logit_cap=-1, path="auto", row_ranges="detect"):
-    _call("ft_stage1", *args, logit_cap, path, None, row_ranges)
+def stage1(*args, logit_cap=-1, path="auto", row_ranges="detect", phase_info=None):
+    _call("ft_stage1", *args, logit_cap, path, None, row_ranges, phase_info)
 
 
 def stage2(*args, logit_cap=-1, o_lse=None):
@@ -295,6 +305,30 @@ def decode_host_io(q_host, o_host, q_dev, k_buffer, v_buffer, o_dev, *rest, logi
     else:
         rc = lib.ft_decode_host_io(ctypes.byref(a), q_host.data_ptr(), o_host.data_ptr(), 1 if wait else 0)
     _lib.check(rc)
+
+
+def prepare_host_io(q_host, o_host, q_dev, k_buffer, v_buffer, o_dev, *rest, logit_cap=-1, path="auto",
+                    row_ranges="detect", wait=True):
+    """A prepared :func:`decode_host_io`: validates once, fills the argument block once and returns a callable
+    whose only work is the foreign call (on the CUDA stream that is current when it is CALLED).  The callable
+    keeps every tensor alive; build a new one when a tensor is replaced."""
+    decode_host_io(q_host, o_host, q_dev, k_buffer, v_buffer, o_dev, *rest, logit_cap=logit_cap, path=path,
+                   row_ranges=row_ranges, wait=True)          # validation, first-use costs, range look-up
+    pn, po, pq, pk, sm_scale = rest[11:16]
+    tensors = (q_dev, k_buffer, v_buffer, o_dev) + tuple(rest[:11])
+    a = build_args(*tensors, pn, po, pq, pk, float(sm_scale), logit_cap, path=path, row_ranges=row_ranges)
+    fn = _lib.load().ft_decode_host_io
+    ref, qp, op, flag = ctypes.byref(a), q_host.data_ptr(), o_host.data_ptr(), 1 if wait else 0
+    keep = (tensors, q_host, o_host, a)
+    device = q_dev.device
+
+    def run(_keep=keep):
+        a.stream = torch.cuda.current_stream(device).cuda_stream
+        rc = fn(ref, qp, op, flag)
+        if rc != 0:
+            _lib.check(rc)
+
+    return run
 
 
 def stage1_path_name(*args, logit_cap=-1, path="auto"):

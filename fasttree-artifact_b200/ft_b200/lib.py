@@ -79,6 +79,7 @@ class DecodeArgs(ctypes.Structure):
         ("sm_scale", ctypes.c_float), ("logit_cap", ctypes.c_float),
         ("stream", ctypes.c_void_p),
         ("vnode_q_kv_ranges", ctypes.c_void_p),
+        ("device_phase_info", ctypes.c_void_p),
     ]
 
 

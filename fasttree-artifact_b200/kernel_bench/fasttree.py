@@ -120,19 +120,30 @@ def fasttree_decode(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_o
 
 
 _STAGING = {}
+_HOST_IO_CALLS = {}
 
 
 def fasttree_decode_host_io(q, k_buffer, v_buffer, o, *aux_and_tiles, logit_cap=-1):
     """:func:`fasttree_decode` with ``q`` and ``o`` in pinned HOST memory (same positional arguments otherwise):
-    the query is copied to the device, the step runs, the output is copied back and the stream is synchronised,
+    the query is brought to the device, the step runs, the output lands in ``o`` and the stream is synchronised,
     all inside one call of the shared library (``ft_decode_host_io``) - the pattern of a decode loop whose
-    sampler lives on the host.  The device staging buffers are kept per (shape, dtype, device) and reused, so a
-    steady loop allocates nothing.  No counterpart in the reference, whose harness keeps Q and the output on the
-    device (kernel_bench/benchmark.py:88-128)."""
-    dev = k_buffer.device
-    key = (tuple(q.shape), q.dtype, dev)
-    stage = _STAGING.get(key)
-    if stage is None:
-        stage = (torch.empty(q.shape, dtype=q.dtype, device=dev), torch.empty(o.shape, dtype=o.dtype, device=dev))
-        _STAGING[key] = stage
-    _engine.decode_host_io(q, o, stage[0], k_buffer, v_buffer, stage[1], *aux_and_tiles, logit_cap=logit_cap)
+    sampler lives on the host.  The device staging buffers are kept per (shape, dtype, device) and reused, and
+    the filled argument block is remembered per set of tensor objects, so a steady loop allocates nothing and
+    spends its host time in one foreign call.  No counterpart in the reference, whose harness keeps Q and the
+    output on the device (kernel_bench/benchmark.py:88-128)."""
+    tiles = aux_and_tiles[13:16]
+    key = (id(q), id(k_buffer), id(v_buffer), id(o), id(aux_and_tiles[0]), id(aux_and_tiles[9]),
+           tiles[0][0], tiles[0][1], float(tiles[2]), logit_cap)
+    call = _HOST_IO_CALLS.get(key)
+    if call is None:
+        dev = k_buffer.device
+        skey = (tuple(q.shape), q.dtype, dev)
+        stage = _STAGING.get(skey)
+        if stage is None:
+            stage = (torch.empty(q.shape, dtype=q.dtype, device=dev), torch.empty(o.shape, dtype=o.dtype, device=dev))
+            _STAGING[skey] = stage
+        call = _engine.prepare_host_io(q, o, stage[0], k_buffer, v_buffer, stage[1], *aux_and_tiles, logit_cap=logit_cap)
+        if len(_HOST_IO_CALLS) >= 64:
+            _HOST_IO_CALLS.clear()
+        _HOST_IO_CALLS[key] = call
+    call()

@@ -118,6 +118,18 @@ typedef struct ft_decode_args {
                                          wide mma.sync) and by the generic kernel; the few-row kernels do not
                                          read it, so rows of vnodes with <= 16 query rows must cover their whole
                                          chunk (the planner of this library only narrows rows of many-row vnodes). */
+  const int32_t* device_phase_info;   /* NULL, or a DEVICE array {phase_node_nums[0], phase_node_nums[1],
+                                         phase_node_offsets[0], phase_node_offsets[1]} that stage 1 reads at run
+                                         time instead of the host values above (the two phases must be adjacent:
+                                         offset[1] = offset[0] + nums[0]).  The launch then does not depend on the
+                                         plan: one persistent grid of 2 CTAs per SM (FT_PATH_PERSIST, which
+                                         FT_PATH_AUTO selects here; 16-bit types, head_dim 128), so a decode step
+                                         captured in a CUDA graph stays valid when the plan tables, which live in
+                                         fixed-capacity device buffers, are rewritten for the next burst - what the
+                                         reference cannot do (it sizes its grids on the host and switches CUDA graphs
+                                         off, fasttree_sglang_plugin_v0_2_13/plugin.py:209-211).  batch, the table
+                                         pointers and num_partial_rows (the capacity of mid_o / mid_lse) stay
+                                         host-side arguments. */
 } ft_decode_args;
 
 /* Library version (major*10000 + minor*100 + patch). */
@@ -145,13 +157,14 @@ int ft_stage1(const ft_decode_args* args);
  * inside ft_decode it is launched as a programmatic dependent of stage 1. */
 int ft_stage2(const ft_decode_args* args);
 
-/* ft_decode fed from and drained to pinned host memory in one call: q_host ([batch, heads, head_dim], packed) is
- * copied to args->q, the decode runs, args->o is copied to o_host, all on args->stream with one cudaMemcpyAsync
- * per buffer; wait != 0 also synchronises the stream before returning.  args->q and args->o are device staging
- * buffers and must be packed.  This is the call pattern of a decode loop whose sampler runs on the host: the
- * reference's harness does the same with two torch copies around fasttree_decode
- * (kernel_bench/benchmark.py:88-128 keeps Q and the output on the device; its SGLang host reads the logits back
- * once per step). */
+/* ft_decode fed from and drained to pinned host memory in one call, on args->stream; wait != 0 also synchronises
+ * the stream before returning, so that o_host is valid.  q_host / o_host are packed [batch, heads, head_dim];
+ * args->q is a packed device staging buffer that receives the query.  When the host buffers are mapped into the
+ * device's address space (cudaHostAlloc / torch pinned memory) the query is fetched by a small copy kernel and
+ * stage 2 writes the output rows straight into o_host over PCIe - no copy-engine transfer on the critical path;
+ * args->o is then not written.  Otherwise: one cudaMemcpyAsync per buffer around the decode, through args->o.
+ * This is the call pattern of a decode loop whose sampler runs on the host; the reference's harness keeps Q and
+ * the output on the device (kernel_bench/benchmark.py:88-128). */
 int ft_decode_host_io(const ft_decode_args* args, const void* q_host, void* o_host, int wait);
 
 /* ft_decode for callers that cannot provide (or allocate) the mid_o / mid_lse scratch.  It has no counterpart

@@ -133,8 +133,9 @@ def test_monkey_patches_and_burst_loop(monkeypatch):
     created = {}
 
     class FakeMd:
-        def __init__(self, hq, hkv, d, device):
+        def __init__(self, hq, hkv, d, device, graph_safe=False):
             created["args"] = (hq, hkv, d, device)
+            created["graph_safe"] = graph_safe
 
     calls = []
     monkeypatch.setattr(plugin, "FastTreeMetadata", FakeMd)

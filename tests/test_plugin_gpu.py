@@ -79,3 +79,72 @@ def run_burst(name, planner, extra, dtype, steps):
             batch.out_cache_loc = torch.stack([rows[r][len(req.origin_input_ids) + len(req.output_ids)]
                                                for r, req in enumerate(batch.reqs)]).cuda()
             schedule.prepare_for_fasttree_step(batch, md)
+
+
+def test_captured_decode_step_survives_a_replan():
+    """``FastTreeMetadata(graph_safe=True)``: the decode call takes its phase split from device memory and runs
+    the persistent stage-1 kernel, whose launch does not depend on the plan.  A step captured ONCE in a CUDA graph
+    is replayed after the plan tables (fixed-capacity device buffers) have been rewritten for other bursts -
+    other trees, other vnode counts, same batch size and pools - and must give the bits of an eager call on the
+    new plan, and the right attention."""
+    from fasttree_sglang_plugin_v0_2_13 import attn_kernels
+    from oracle import ref_inputs
+    hq, hkv, d, dtype = 32, 8, 128, torch.float16
+    shapes = [([1, 3, 9], [100, 30, 7]), ([1, 9], [300, 11]), ([1, 9], [5, 70]), ([1, 1, 9], [700, 64, 1])]
+    pool, width, gen = 8192, 1024, [3, 0, 5, 1]
+    bursts = []
+    for i, (sizes, lens) in enumerate(shapes):
+        nodes = ref_inputs.layered_tree(sizes, lens)
+        generated = [gen[(r + i) % len(gen)] for r in range(9)]
+        bursts.append(sglang_standin.build_batch(nodes, 2, generated, pool, hkv, d, dtype, "cuda", seed=50 + i,
+                                                 max_context_len=width, steps=1))
+    base = bursts[0][0]
+    r2t = base.req_to_token_pool.req_to_token
+    k_buf, v_buf = base.token_to_kv_pool.get_key_buffer(0), base.token_to_kv_pool.get_value_buffer(0)
+    md = metadata.FastTreeMetadata(hq, hkv, d, "cuda", max_vnodes=1024, max_vnode_to_q_entries=4096,
+                                   max_batch_size=64, graph_safe=True)
+    q = torch.zeros(9, hq, d, dtype=dtype, device="cuda")
+    o = torch.zeros_like(q)
+    scale = 1.0 / d ** 0.5
+
+    def call():
+        attn_kernels.fasttree_decode(q, k_buf, v_buf, o, r2t, md.vnode_to_kv_offs, md.vnode_to_kv_lens,
+                                     md.vnode_to_q_entries, md.vnode_to_q_offs, md.vnode_to_q_lens,
+                                     md.req_to_vnode_entries, md.req_to_vnode_offs, md.req_to_vnode_lens,
+                                     md.mid_o, md.mid_lse, md.phase_node_nums, md.phase_node_offsets,
+                                     md.phase_q_tile_sizes, md.phase_kv_tile_sizes, scale, phase_info=md.phase_info_dev)
+
+    schedule.prepare_for_fasttree_meta(base, md)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        call()
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            call()
+    torch.cuda.current_stream().wait_stream(side)
+    plans = set()
+    g = torch.Generator(device="cuda").manual_seed(3)
+    for batch, rows in bursts[1:] + bursts[:1]:
+        # the pools are persistent in a serving process: bring this burst's contents into the captured tensors
+        r2t.copy_(batch.req_to_token_pool.req_to_token)
+        k_buf.copy_(batch.token_to_kv_pool.get_key_buffer(0))
+        v_buf.copy_(batch.token_to_kv_pool.get_value_buffer(0))
+        batch.req_to_token_pool.req_to_token = r2t
+        batch.token_to_kv_pool.k_buffer[0], batch.token_to_kv_pool.v_buffer[0] = k_buf, v_buf
+        schedule.prepare_for_fasttree_meta(batch, md)
+        plans.add((tuple(md.phase_node_nums), md.num_vnodes, md.num_partial_rows))
+        q.copy_((torch.randn(9, hq, d, generator=g, device="cuda") * 0.5).to(dtype))
+        o.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        replayed = o.clone()
+        assert lib.read_device_status() == 0
+        o.fill_(float("nan"))
+        call()
+        torch.cuda.synchronize()
+        assert torch.equal(replayed, o)
+        want = reference_attention(batch, rows, q, 0, 0, scale)
+        assert (replayed.float().cpu() - want).abs().max().item() <= 2e-3
+    assert len(plans) >= 3          # the replays really ran on different plans
