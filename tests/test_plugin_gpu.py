@@ -126,11 +126,14 @@ def test_captured_decode_step_survives_a_replan():
     torch.cuda.current_stream().wait_stream(side)
     plans = set()
     g = torch.Generator(device="cuda").manual_seed(3)
-    for batch, rows in bursts[1:] + bursts[:1]:
+    contents = [(b.req_to_token_pool.req_to_token.clone(), b.token_to_kv_pool.get_key_buffer(0).clone(),
+                 b.token_to_kv_pool.get_value_buffer(0).clone()) for b, _ in bursts]
+    for idx in (1, 2, 3, 0):
+        batch, rows = bursts[idx]
         # the pools are persistent in a serving process: bring this burst's contents into the captured tensors
-        r2t.copy_(batch.req_to_token_pool.req_to_token)
-        k_buf.copy_(batch.token_to_kv_pool.get_key_buffer(0))
-        v_buf.copy_(batch.token_to_kv_pool.get_value_buffer(0))
+        r2t.copy_(contents[idx][0])
+        k_buf.copy_(contents[idx][1])
+        v_buf.copy_(contents[idx][2])
         batch.req_to_token_pool.req_to_token = r2t
         batch.token_to_kv_pool.k_buffer[0], batch.token_to_kv_pool.v_buffer[0] = k_buf, v_buf
         schedule.prepare_for_fasttree_meta(batch, md)
