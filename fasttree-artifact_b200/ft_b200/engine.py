@@ -47,6 +47,15 @@ ROW_RANGE_MAGIC = 0x46545252          # "FTRR": trailer of a vnode_to_q_entries 
 _RANGE_CACHE = {}     # id(tensor) -> (weak reference to it, (version, data_ptr, numel), rows or -1)
 
 
+def _version_of(t):
+    """In-place-write counter of a tensor; tensors created under ``torch.inference_mode()`` keep none (a serving
+    host runs its decode loop there), and for those the answer is a constant."""
+    try:
+        return t._version
+    except RuntimeError:
+        return -1
+
+
 def pack_row_ranges(q_entries, ranges):
     """The B200 plan format's optional tenth table - per partial row the tokens
     ``[begin, end)`` of its vnode's KV chunk that the row attends to (int32
@@ -78,7 +87,7 @@ def split_q_entries(vnode_to_q_entries):
     n = t.numel()
     if n < 5 or (n - 2) % 3 != 0:
         return n, None
-    state = (t._version, t.data_ptr(), n)
+    state = (_version_of(t), t.data_ptr(), n)
     ident = id(t)
     known = _RANGE_CACHE.get(ident)
     if known is not None and known[0]() is t and known[1] == state:
@@ -226,7 +235,7 @@ def _cached_args(tensors, rest, path, o_lse, row_ranges, phase_info=None):
            id(phase_info) if phase_info is not None else None)
     ptrs = tuple([t.data_ptr() for t in persistent])
     hit = _ARG_CACHE.get(key)
-    if hit is not None and hit[1] == ptrs and (not is_detect or hit[3] == tensors[7]._version):
+    if hit is not None and hit[1] == ptrs and (not is_detect or hit[3] == _version_of(tensors[7])):
         a = hit[0]
         if not (q.is_cuda and o.is_cuda):
             raise ValueError("q / o must live on a CUDA device; the engine has no CPU path")
@@ -236,7 +245,7 @@ def _cached_args(tensors, rest, path, o_lse, row_ranges, phase_info=None):
         if len(_ARG_CACHE) >= _ARG_CACHE_MAX:
             _ARG_CACHE.clear()
         keep = (row_ranges if isinstance(row_ranges, torch.Tensor) else None, phase_info)
-        _ARG_CACHE[key] = (a, ptrs, persistent, tensors[7]._version, keep)
+        _ARG_CACHE[key] = (a, ptrs, persistent, _version_of(tensors[7]), keep)
     a.q, a.o = q.data_ptr(), o.data_ptr()
     if o_lse is not None:
         if (not o_lse.is_cuda or o_lse.dtype != torch.float32 or not o_lse.is_contiguous()

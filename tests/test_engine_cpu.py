@@ -28,3 +28,11 @@ def test_pack_row_ranges_rejects_a_mismatched_table():
     except ValueError:
         return
     raise AssertionError("a range table of the wrong length was accepted")
+
+
+def test_range_lookup_works_on_inference_tensors():
+    """A serving host decodes under torch.inference_mode(); such tensors have no version counter."""
+    with torch.inference_mode():
+        t = torch.arange(23, dtype=torch.int32)
+        rows, got = engine.split_q_entries(t)
+    assert rows == 23 and got is None
