@@ -642,7 +642,7 @@ def main():
                          "'' for none")
     ap.add_argument("--regions", type=int, default=20, help="timed regions of --steps steps each; the median is reported")
     ap.add_argument("--planner", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--path", default="auto", choices=["auto", "generic", "mma", "tcgen05", "persist"])
+    ap.add_argument("--path", default="auto", choices=["auto", "generic", "mma", "mma_wide", "tcgen05", "stream", "persist"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--ref-requests", type=int, default=16, help="requests per step of the CPU arm")
     ap.add_argument("--prewarm-s", type=float, default=0.3, help="seconds' worth of untimed steps before the warm-up (clock ramp)")

@@ -11,6 +11,7 @@
 
 #include "fasttree_b200.h"
 #include "ft_common.cuh"
+#include "ft_stage1_f32.cuh"
 #include "ft_stage1_generic.cuh"
 #include "ft_stage1_mma.cuh"
 #include "ft_stage1_narrow.cuh"
@@ -446,6 +447,29 @@ int launch_tensor(const ft::Stage1Params& p, const ft_decode_args* a, int hkv, c
   return launch_mma<T, D>(p, hkv, st);
 }
 
+// fp32 storage at head_dim 64 / 128 with 16-byte aligned rows: the tiled CUDA-core kernel
+bool f32_tiled_ok(const ft_decode_args* a) {
+  if (a->dtype != FT_F32 || (a->head_dim != 64 && a->head_dim != 128)) return false;
+  if (!aligned16(a->q) || !aligned16(a->k_buffer) || !aligned16(a->v_buffer)) return false;
+  return a->q_stride0 % 4 == 0 && a->q_stride1 % 4 == 0 && a->k_stride0 % 4 == 0 && a->k_stride1 % 4 == 0 &&
+         a->v_stride0 % 4 == 0 && a->v_stride1 % 4 == 0;
+}
+
+template <int D>
+int launch_f32(const ft::Stage1Params& p, int hkv, cudaStream_t st, int max_rows) {
+  using C = ft::F32Cfg<D>;
+  if (dry_run("stage1_f32_kernel")) return FT_OK;
+  static OncePerDevice once;
+  FT_CUDA_OK(raise_smem_limit(once, ft::stage1_f32_kernel<D>, C::SMEM_BYTES));
+  const int blocks_z = (max_rows + C::ROWS - 1) / C::ROWS;
+  if (blocks_z > 65535) return fail(FT_ERR_TOO_LARGE, "too many query rows per vnode for the fp32 kernel");
+  dim3 grid(p.node_count, hkv, blocks_z);
+  ft::stage1_f32_kernel<D><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(p);
+  FT_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return FT_OK;
+}
+
 template <typename T>
 int launch_generic(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
   if (dry_run("stage1_generic_kernel")) return FT_OK;
@@ -471,6 +495,10 @@ int launch_stage1_range(const ft_decode_args* a, int path, int offset, int count
     return a->head_dim == 128 ? launch_tensor<__nv_bfloat16, 128>(p, a, hkv, st, max_rows, path)
                               : launch_tensor<__nv_bfloat16, 64>(p, a, hkv, st, max_rows, path);
   }
+  // fp32 storage: the tiled kernel when the caller named no path (FT_PATH_GENERIC stays the scalar kernel) and the
+  // phase's request tile bounds its rows
+  if (a->path == FT_PATH_AUTO && f32_tiled_ok(a) && max_rows > 0 && max_rows < (1 << 20))
+    return a->head_dim == 128 ? launch_f32<128>(p, hkv, st, max_rows) : launch_f32<64>(p, hkv, st, max_rows);
   switch (a->dtype) {
     case FT_F16: return launch_generic<__half>(p, hkv, st);
     case FT_BF16: return launch_generic<__nv_bfloat16>(p, hkv, st);

@@ -31,7 +31,7 @@ def atol_for(dtype):
 def paths_for(c):
     fast = c["dtype"] != torch.float32 and c["d"] in (64, 128)
     if not fast:
-        return ["generic"]
+        return ["generic", "auto"]      # fp32 storage: the scalar kernel, and the tiled fp32 kernel that "auto" picks
     return ["generic", "mma", "mma_wide", "stream"] + (["tcgen05", "persist", "auto"] if c["d"] == 128 else [])
 
 
