@@ -129,6 +129,16 @@ def main(args):
         except Exception as exc:          # optional baseline: not installed, or no kernel for this GPU / shape
             print(f"sglang_flashinfer skipped ({type(exc).__name__}: {str(exc)[:120]})")
 
+    out_cascade = None
+    if args.choice in ("cascade", "all"):
+        try:
+            from flashinfer_wrap import cascade_preparation, cascade_decode
+            cwrap = cascade_preparation(tree_info, KV_ptrs, batch_size, args.num_qo_heads, args.num_kv_heads,
+                                        args.head_dim, dtype)
+            out_cascade = run_and_bench(lambda: cascade_decode(cwrap, Q, K_tree, V_tree), "flashinfer cascade").cpu()
+        except Exception as exc:          # optional baseline: not installed, or no kernel for this GPU / shape
+            print(f"cascade skipped ({type(exc).__name__}: {str(exc)[:120]})")
+
     for name in ("sglang_triton", "DeFT"):
         if args.choice in (name, "all"):
             print(f"{name} skipped (baseline kernels are not part of this build)")
@@ -139,6 +149,9 @@ def main(args):
     if out_fi is not None and out_tree is not None:
         ok = torch.allclose(out_fi, out_tree, rtol=1e-2, atol=1e-2)
         print("fasttree vs flashinfer Check passed!" if ok else "fasttree vs flashinfer Check failed!")
+    if out_cascade is not None and out_tree is not None:
+        ok = torch.allclose(out_cascade, out_tree, rtol=1e-2, atol=1e-2)
+        print("fasttree vs cascade Check passed!" if ok else "fasttree vs cascade Check failed!")
 
 
 if __name__ == "__main__":
@@ -158,7 +171,7 @@ if __name__ == "__main__":
     ap.add_argument("--head_dim", type=int, default=128)
     ap.add_argument("--signature", type=str, default=None)
     ap.add_argument("--choice", type=str, default="all",
-                    choices=["flash_attn", "fasttree", "sglang_triton", "sglang_flashinfer", "DeFT", "all"])
+                    choices=["flash_attn", "fasttree", "sglang_triton", "sglang_flashinfer", "cascade", "DeFT", "all"])
     ap.add_argument("--profile", action="store_true", default=False)
     ap.add_argument("--planner", type=str, default="b200", choices=["b200", "reference"],
                     help="b200: the 148-SM splitter; reference: tables identical to the reference planner")

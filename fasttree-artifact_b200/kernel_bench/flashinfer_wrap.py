@@ -46,3 +46,53 @@ def flashinfer_preparation(tree_info, KV_ptrs, batch_size, num_qo_heads, num_kv_
 def flashinfer_decode(wrapper, Q, K_tree, V_tree):
     """K_tree/V_tree [T, Hkv, D] are viewed as T pages of one token each."""
     return wrapper.run(Q, (K_tree.unsqueeze(1), V_tree.unsqueeze(1)))
+
+
+def cascade_levels(tree_info, KV_ptrs, batch_size):
+    """The tree as FlashInfer's multi-level cascade wants it (reference: kernel_bench/bench_cascade.py:117-159):
+    per tree depth the nodes of that depth in id order, each node's K/V rows as its pages and the (consecutive)
+    requests below it as its query range.  Works for any tree whose requests below a node are consecutive ids and
+    whose leaves all sit on the last level (the layered and the seeded irregular trees of this package)."""
+    depth = [0] * len(tree_info)
+    for i, nd in enumerate(tree_info):
+        depth[i] = 0 if nd.parent < 0 else depth[nd.parent] + 1
+    levels = max(depth) + 1
+    qo_indptr, kv_indptr, kv_indices = [], [], []
+    for lv in range(levels):
+        nodes = [i for i in range(len(tree_info)) if depth[i] == lv]
+        qo, kv, idx = [0], [0], []
+        covered = 0
+        for i in nodes:
+            reqs = sorted(tree_info[i].requests)
+            if not reqs:
+                continue
+            if reqs != list(range(reqs[0], reqs[0] + len(reqs))) or reqs[0] != covered:
+                raise ValueError("cascade needs every level to split the requests into consecutive ranges")
+            covered += len(reqs)
+            qo.append(covered)
+            idx.extend(range(KV_ptrs[i], KV_ptrs[i + 1]))
+            kv.append(len(idx))
+        if covered != batch_size:
+            raise ValueError("cascade needs every request to pass through every level")
+        qo_indptr.append(qo)
+        kv_indptr.append(kv)
+        kv_indices.append(idx)
+    return qo_indptr, kv_indptr, kv_indices
+
+
+def cascade_preparation(tree_info, KV_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, dtype, device="cuda"):
+    """FlashInfer's MultiLevelCascadeAttentionWrapper over the flat tree tensors, page size 1: the engine of the
+    reference's cascade yard-stick (kernel_bench/bench_cascade.py), an optional baseline like the paged decode."""
+    from flashinfer import MultiLevelCascadeAttentionWrapper
+    qo_indptr, kv_indptr, kv_indices = cascade_levels(tree_info, KV_ptrs, batch_size)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
+    workspace = torch.empty(512 * 1024 * 1024, dtype=torch.uint8, device=device)
+    wrapper = MultiLevelCascadeAttentionWrapper(len(qo_indptr), workspace, "NHD")
+    wrapper.plan([i32(q) for q in qo_indptr], [i32(k) for k in kv_indptr], [i32(x) for x in kv_indices],
+                 [torch.ones(len(k) - 1, dtype=torch.int32, device=device) for k in kv_indptr],
+                 num_qo_heads, num_kv_heads, head_dim, 1, q_data_type=dtype)
+    return wrapper
+
+
+def cascade_decode(wrapper, Q, K_tree, V_tree):
+    return wrapper.run(Q, (K_tree.unsqueeze(1), V_tree.unsqueeze(1)))

@@ -344,3 +344,17 @@ def test_product_tree_builders_match_the_oracle():
     ref_inputs.assign_requests(theirs)
     assert [(n.parent, n.seqlen, n.num_children, n.requests) for n in mine] == \
            [(n.parent, n.seqlen, n.num_children, n.requests) for n in theirs]
+
+
+def test_cascade_levels_describe_the_tree():
+    """The multi-level cascade adapter's page lists: per depth every node's rows once, the requests split into
+    consecutive ranges."""
+    import flashinfer_wrap
+    import kv_tree_simple
+    for rows in (tree_generation.generate_tree([1, 4, 16], [256, 64, 32]), tree_generation.generate_random_tree(4, 1)):
+        tree = kv_tree_simple.tree_from_rows(rows)
+        batch, ptrs = kv_tree_simple.assign_requests(tree)
+        qo, kv, idx = flashinfer_wrap.cascade_levels(tree, ptrs, batch)
+        assert sorted(x for lv in idx for x in lv) == list(range(ptrs[-1]))
+        for q, k in zip(qo, kv):
+            assert q[0] == 0 and q[-1] == batch and len(q) == len(k) and all(b > a for a, b in zip(q, q[1:]))
