@@ -377,8 +377,12 @@ class Problem:
         def draw(*shape):
             return torch.randn(*shape, generator=g, device=dev, dtype=torch.float32)
 
-        self.ks = [draw(self.tokens, self.hkv_l, HEAD_DIM).to(self.dtype) for _ in range(copies)]
-        self.vs = [draw(self.tokens, self.hkv_l, HEAD_DIM).to(self.dtype) for _ in range(copies)]
+        if args.kv_layout == "head_major":     # [Hkv, T, D] storage handed to the engine as a strided [T, Hkv, D] view
+            self.ks = [draw(self.hkv_l, self.tokens, HEAD_DIM).to(self.dtype).transpose(0, 1) for _ in range(copies)]
+            self.vs = [draw(self.hkv_l, self.tokens, HEAD_DIM).to(self.dtype).transpose(0, 1) for _ in range(copies)]
+        else:                                  # the reference's layout: [T, Hkv, D], packed
+            self.ks = [draw(self.tokens, self.hkv_l, HEAD_DIM).to(self.dtype) for _ in range(copies)]
+            self.vs = [draw(self.tokens, self.hkv_l, HEAD_DIM).to(self.dtype) for _ in range(copies)]
         self.q = (draw(batch, self.hq_l, HEAD_DIM) * qs).to(self.dtype)
         self.o = torch.empty_like(self.q)
         self.o_all = torch.empty(world, batch, self.hq_l, HEAD_DIM, device=dev, dtype=self.dtype) if world > 1 else None
@@ -612,6 +616,7 @@ def measure(ctx, workload, primary):
     out["roofline"] = p.roofline(min(args.steps, GRAPH_CHUNK), regions, allow_graph)
     out["plan"] = {"planner": args.planner, "vnodes": p.n_vnodes, "partial_rows": p.n_rows, "plan_ms_host": p.plan_ms,
                    "requests": p.batch, "tokens": p.tokens}
+    out["kv_layout"] = args.kv_layout
     out["l2"] = f"K/V rotated over {p.copies} copies = {p.copies * p.kv_bytes / 2 ** 20:.0f} MiB per GPU (> 126 MiB L2)"
     out["hbm_gbs_whole_step"] = p.algo_bytes() * ctx.world / (t["us"] * 1e-6) / 1e9
     if ctx.world == 1 and not args.no_reference_triton:
@@ -644,6 +649,9 @@ def main():
     ap.add_argument("--planner", default="b200", choices=["b200", "reference"])
     ap.add_argument("--path", default="auto", choices=["auto", "generic", "mma", "mma_wide", "tcgen05", "stream", "persist"])
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--kv-layout", default="token_major", choices=["token_major", "head_major"],
+                    help="token_major: K/V stored [T, Hkv, D] as the reference's tree tensors and SGLang's pool are; "
+                         "head_major: stored [Hkv, T, D] and passed as a strided view (an experiment on DRAM locality)")
     ap.add_argument("--ref-requests", type=int, default=16, help="requests per step of the CPU arm")
     ap.add_argument("--prewarm-s", type=float, default=0.3, help="seconds' worth of untimed steps before the warm-up (clock ramp)")
     ap.add_argument("--planner-opt", default="", help="comma-separated B200Model overrides, e.g. waves=3,min_chunk=64")

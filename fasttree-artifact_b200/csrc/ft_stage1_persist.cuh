@@ -384,8 +384,13 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             float2 e = __ffma2_rn(make_float2(s[2 * i], s[2 * i + 1]), sc2, no2);
-            e.x = fast_exp2(e.x);
-            e.y = fast_exp2(e.y);
+            if (FT_EXP2_FMA_EVERY > 0 && (i % (FT_EXP2_FMA_EVERY > 0 ? FT_EXP2_FMA_EVERY : 1)) == (FT_EXP2_FMA_EVERY > 0 ? FT_EXP2_FMA_EVERY : 1) - 1) {
+              e.x = exp2_fma(e.x);
+              e.y = exp2_fma(e.y);
+            } else {
+              e.x = fast_exp2(e.x);
+              e.y = fast_exp2(e.y);
+            }
             sum2 = __fadd2_rn(sum2, e);
             w[i] = pack2<T>(e.x, e.y);
           }

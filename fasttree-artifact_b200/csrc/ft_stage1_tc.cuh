@@ -159,6 +159,23 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
+// 2^x on the FMA / ALU pipes: floor(x) is peeled off with a round-down add of 1.5 * 2^23 (the integer lands in the
+// low mantissa bits), a cubic gives 2^frac to 9e-5 relative (far below the rounding of P to its 16-bit type), and the
+// integer is added back into the exponent field.  Exactly 0 for x <= -126 (masked scores are -inf).  Used for a
+// share of the softmax's exponentials where the MUFU unit (ex2.approx: a quarter-rate pipe) is the limiter.
+__device__ __forceinline__ float exp2_fma(float x) {
+  const float xc = fmaxf(x, -126.f);
+  float t;
+  asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(t) : "f"(xc), "f"(12582912.f));
+  const float f = xc - (t - 12582912.f);
+  const float p = fmaf(f, fmaf(f, fmaf(f, 0.07706569f, 0.22764646f), 0.69511646f), 1.f);
+  const float r = __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+  return x > -126.f ? r : 0.f;
+}
+#ifndef FT_EXP2_FMA_EVERY
+#define FT_EXP2_FMA_EVERY 0  // n > 0: every n-th pair of a row's 32 score pairs takes exp2_fma instead of ex2.approx
+#endif
+
 // Bounded wait for the phase of `bar` with the given parity.  Gives up after WAIT_LIMIT probes or as soon as
 // another role has raised the CTA's abort flag; the caller then raises the flag itself and unwinds.
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
@@ -322,8 +339,13 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
 #pragma unroll
           for (int i = 0; i < 32; ++i) {  // scores stay unscaled until the exponent: one packed FMA per pair
             float2 x = __ffma2_rn(make_float2(s[2 * i], s[2 * i + 1]), sc2, no2);
-            x.x = fast_exp2(x.x);
-            x.y = fast_exp2(x.y);
+            if (FT_EXP2_FMA_EVERY > 0 && (i % (FT_EXP2_FMA_EVERY > 0 ? FT_EXP2_FMA_EVERY : 1)) == (FT_EXP2_FMA_EVERY > 0 ? FT_EXP2_FMA_EVERY : 1) - 1) {
+              x.x = exp2_fma(x.x);
+              x.y = exp2_fma(x.y);
+            } else {
+              x.x = fast_exp2(x.x);
+              x.y = fast_exp2(x.y);
+            }
             sum2 = __fadd2_rn(sum2, x);
             w[i] = pack2<T>(x.x, x.y);
           }
