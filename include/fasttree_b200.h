@@ -97,8 +97,12 @@ typedef struct ft_decode_args {
   int64_t num_partial_rows;
   int32_t phase_node_nums[2];         /* vnodes per phase (reference: big / small request tiles) */
   int32_t phase_node_offsets[2];
-  int32_t phase_q_tile_sizes[2];      /* accepted for signature compatibility; the kernels size themselves from q_lens */
-  int32_t phase_kv_tile_sizes[2];
+  int32_t phase_q_tile_sizes[2];      /* requests per vnode of each phase AT MOST: tile x GQA group bounds the query rows
+                                         of the phase's tasks and selects its kernel (> 16 rows: many-row kernels, else
+                                         few-row kernels; fp32: row blocks of the tiled kernel).  The kernels read the
+                                         actual counts from vnode_to_q_lens, but rows beyond the declared bound are
+                                         dropped and flagged (FT_DEV_BAD_ROW_INDEX).  <= 0 = unknown (slow, safe choice). */
+  int32_t phase_kv_tile_sizes[2];     /* accepted for signature compatibility; the kernels use 64-token tiles */
   /* scratch (caller-owned) ------------------------------------------------ */
   float* mid_o;                       /* [num_partial_rows, num_qo_heads, head_dim] */
   float* mid_lse;                     /* [num_partial_rows, num_qo_heads]           */
@@ -181,7 +185,8 @@ int ft_decode_host_io(const ft_decode_args* args, const void* q_host, void* o_ho
  * Limit: num_partial_rows * num_qo_heads * (head_dim + 1) * 4 bytes must fit in the array (e.g. 1016 partial
  * rows at 32 heads x 128); larger plans get FT_ERR_TOO_LARGE and must use ft_decode.
  * Set-up: the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
- * device current); make that first call before any stream capture begins.
+ * device current); make that first call before any stream capture begins.  The address is remembered per device
+ * for the life of the process: after cudaDeviceReset the library must be reloaded.
  * Sharing: every call on a device uses the same array, which still holds the previous call's partials; stage 1
  * overwrites every row stage 2 reads, so nothing needs clearing, but two calls that overlap on the GPU
  * (different streams, or several threads) race on it - serialise them. */

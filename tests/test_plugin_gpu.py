@@ -45,14 +45,20 @@ def test_serving_traffic_shapes_through_the_hook(name):
     run_burst(name, "b200", 2, torch.float16, steps=2)
 
 
-def run_burst(name, planner, extra, dtype, steps):
+@pytest.mark.parametrize("name", ["long_tail", "system_4x128", "small_g4"])
+def test_decode_burst_in_graph_safe_mode(name):
+    """The same bursts with the phase split read on the device and the persistent stage-1 kernel behind the hook."""
+    run_burst(name, "b200", 2, torch.float16, steps=3, graph_safe=True)
+
+
+def run_burst(name, planner, extra, dtype, steps, graph_safe=False):
     from sglang.srt.layers.radix_attention import RadixAttention
     from sglang.srt.model_executor.forward_batch_info import InputMetadata
 
     batch, rows, hq, hkv = plugin_cases.build(name, device="cuda", dtype=dtype, extra_prompt=extra, steps=steps)
     d = 128
     md = metadata.FastTreeMetadata(hq, hkv, d, "cuda", max_vnodes=4096, max_vnode_to_q_entries=8192,
-                                   max_batch_size=512, planner=planner)
+                                   max_batch_size=512, planner=planner, graph_safe=graph_safe)
     plugin._replace_fwd_batch_info()
     plugin._replace_radix_attn()
     attn = RadixAttention(hq, d, 1.0 / d ** 0.5, hkv, 0)
