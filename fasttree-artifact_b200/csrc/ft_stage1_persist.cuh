@@ -358,17 +358,23 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
         uint32_t w[32];
         if (warp_live) {
           float s[64];
-          tmem_ld32(s_col, *reinterpret_cast<float(*)[32]>(&s[0]));
-          tmem_ld32(s_col + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+          tmem_ld32_nowait(s_col, *reinterpret_cast<float(*)[32]>(&s[0]));  // both halves in flight, one wait
+          tmem_ld32_nowait(s_col + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+          tmem_wait_ld();
           const int lo = r_lo - j * C::TILE, hi = r_hi - j * C::TILE;
           if (lo > 0 || hi < C::TILE) {
 #pragma unroll
             for (int c = 0; c < 64; ++c)
               if (c < lo || c >= hi) s[c] = -INFINITY;
           }
-          float mx = fmaxf(s[0], s[1]);
+          // four independent chains (one warp or two per scheduler cannot hide a 32-deep dependent chain)
+          float mx4[4] = {fmaxf(s[0], s[1]), fmaxf(s[2], s[3]), fmaxf(s[4], s[5]), fmaxf(s[6], s[7])};
 #pragma unroll
-          for (int c = 2; c < 64; c += 2) asm("max.f32 %0, %0, %1, %2;" : "+f"(mx) : "f"(s[c]), "f"(s[c + 1]));
+          for (int c = 8; c < 64; c += 8) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) asm("max.f32 %0, %0, %1, %2;" : "+f"(mx4[k]) : "f"(s[c + 2 * k]), "f"(s[c + 2 * k + 1]));
+          }
+          float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
           mx *= scale2;  // scale2 > 0
           if (mx > m_used + 8.f || m_used == -INFINITY) {  // the offset may lag the true maximum by up to 2^8
             grow = mx > -INFINITY;
@@ -380,7 +386,7 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
           l_run *= corr;
           const float neg_off = m_used == -INFINITY ? 0.f : -m_used;
           const float2 sc2 = make_float2(scale2, scale2), no2 = make_float2(neg_off, neg_off);
-          float2 sum2 = make_float2(0.f, 0.f);
+          float2 sum4[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             float2 e = __ffma2_rn(make_float2(s[2 * i], s[2 * i + 1]), sc2, no2);
@@ -391,10 +397,13 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
               e.x = fast_exp2(e.x);
               e.y = fast_exp2(e.y);
             }
-            sum2 = __fadd2_rn(sum2, e);
+            sum4[i & 3] = __fadd2_rn(sum4[i & 3], e);
             w[i] = pack2<T>(e.x, e.y);
           }
-          l_run += sum2.x + sum2.y;
+          {
+            const float2 sum2 = __fadd2_rn(__fadd2_rn(sum4[0], sum4[1]), __fadd2_rn(sum4[2], sum4[3]));
+            l_run += sum2.x + sum2.y;
+          }
         }
         // P_t goes to the S buffer just read, which the tensor core does not write again before it has consumed it
         // (the MMA warp waits for P.V of tile t before it issues S of tile t + 2).  Bookkeeping first: P.V of tile

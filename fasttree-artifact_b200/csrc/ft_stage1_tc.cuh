@@ -145,6 +145,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
       : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
+// 32 columns without the wait: for callers that issue several loads and wait once (tmem_wait_ld)
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, float (&v)[32]) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
   const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
   asm volatile(
@@ -307,8 +321,9 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           if (j == 5 && tid == 0) FT_TL_MARK(10);
           float s[64];
           const uint32_t s_col = t_lane + C::S_COL + b * C::TILE;
-          tmem_ld32(s_col, *reinterpret_cast<float(*)[32]>(&s[0]));
-          tmem_ld32(s_col + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+          tmem_ld32_nowait(s_col, *reinterpret_cast<float(*)[32]>(&s[0]));  // both halves in flight, one wait
+          tmem_ld32_nowait(s_col + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+          tmem_wait_ld();
           tc_fence_before();
           mbar_arrive(bar(C::S_EMPTY + b));  // the scores are in registers: the buffer may take tile j+2
           // columns outside [lo, hi) are padding (last tile) or tokens this row does not attend to
@@ -318,9 +333,14 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
             for (int c = 0; c < 64; ++c)
               if (c < lo || c >= hi) s[c] = -INFINITY;
           }
-          float mx = fmaxf(s[0], s[1]);
+          // four independent chains (one warp or two per scheduler cannot hide a 32-deep dependent chain)
+          float mx4[4] = {fmaxf(s[0], s[1]), fmaxf(s[2], s[3]), fmaxf(s[4], s[5]), fmaxf(s[6], s[7])};
 #pragma unroll
-          for (int c = 2; c < 64; c += 2) asm("max.f32 %0, %0, %1, %2;" : "+f"(mx) : "f"(s[c]), "f"(s[c + 1]));
+          for (int c = 8; c < 64; c += 8) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) asm("max.f32 %0, %0, %1, %2;" : "+f"(mx4[k]) : "f"(s[c + 2 * k]), "f"(s[c + 2 * k + 1]));
+          }
+          float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
           mx *= scale2;  // scale2 > 0
           float corr = 1.f;
           bool grow = false;
@@ -334,7 +354,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           l_run *= corr;
           const float neg_off = m_used == -INFINITY ? 0.f : -m_used;
           const float2 sc2 = make_float2(scale2, scale2), no2 = make_float2(neg_off, neg_off);
-          float2 sum2 = make_float2(0.f, 0.f);
+          float2 sum4[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
           uint32_t w[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) {  // scores stay unscaled until the exponent: one packed FMA per pair
@@ -346,10 +366,13 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
               x.x = fast_exp2(x.x);
               x.y = fast_exp2(x.y);
             }
-            sum2 = __fadd2_rn(sum2, x);
+            sum4[i & 3] = __fadd2_rn(sum4[i & 3], x);
             w[i] = pack2<T>(x.x, x.y);
           }
-          l_run += sum2.x + sum2.y;
+          {
+            const float2 sum2 = __fadd2_rn(__fadd2_rn(sum4[0], sum4[1]), __fadd2_rn(sum4[2], sum4[3]));
+            l_run += sum2.x + sum2.y;
+          }
           // P.V of the previous tile must be done before P and O are touched
           if (j == 5 && tid == 0) FT_TL_MARK(11);
           if (j > 0) {
