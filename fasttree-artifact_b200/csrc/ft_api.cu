@@ -6,6 +6,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <mutex>
+#include <utility>
 #include <cstdio>
 #include <cstring>
 
@@ -197,6 +198,26 @@ ft::Stage1Params stage1_params(const ft_decode_args* a) {
   return p;
 }
 
+// Every stage-1 kernel is launched with permission to be scheduled before the preceding kernel of the stream has
+// drained (programmatic dependent launch).  The kernels do nothing but on-chip set-up before their
+// griddepcontrol.wait, which returns once the preceding kernel has completed and its writes are visible, so the
+// permission is safe after any kernel; it pays after kernels that release their dependents early, as both stages of
+// this library do: back-to-back decode calls overlap each launch and set-up with the previous kernel's tail.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_early(void (*kernel)(KArgs...), dim3 grid, unsigned block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 template <typename T, int D>
 int launch_mma(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
   using C = ft::MmaCfg<D>;
@@ -204,8 +225,7 @@ int launch_mma(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
   static OncePerDevice once;
   FT_CUDA_OK(raise_smem_limit(once, ft::stage1_mma_kernel<T, D>, C::SMEM_BYTES));
   const unsigned grid = (unsigned)p.node_count * (unsigned)hkv;
-  ft::stage1_mma_kernel<T, D><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(p);
-  FT_CUDA_OK(cudaGetLastError());
+  FT_CUDA_OK(launch_early(ft::stage1_mma_kernel<T, D>, grid, C::THREADS, C::SMEM_BYTES, st, p));
   count_launch();
   return FT_OK;
 }
@@ -217,8 +237,7 @@ int launch_narrow(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
   static OncePerDevice once;
   FT_CUDA_OK(raise_smem_limit(once, ft::stage1_narrow_kernel<T, D>, C::SMEM_BYTES));
   const unsigned grid = (unsigned)p.node_count * (unsigned)hkv;
-  ft::stage1_narrow_kernel<T, D><<<grid, 128, C::SMEM_BYTES, st>>>(p);
-  FT_CUDA_OK(cudaGetLastError());
+  FT_CUDA_OK(launch_early(ft::stage1_narrow_kernel<T, D>, grid, 128, C::SMEM_BYTES, st, p));
   count_launch();
   return FT_OK;
 }
@@ -245,8 +264,7 @@ int launch_stream(const ft::TcParams& tp, int hkv, cudaStream_t st) {
   const int64_t tasks = (int64_t)tp.p.node_count * hkv;
   const int64_t slots = 2LL * sm_count(dev);
   const unsigned grid = (unsigned)(tasks < slots ? tasks : slots);
-  ft::stage1_stream_kernel<T, D><<<grid, 128, C::SMEM_BYTES, st>>>(tp);
-  FT_CUDA_OK(cudaGetLastError());
+  FT_CUDA_OK(launch_early(ft::stage1_stream_kernel<T, D>, grid, 128, C::SMEM_BYTES, st, tp));
   count_launch();
   return FT_OK;
 }
@@ -355,8 +373,7 @@ int launch_tc(const ft::TcParams& p, int hkv, cudaStream_t st) {
   static OncePerDevice once;
   FT_CUDA_OK(raise_smem_limit(once, ft::stage1_tc_kernel<T>, C::SMEM_BYTES));
   const unsigned grid = (unsigned)p.p.node_count * (unsigned)hkv;
-  ft::stage1_tc_kernel<T><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(p);
-  FT_CUDA_OK(cudaGetLastError());
+  FT_CUDA_OK(launch_early(ft::stage1_tc_kernel<T>, grid, C::THREADS, C::SMEM_BYTES, st, p));
   count_launch();
   return FT_OK;
 }
@@ -388,8 +405,7 @@ int launch_persist(ft::TcParams p, int hkv, cudaStream_t st) {
   if (tasks <= 0) return FT_OK;
   if (tasks > 0x7fffffffLL) return fail(FT_ERR_TOO_LARGE, "vnodes x kv heads exceeds the task limit");
   const unsigned grid = (unsigned)(tasks < slots ? tasks : slots);
-  ft::stage1_persist_kernel<T><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(p);
-  FT_CUDA_OK(cudaGetLastError());
+  FT_CUDA_OK(launch_early(ft::stage1_persist_kernel<T>, grid, C::THREADS, C::SMEM_BYTES, st, p));
   count_launch();
   return FT_OK;
 }
@@ -421,8 +437,7 @@ int launch_fused(ft::TcParams p, int hkv, cudaStream_t st) {
   if (wide + few_ctas > 0x7fffffffLL) return fail(FT_ERR_TOO_LARGE, "vnodes x kv heads exceeds the grid limit");
   p.p.workers = (int)workers;
   p.p.lead_wide = (int)lead;
-  ft::stage1_fused_kernel<T><<<(unsigned)(wide + few_ctas), ft::TcCfg::THREADS, smem, st>>>(p);
-  FT_CUDA_OK(cudaGetLastError());
+  FT_CUDA_OK(launch_early(ft::stage1_fused_kernel<T>, (unsigned)(wide + few_ctas), ft::TcCfg::THREADS, smem, st, p));
   count_launch();
   return FT_OK;
 }
@@ -464,8 +479,7 @@ int launch_f32(const ft::Stage1Params& p, int hkv, cudaStream_t st, int max_rows
   const int blocks_z = (max_rows + C::ROWS - 1) / C::ROWS;
   if (blocks_z > 65535) return fail(FT_ERR_TOO_LARGE, "too many query rows per vnode for the fp32 kernel");
   dim3 grid(p.node_count, hkv, blocks_z);
-  ft::stage1_f32_kernel<D><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(p);
-  FT_CUDA_OK(cudaGetLastError());
+  FT_CUDA_OK(launch_early(ft::stage1_f32_kernel<D>, grid, C::THREADS, C::SMEM_BYTES, st, p));
   count_launch();
   return FT_OK;
 }
@@ -474,8 +488,7 @@ template <typename T>
 int launch_generic(const ft::Stage1Params& p, int hkv, cudaStream_t st) {
   if (dry_run("stage1_generic_kernel")) return FT_OK;
   dim3 grid(p.node_count, hkv);
-  ft::stage1_generic_kernel<T><<<grid, 128, 0, st>>>(p);
-  FT_CUDA_OK(cudaGetLastError());
+  FT_CUDA_OK(launch_early(ft::stage1_generic_kernel<T>, grid, 128, 0, st, p));
   count_launch();
   return FT_OK;
 }

@@ -41,8 +41,21 @@ __device__ __forceinline__ unsigned long long timeline_now() {
   do {                                                                         \
     if (blockIdx.x < ft::FT_TIMELINE_CTAS) ft::g_timeline[16 * blockIdx.x + 4 + (i)] = ft::timeline_now(); \
   } while (0)
+// -DFT_TL_TILE=n moves the per-tile marks of the tensor-core kernel to tile n and swaps the start-up marks 2, 5, 6, 7 for
+// {tile n+1's scores seen, scores in registers, row maximum known, P stored}.
+#ifdef FT_TL_TILE
+#define FT_TL_DETAIL_MARK(i) FT_TL_MARK(i)
+#define FT_TL_COARSE_MARK(i) do { } while (0)
+#else
+#define FT_TL_TILE 5
+#define FT_TL_DETAIL_MARK(i) do { } while (0)
+#define FT_TL_COARSE_MARK(i) FT_TL_MARK(i)
+#endif
 #else
 #define FT_TL_MARK(i) do { } while (0)
+#define FT_TL_DETAIL_MARK(i) do { } while (0)
+#define FT_TL_COARSE_MARK(i) do { } while (0)
+#define FT_TL_TILE 5
 #define FT_TL_BEGIN() do { } while (0)
 #define FT_TL_END(kind) do { } while (0)
 #endif

@@ -34,6 +34,7 @@ template <int D>
 __global__ void __launch_bounds__(128) stage1_f32_kernel(Stage1Params p) {
   using C = F32Cfg<D>;
   allow_dependent_launch();
+  wait_for_prior_grid();  // nothing of the preceding kernel's is read or overwritten before this
   extern __shared__ __align__(16) float smem_f32[];
   float* q_s = smem_f32;
   float* k_s = smem_f32 + C::K_OFF;

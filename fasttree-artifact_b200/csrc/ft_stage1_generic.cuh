@@ -16,6 +16,7 @@ namespace ft {
 template <typename T>
 __global__ void __launch_bounds__(128) stage1_generic_kernel(Stage1Params p) {
   allow_dependent_launch();
+  wait_for_prior_grid();  // nothing of the preceding kernel's is read or overwritten before this
   constexpr int MAXJ = 8;  // 8 x 32 lanes = head_dim up to 256
   constexpr int TB = 4;    // tokens per step (more in flight per step measured slower: register pressure)
   const int vn = blockIdx.x + p.node_offset;

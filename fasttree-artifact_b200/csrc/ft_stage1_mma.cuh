@@ -333,6 +333,7 @@ __device__ __forceinline__ void mma_tile(const uint32_t k_sm, const uint32_t v_s
 template <typename T, int D>
 __global__ void __launch_bounds__(128, 2) stage1_mma_kernel(Stage1Params p) {
   allow_dependent_launch();
+  wait_for_prior_grid();  // nothing of the preceding kernel's is read or overwritten before this
   using C = MmaCfg<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t q_sm = smem_u32(smem);

@@ -290,6 +290,7 @@ __device__ __forceinline__ void narrow_dispatch(const Stage1Params& p, uint8_t* 
 template <typename T, int D>
 __global__ void __launch_bounds__(128, 2) stage1_narrow_kernel(Stage1Params p) {
   allow_dependent_launch();
+  wait_for_prior_grid();  // nothing of the preceding kernel's is read or overwritten before this
   extern __shared__ __align__(1024) uint8_t smem[];
   int vn, kvh;
   task_of_block(p, blockIdx.x, vn, kvh);

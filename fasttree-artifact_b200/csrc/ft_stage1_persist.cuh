@@ -150,18 +150,6 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = p.group, H = p.num_kv_heads;
-  // the launch's vnode range: host arguments, or read from the device so that the launch outlives the plan
-  int node_offset = p.node_offset, node_count = p.node_count;
-  if (p.dev_phase != nullptr) {
-    const int n0 = max(__ldg(p.dev_phase + 0), 0), n1 = max(__ldg(p.dev_phase + 1), 0);
-    node_offset = max(__ldg(p.dev_phase + 2), 0);
-    node_count = n0 + n1;
-    if (n0 > 0 && n1 > 0 && __ldg(p.dev_phase + 3) != node_offset + n0) {  // the phases must be adjacent
-      if (threadIdx.x == 0) flag_error(FT_DEV_BAD_ROW_INDEX);
-      node_count = n0;
-    }
-  }
-  const int total_tasks = (int)min((long long)node_count * H, 0x7fffffffLL);
   const float scale2 = p.sm_scale * 1.4426950408889634f;
   const uint32_t row_lim = (uint32_t)(p.kv_rows < 0x7fffffffLL ? p.kv_rows : 0x7fffffffLL);
 
@@ -212,6 +200,19 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = usable ? *tmem_slot : 0u;
+  wait_for_prior_grid();  // everything above is on-chip set-up; the preceding kernel's results are visible from here on
+  // the launch's vnode range: host arguments, or read from the device so that the launch outlives the plan
+  int node_offset = p.node_offset, node_count = p.node_count;
+  if (p.dev_phase != nullptr) {
+    const int n0 = max(__ldg(p.dev_phase + 0), 0), n1 = max(__ldg(p.dev_phase + 1), 0);
+    node_offset = max(__ldg(p.dev_phase + 2), 0);
+    node_count = n0 + n1;
+    if (n0 > 0 && n1 > 0 && __ldg(p.dev_phase + 3) != node_offset + n0) {  // the phases must be adjacent
+      if (threadIdx.x == 0) flag_error(FT_DEV_BAD_ROW_INDEX);
+      node_count = n0;
+    }
+  }
+  const int total_tasks = (int)min((long long)node_count * H, 0x7fffffffLL);
   if (tid == 0) FT_TL_MARK(0);
 #ifdef FT_TIMELINE
   long long tl_s = 0, tl_epi = 0, tl_task = 0, tl_pv = 0, tl_c = 0;

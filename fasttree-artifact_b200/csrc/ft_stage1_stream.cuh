@@ -537,6 +537,7 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
 template <typename T, int D>
 __global__ void __launch_bounds__(128, 2) stage1_stream_kernel(const __grid_constant__ TcParams tp) {
   allow_dependent_launch();
+  wait_for_prior_grid();  // nothing of the preceding kernel's is read or overwritten before this
   extern __shared__ __align__(1024) uint8_t smem[];
   stream_worker<T, D>(tp, smem, 0, tp.p.node_count * tp.p.num_kv_heads, (int)blockIdx.x, (int)gridDim.x);
 }

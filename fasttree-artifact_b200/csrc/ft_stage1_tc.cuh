@@ -217,22 +217,27 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
   auto bar = [&](int i) { return bars + 8u * i; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int q_off = p.q_offs[vn], q_len = p.q_lens[vn];
-  const int kv_off = p.kv_offs[vn], kv_len = max(p.kv_lens[vn], 0);
-  const int G = p.group;
-  const int rows = q_len * G;
-  if (rows <= 0) return;
   if ((sm & 1023u) != 0u) {  // the swizzled operand layout needs a 1024-byte aligned window
     if (tid == 0) flag_error(FT_DEV_WAIT_TIMEOUT);
     return;
   }
-  const float scale2 = p.sm_scale * 1.4426950408889634f;
-  const int ntiles = (kv_len + C::TILE - 1) / C::TILE;
-  // row ids past the end of the table are a plan error: flag once, treat those tokens as padding
-  const int64_t readable = p.kv_entries_len - (int64_t)kv_off;
-  const int id_lim = kv_off < 0 ? 0 : (int)(readable < (int64_t)kv_len ? (readable < 0 ? 0 : readable) : kv_len);
-  if (id_lim < kv_len && tid == 0) flag_error(FT_DEV_BAD_KV_INDEX);
-  const uint32_t row_lim = (uint32_t)(p.kv_rows < 0x7fffffffLL ? p.kv_rows : 0x7fffffffLL);
+  // The kernel may have been scheduled while the preceding kernel of the stream is still running (programmatic
+  // dependent launch).  CTAs of the first wave - the only ones that can be resident that early - do their on-chip
+  // set-up first and wait for the preceding kernel after it, so launch and set-up hide under that kernel's tail;
+  // later CTAs find the wait already satisfied and issue their task's table reads before the set-up instead, which
+  // hides the reads' latency as well.
+  uint32_t num_sms;
+  asm("mov.u32 %0, %%nsmid;" : "=r"(num_sms));
+  const bool first_wave = blockIdx.x < 2u * num_sms;
+  int q_off = 0, q_len = 0, kv_off = 0, kv_len = 0;
+  auto read_task = [&]() {
+    wait_for_prior_grid();
+    q_off = p.q_offs[vn];
+    q_len = p.q_lens[vn];
+    kv_off = p.kv_offs[vn];
+    kv_len = max(p.kv_lens[vn], 0);
+  };
+  if (!first_wave) read_task();
 
   // ---- one-time set-up: barriers, tensor memory
   if (tid == 32 && tp.has_tma) {  // the first TMA copy would otherwise pay for fetching its descriptor
@@ -268,7 +273,17 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  if (first_wave) read_task();
   if (tid == 0) FT_TL_MARK(0);
+  const int G = p.group;
+  const int rows = q_len * G;  // <= 0: nothing to do but to give the tensor memory back
+  const float scale2 = p.sm_scale * 1.4426950408889634f;
+  const int ntiles = (kv_len + C::TILE - 1) / C::TILE;
+  // row ids past the end of the table are a plan error: flag once, treat those tokens as padding
+  const int64_t readable = p.kv_entries_len - (int64_t)kv_off;
+  const int id_lim = kv_off < 0 ? 0 : (int)(readable < (int64_t)kv_len ? (readable < 0 ? 0 : readable) : kv_len);
+  if (rows > 0 && id_lim < kv_len && tid == 0) flag_error(FT_DEV_BAD_KV_INDEX);
+  const uint32_t row_lim = (uint32_t)(p.kv_rows < 0x7fffffffLL ? p.kv_rows : 0x7fffffffLL);
   auto k_buf = [&](int t) { return sm + C::K_OFF + (t & 1) * 16384; };
   auto v_buf = [&](int t) { return sm + C::V_OFF + (t & 1) * 16384; };
 
@@ -317,13 +332,15 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
             break;
           }
           tc_fence_after();
-          if (j == 0 && tid == 0) FT_TL_MARK(2);
-          if (j == 5 && tid == 0) FT_TL_MARK(10);
+          if (j == 0 && tid == 0) FT_TL_COARSE_MARK(2);
+          if (j == FT_TL_TILE && tid == 0) FT_TL_MARK(10);
+          if (j == FT_TL_TILE + 1 && tid == 0) FT_TL_DETAIL_MARK(2);
           float s[64];
           const uint32_t s_col = t_lane + C::S_COL + b * C::TILE;
           tmem_ld32_nowait(s_col, *reinterpret_cast<float(*)[32]>(&s[0]));  // both halves in flight, one wait
           tmem_ld32_nowait(s_col + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
           tmem_wait_ld();
+          if (j == FT_TL_TILE && tid == 0) FT_TL_DETAIL_MARK(5);
           tc_fence_before();
           mbar_arrive(bar(C::S_EMPTY + b));  // the scores are in registers: the buffer may take tile j+2
           // columns outside [lo, hi) are padding (last tile) or tokens this row does not attend to
@@ -342,6 +359,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           }
           float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
           mx *= scale2;  // scale2 > 0
+          if (j == FT_TL_TILE && tid == 0) FT_TL_DETAIL_MARK(6);
           float corr = 1.f;
           bool grow = false;
           if (mx > m_used + 8.f || m_used == -INFINITY) {  // the offset may lag the true maximum by up to 2^8
@@ -374,7 +392,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
             l_run += sum2.x + sum2.y;
           }
           // P.V of the previous tile must be done before P and O are touched
-          if (j == 5 && tid == 0) FT_TL_MARK(11);
+          if (j == FT_TL_TILE && tid == 0) FT_TL_MARK(11);
           if (j > 0) {
             if (!tc_wait(bar(C::PV_DONE), (uint32_t)(g - 1) & 1u, abort_flag)) {
               give_up();
@@ -393,17 +411,18 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
               tmem_wait_st();
             }
           }
-          if (j == 5 && tid == 0) FT_TL_MARK(1);
+          if (j == FT_TL_TILE && tid == 0) FT_TL_MARK(1);
           const uint32_t p_row = p_sm + (tid >> 3) * 1024 + (tid & 7) * 128;
 #pragma unroll
           for (int c8 = 0; c8 < 8; ++c8)
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + ((c8 ^ (tid & 7)) << 4)),
                          "r"(w[4 * c8]), "r"(w[4 * c8 + 1]), "r"(w[4 * c8 + 2]), "r"(w[4 * c8 + 3])
                          : "memory");
+          if (j == FT_TL_TILE && tid == 0) FT_TL_DETAIL_MARK(7);
           proxy_fence();      // P (generic stores) becomes visible to the tensor core
           tc_fence_before();  // orders this thread's tcgen05.ld/st before the hand-off
           mbar_arrive(bar(C::P_FULL));
-          if (j == 5 && tid == 0) FT_TL_MARK(4);
+          if (j == FT_TL_TILE && tid == 0) FT_TL_MARK(4);
         }
         // ---- epilogue: wait for the last P.V, normalise, write this thread's partial row
         if (!dead && ntiles > 0 && !tc_wait(bar(C::PV_DONE), (uint32_t)(g0 + ntiles - 1) & 1u, abort_flag)) give_up();
@@ -654,7 +673,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           const int g = g0 + s, b = g & 1;
           cp_async_wait<1>();  // ids of tile s have landed (this lane's copies)
           __syncwarp();
-          if (s == 0 && lane == 0) FT_TL_MARK(5);
+          if (s == 0 && lane == 0) FT_TL_COARSE_MARK(5);
           // dense tile: 64 valid, consecutive row ids inside the buffer -> TMA
           const int* ids = ring + (s % C::IDX_SLOTS) * C::TILE;
           bool dense = false;
@@ -695,7 +714,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
             return true;
           };
           if (ntiles > 0 && !tc_wait(bar(C::Q_FULL), (uint32_t)pass & 1u, abort_flag)) give_up();
-          FT_TL_MARK(7);
+          FT_TL_COARSE_MARK(7);
           for (int t = 0; t < ntiles && !dead; ++t) {
             const int g = g0 + t, b = g & 1;
             const uint32_t use = (uint32_t)(g >> 1) & 1u;
@@ -704,7 +723,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
               give_up();
               break;
             }
-            if (t == 0) FT_TL_MARK(6);
+            if (t == 0) FT_TL_COARSE_MARK(6);
             proxy_fence();
             tc_fence_after();
             const uint64_t k_desc = tc_desc(k_buf(g), 16, 1024);
@@ -780,6 +799,7 @@ __global__ void __launch_bounds__(TcCfg::THREADS, 2) stage1_fused_kernel(const _
       return;
     }
     reg_grow<TcCfg::REGS_WORKER>();
+    wait_for_prior_grid();  // nothing of the preceding kernel's is read or overwritten before this
     const int w = b - p.lead_wide;
     if (p.workers > 0) {
       stream_worker<T, 128>(tp, smem, wide_tasks, few_tasks, w, p.workers);

@@ -17,6 +17,7 @@ namespace ft {
 // registers for the rows in flight, which is what bounds the warps per SM here.
 template <typename T, int MAXC>
 __global__ void __launch_bounds__(128, MAXC == 1 ? 9 : 6) stage2_merge_kernel(Stage2Params p) {
+  allow_dependent_launch();  // a following stage-1 launch may set itself up under this kernel's tail
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t pair = (int64_t)blockIdx.x * 4 + warp;
   if (pair >= (int64_t)p.batch * p.heads) return;
