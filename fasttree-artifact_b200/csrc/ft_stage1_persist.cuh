@@ -74,14 +74,6 @@ struct PsCfg {
 static_assert(PsCfg::SMEM_BYTES <= 115712, "two CTAs must fit in one SM's shared memory");
 static_assert((PsCfg::BAR_OFF & 7) == 0, "mbarriers are 8-byte aligned");
 
-// O += A . B with A in tensor memory (lane = row, two 16-bit elements per column, K-major) and B in shared memory
-__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
-      : "memory");
-}
 
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;

@@ -12,10 +12,13 @@
 // Roles
 //   warps 0-3  softmax: thread t owns query row t = TMEM lane t.  It reads its
 //              row of S with tcgen05.ld, does the online softmax with no
-//              cross-lane traffic, writes its row of P to shared memory and
-//              rescales its row of O in TMEM only when the running maximum grew
-//              by more than 2^8 (the exponent offset may lag the true maximum;
-//              sum and output use the same offset, so the result is unchanged).
+//              cross-lane traffic, writes its row of P over the first half of
+//              the S buffer it has just read (tcgen05.st; P.V takes its A
+//              operand from tensor memory) and rescales its row of O in TMEM
+//              only when the running maximum grew by more than 2^8 (the
+//              exponent offset may lag the true maximum; sum and output use the
+//              same offset, so the result is unchanged).  Only that rescale
+//              waits for the previous tile's P.V.
 //              At the end it stages its normalised row in shared memory and
 //              each warp writes its 32 rows to the partial buffer with full-row
 //              (512-byte) store instructions.
@@ -45,9 +48,14 @@
 // done), each with exactly one waiting role; every wait is bounded and unwinds
 // the CTA through an abort flag.
 //
-// Q, K, V and P use the canonical 128-byte-swizzled operand layout (64-element
-// blocks, 8-row groups of 1024 bytes).  TMEM: two 64-column S buffers and 128
-// columns of O in a 256-column allocation, so two CTAs share an SM.
+// Q, K and V use the canonical 128-byte-swizzled operand layout (64-element
+// blocks, 8-row groups of 1024 bytes).  TMEM: two 64-column S buffers (P of a
+// tile, 16-bit, takes the first 32 columns of its S buffer) and 128 columns of O
+// in a 256-column allocation, so two CTAs share an SM.
+// S buffer b is written again by S_{t+2} while it may still hold P_t.  Nothing
+// but issue order protects it: every MMA of this kernel has the same shape
+// (M 128, N 64, K 16 - P.V is issued as two 64-column halves of O for that
+// reason), and same-shape MMAs of one CTA execute in the order they were issued.
 //
 // Arithmetic conventions as in the other stage-1 kernels
 // (kernel_bench/fasttree.py:360-413): fp32 scores scaled after the dot product,
@@ -71,13 +79,13 @@ struct TcCfg {
   static constexpr int TILE = 64;     // tokens per tile (UMMA N of S, K of P.V)
   static constexpr int D = 128;
   static constexpr int Q_OFF = 0;                     // 2 blocks x [128 rows][128 B]
-  static constexpr int K_OFF = 32768;                 // 2 buffers x (2 blocks x [64 tok][128 B])
-  static constexpr int V_OFF = K_OFF + 2 * 16384;
-  static constexpr int P_OFF = V_OFF + 2 * 16384;     // [128 rows][128 B]
+  static constexpr int NSK = 3;                       // K ring: one stage more than V, K being needed a softmax earlier
+  static constexpr int K_OFF = 32768;                 // NSK buffers x (2 blocks x [64 tok][128 B])
+  static constexpr int V_OFF = K_OFF + NSK * 16384;   // 2 buffers, same shape
   static constexpr int IDX_SLOTS = 3;
-  static constexpr int IDX_OFF = P_OFF + 16384;       // IDX_SLOTS x 64 row ids
+  static constexpr int IDX_OFF = V_OFF + 2 * 16384;   // IDX_SLOTS x 64 row ids
   static constexpr int BAR_OFF = IDX_OFF + IDX_SLOTS * 64 * 4;
-  static constexpr int NBARS = 15;
+  static constexpr int NBARS = 18;
   static constexpr int ABORT_OFF = BAR_OFF + NBARS * 8;
   static constexpr int TMEM_SLOT_OFF = ABORT_OFF + 4;
   static constexpr int SMEM_BYTES = TMEM_SLOT_OFF + 4;
@@ -85,14 +93,14 @@ struct TcCfg {
   static constexpr int S_COL = 0, O_COL = 128;        // S is double-buffered: columns [0,64) and [64,128)
   static constexpr int WAIT_LIMIT = 1 << 16;          // probes of mbarrier.try_wait before a wait gives up
   // barrier indices
-  static constexpr int K_FULL = 0, K_EMPTY = 2, V_FULL = 4, V_EMPTY = 6, S_FULL = 8, S_EMPTY = 10, P_FULL = 12,
-                       PV_DONE = 13, Q_FULL = 14;
+  static constexpr int K_FULL = 0, K_EMPTY = 3, V_FULL = 6, V_EMPTY = 8, S_FULL = 10, P_FULL = 12, PV_DONE = 14,
+                       Q_FULL = 16;
   static constexpr int OUT_STRIDE = 528;              // bytes between staged output rows (512 + 16: conflict-free 16-byte stores)
   static constexpr int REGS_SOFTMAX = 184, REGS_OTHER = 72;
   static constexpr int REGS_WORKER = 232;             // few-row workers of the fused kernel: four warps, the other four leave
 };
 static_assert(TcCfg::SMEM_BYTES <= 115712, "two CTAs must fit in one SM's shared memory");
-static_assert(128 * TcCfg::OUT_STRIDE <= TcCfg::P_OFF, "the staged output rows reuse the Q, K and V buffers");
+static_assert(128 * TcCfg::OUT_STRIDE <= TcCfg::IDX_OFF, "the staged output rows reuse the Q, K and V buffers");
 static_assert((TcCfg::REGS_SOFTMAX + TcCfg::REGS_OTHER) * 128 <= 2 * 128 * 128, "register trade must balance");
 
 template <int N>
@@ -125,6 +133,14 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// O += A . B with A in tensor memory (lane = row, two 16-bit elements per column, K-major) and B in shared memory
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
       : "memory");
 }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -211,7 +227,8 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
   using C = TcCfg;
   const Stage1Params& p = tp.p;
   const uint32_t sm = smem_u32(smem);
-  const uint32_t q_sm = sm + C::Q_OFF, p_sm = sm + C::P_OFF, idx_sm = sm + C::IDX_OFF, bars = sm + C::BAR_OFF;
+  const uint32_t q_sm = sm + C::Q_OFF, idx_sm = sm + C::IDX_OFF, bars = sm + C::BAR_OFF;
+  const uint32_t req_sm = sm + C::V_OFF;  // request ids of a pass's rows, staged before the pass's first V load
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::ABORT_OFF);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::TMEM_SLOT_OFF);
   auto bar = [&](int i) { return bars + 8u * i; };
@@ -249,16 +266,19 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
     }
   }
   if (tid == 0) {
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < C::NSK; ++b) {
       mbar_init(bar(C::K_FULL + b), 32);   // the loader's lanes
-      mbar_init(bar(C::V_FULL + b), 32);
       mbar_init(bar(C::K_EMPTY + b), 1);   // tcgen05.commit
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar(C::V_FULL + b), 32);
       mbar_init(bar(C::V_EMPTY + b), 1);
       mbar_init(bar(C::S_FULL + b), 1);
-      mbar_init(bar(C::S_EMPTY + b), 128);  // the softmax threads
+      // P of tile g is announced on barrier g & 1: a thread that is a tile ahead of the slowest one arrives on the
+      // other barrier, never twice in one phase
+      mbar_init(bar(C::P_FULL + b), 128);  // the softmax threads
+      mbar_init(bar(C::PV_DONE + b), 1);
     }
-    mbar_init(bar(C::P_FULL), 128);
-    mbar_init(bar(C::PV_DONE), 1);
     mbar_init(bar(C::Q_FULL), 64);  // the Q-gather threads
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -284,11 +304,11 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
   const int id_lim = kv_off < 0 ? 0 : (int)(readable < (int64_t)kv_len ? (readable < 0 ? 0 : readable) : kv_len);
   if (rows > 0 && id_lim < kv_len && tid == 0) flag_error(FT_DEV_BAD_KV_INDEX);
   const uint32_t row_lim = (uint32_t)(p.kv_rows < 0x7fffffffLL ? p.kv_rows : 0x7fffffffLL);
-  auto k_buf = [&](int t) { return sm + C::K_OFF + (t & 1) * 16384; };
+  auto k_buf = [&](int t) { return sm + C::K_OFF + (t % C::NSK) * 16384; };
   auto v_buf = [&](int t) { return sm + C::V_OFF + (t & 1) * 16384; };
 
-  // Tiles are numbered g = 0, 1, 2, ... across passes; tile g uses K/V/S buffer g & 1 for the (g >> 1)-th time,
-  // and is the g-th use of the P buffer, which gives every wait its barrier phase without per-barrier counters.
+  // Tiles are numbered g = 0, 1, 2, ... across passes; tile g uses V / S buffer g & 1 for the (g >> 1)-th time and K
+  // buffer g % NSK for the (g / NSK)-th time, which gives every wait its barrier phase without per-barrier counters.
   int g0 = 0, pass = 0;
   bool dead = false;
   auto give_up = [&]() {
@@ -341,8 +361,6 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           tmem_ld32_nowait(s_col + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
           tmem_wait_ld();
           if (j == FT_TL_TILE && tid == 0) FT_TL_DETAIL_MARK(5);
-          tc_fence_before();
-          mbar_arrive(bar(C::S_EMPTY + b));  // the scores are in registers: the buffer may take tile j+2
           // columns outside [lo, hi) are padding (last tile) or tokens this row does not attend to
           const int lo = r_lo - j * C::TILE, hi = r_hi - j * C::TILE;
           if (lo > 0 || hi < C::TILE) {
@@ -391,41 +409,37 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
             const float2 sum2 = __fadd2_rn(__fadd2_rn(sum4[0], sum4[1]), __fadd2_rn(sum4[2], sum4[3]));
             l_run += sum2.x + sum2.y;
           }
-          // P.V of the previous tile must be done before P and O are touched
+          // Only a rescale of O has to wait for P.V of the previous tile.  (That tile's barrier phase cannot be
+          // confused with an older one: S_g was committed after P.V of tile g-2, so that phase is long complete.)
           if (j == FT_TL_TILE && tid == 0) FT_TL_MARK(11);
-          if (j > 0) {
-            if (!tc_wait(bar(C::PV_DONE), (uint32_t)(g - 1) & 1u, abort_flag)) {
+          if (j > 0 && __any_sync(0xffffffffu, grow)) {
+            if (!tc_wait(bar(C::PV_DONE + ((g - 1) & 1)), (uint32_t)((g - 1) >> 1) & 1u, abort_flag)) {
               give_up();
               break;
             }
             tc_fence_after();
-            if (__any_sync(0xffffffffu, grow)) {  // rescale this warp's rows of O in tensor memory
 #pragma unroll
-              for (int cb = 0; cb < 4; ++cb) {
-                float o[32];
-                tmem_ld32(t_lane + C::O_COL + cb * 32, o);
+            for (int cb = 0; cb < 4; ++cb) {  // this warp's rows of O in tensor memory
+              float o[32];
+              tmem_ld32(t_lane + C::O_COL + cb * 32, o);
 #pragma unroll
-                for (int c = 0; c < 32; ++c) o[c] *= corr;
-                tmem_st32(t_lane + C::O_COL + cb * 32, o);
-              }
-              tmem_wait_st();
+              for (int c = 0; c < 32; ++c) o[c] *= corr;
+              tmem_st32(t_lane + C::O_COL + cb * 32, o);
             }
           }
           if (j == FT_TL_TILE && tid == 0) FT_TL_MARK(1);
-          const uint32_t p_row = p_sm + (tid >> 3) * 1024 + (tid & 7) * 128;
-#pragma unroll
-          for (int c8 = 0; c8 < 8; ++c8)
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + ((c8 ^ (tid & 7)) << 4)),
-                         "r"(w[4 * c8]), "r"(w[4 * c8 + 1]), "r"(w[4 * c8 + 2]), "r"(w[4 * c8 + 3])
-                         : "memory");
+          // P_g takes the place of the scores just read: 64 16-bit values = the first 32 columns of S buffer b
+          tmem_st32(s_col, *reinterpret_cast<float(*)[32]>(&w[0]));
+          tmem_wait_st();
           if (j == FT_TL_TILE && tid == 0) FT_TL_DETAIL_MARK(7);
-          proxy_fence();      // P (generic stores) becomes visible to the tensor core
           tc_fence_before();  // orders this thread's tcgen05.ld/st before the hand-off
-          mbar_arrive(bar(C::P_FULL));
+          mbar_arrive(bar(C::P_FULL + b));
           if (j == FT_TL_TILE && tid == 0) FT_TL_MARK(4);
         }
         // ---- epilogue: wait for the last P.V, normalise, write this thread's partial row
-        if (!dead && ntiles > 0 && !tc_wait(bar(C::PV_DONE), (uint32_t)(g0 + ntiles - 1) & 1u, abort_flag)) give_up();
+        if (!dead && ntiles > 0 &&
+            !tc_wait(bar(C::PV_DONE + ((g0 + ntiles - 1) & 1)), (uint32_t)((g0 + ntiles - 1) >> 1) & 1u, abort_flag))
+          give_up();
         if (!dead) {
           tc_fence_after();
           if (tid == 0) FT_TL_MARK(3);
@@ -483,23 +497,23 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
     for (int row0 = 0; row0 < rows; row0 += C::ROWS) {
       if (warp >= 6) {
         // ================================================================ Q gather (64 threads)
-        // request ids of this pass's slots -> the (still unused) P buffer, then the rows themselves
+        // request ids of this pass's slots -> the (still unused) V buffers, then the rows themselves
         const int qt = tid - 192, ld_c = qt & 15, ld_r = qt >> 4;
         const int row_end = min(rows, row0 + C::ROWS);
         const int first_slot = row0 / G, nslots = (row_end - 1) / G - first_slot + 1;  // <= 128
         for (int i = qt; i < nslots; i += 64) {
           const int64_t part = (int64_t)q_off + first_slot + i;
           if (part >= 0 && part < p.num_partial_rows) {
-            cp_async4(p_sm + i * 4, p.q_entries + part);
+            cp_async4(req_sm + i * 4, p.q_entries + part);
           } else {
             flag_error(FT_DEV_BAD_ROW_INDEX);
-            asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(p_sm + i * 4), "r"(-1) : "memory");
+            asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(req_sm + i * 4), "r"(-1) : "memory");
           }
         }
         cp_async_commit();
         cp_async_wait<0>();
         asm volatile("bar.sync 1, 64;\n" ::: "memory");
-        const int* req_of = reinterpret_cast<const int*>(smem + C::P_OFF);
+        const int* req_of = reinterpret_cast<const int*>(smem + C::V_OFF);
         // Requests with consecutive ids (the usual case: the leaves under a node are numbered in tree order) make
         // the whole Q tile one strided block of the Q tensor: two boxes of [128 / G requests][G heads][64].
         bool in_order = false;
@@ -561,6 +575,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           mbar_arrive_on_cp_async(bar(C::Q_FULL));  // one arrival per thread once its copies have landed
           cp_async_wait<0>();
         }
+        asm volatile("bar.sync 1, 64;\n" ::: "memory");  // both warps are done with the staged request ids: V may land there
         if (warp == 6) {
           // ============================================================== V loader (this warp, once Q is on its way)
           // Row ids live in registers, two per lane and one tile ahead, so this role shares nothing with the K
@@ -670,7 +685,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
         // K only: the V tiles have a loader warp of their own (below), so a tile whose rows must be gathered one
         // by one costs each of the two warps half of the copies, and K never waits behind a V buffer.
         for (int s = 0; s < ntiles && !dead; ++s) {
-          const int g = g0 + s, b = g & 1;
+          const int g = g0 + s, b = g % C::NSK;
           cp_async_wait<1>();  // ids of tile s have landed (this lane's copies)
           __syncwarp();
           if (s == 0 && lane == 0) FT_TL_COARSE_MARK(5);
@@ -683,7 +698,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
             const bool mine = ids[lane] == first_row + lane && ids[lane + 32] == first_row + lane + 32;
             dense = __all_sync(0xffffffffu, mine) && first_row >= 0 && (uint32_t)(first_row + C::TILE) <= row_lim;
           }
-          if (!tc_wait(bar(C::K_EMPTY + b), ((uint32_t)(g >> 1) & 1u) ^ 1u, abort_flag)) {
+          if (!tc_wait(bar(C::K_EMPTY + b), ((uint32_t)(g / C::NSK) & 1u) ^ 1u, abort_flag)) {
             give_up();
             break;
           }
@@ -696,30 +711,35 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
         // ================================================================ MMA issue
         if (lane == 0) {
           const uint32_t idesc_s = tc_idesc<T>(128, C::TILE, false);
-          const uint32_t idesc_o = tc_idesc<T>(128, C::D, true);
-          const uint64_t q_desc = tc_desc(q_sm, 16, 1024), p_desc = tc_desc(p_sm, 16, 1024);
-          auto issue_pv = [&](int t) {  // O += P_t V_t : 4 k-steps of 16 tokens
+          const uint32_t idesc_o = tc_idesc<T>(128, 64, true);  // P.V in two 64-column halves: the shape of S
+          const uint64_t q_desc = tc_desc(q_sm, 16, 1024);
+          auto issue_pv = [&](int t) {  // O += P_t V_t : per half of O, 4 k-steps of 16 tokens, A = P_t in tensor memory
             const int g = g0 + t, b = g & 1;
-            if (!tc_wait(bar(C::P_FULL), (uint32_t)g & 1u, abort_flag)) return false;
-            if (!tc_wait(bar(C::V_FULL + b), (uint32_t)(g >> 1) & 1u, abort_flag)) return false;
+            const uint32_t use = (uint32_t)(g >> 1) & 1u;
+            if (!tc_wait(bar(C::P_FULL + b), use, abort_flag)) return false;
+            if (!tc_wait(bar(C::V_FULL + b), use, abort_flag)) return false;
             proxy_fence();
             tc_fence_after();
-            const uint64_t v_desc = tc_desc(v_buf(g), 8192, 1024);
+            const uint32_t p_tmem = tmem + C::S_COL + b * C::TILE;
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              tc_mma(tmem + C::O_COL, p_desc + (uint64_t)(ks * 2), v_desc + (uint64_t)(ks * 128), idesc_o,
-                     (t > 0 || ks > 0) ? 1u : 0u);
+            for (int h = 0; h < 2; ++h) {
+              const uint64_t v_desc = tc_desc(v_buf(g) + h * 8192, 8192, 1024);
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks)
+                tc_mma_ts(tmem + C::O_COL + h * 64, p_tmem + (uint32_t)(ks * 8), v_desc + (uint64_t)(ks * 128), idesc_o,
+                          (t > 0 || ks > 0) ? 1u : 0u);
+            }
             tc_commit(bar(C::V_EMPTY + b));
-            tc_commit(bar(C::PV_DONE));
+            tc_commit(bar(C::PV_DONE + b));
             return true;
           };
           if (ntiles > 0 && !tc_wait(bar(C::Q_FULL), (uint32_t)pass & 1u, abort_flag)) give_up();
           FT_TL_COARSE_MARK(7);
           for (int t = 0; t < ntiles && !dead; ++t) {
-            const int g = g0 + t, b = g & 1;
-            const uint32_t use = (uint32_t)(g >> 1) & 1u;
-            // S_t = Q K_t^T into S buffer b (free once the softmax of the tile two before has read it)
-            if (!tc_wait(bar(C::K_FULL + b), use, abort_flag) || !tc_wait(bar(C::S_EMPTY + b), use ^ 1u, abort_flag)) {
+            const int g = g0 + t, b = g & 1, kb = g % C::NSK;
+            // S_t = Q K_t^T into S buffer b.  The buffer's previous tenant, P of tile t-2, was consumed by a P.V issued
+            // before this point, and same-shape MMAs execute in issue order.
+            if (!tc_wait(bar(C::K_FULL + kb), (uint32_t)(g / C::NSK) & 1u, abort_flag)) {
               give_up();
               break;
             }
@@ -733,7 +753,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
               const uint64_t bb = k_desc + (uint64_t)((ks >> 2) * (8192 >> 4) + (ks & 3) * 2);
               tc_mma(tmem + C::S_COL + b * C::TILE, a, bb, idesc_s, ks > 0);
             }
-            tc_commit(bar(C::K_EMPTY + b));
+            tc_commit(bar(C::K_EMPTY + kb));
             tc_commit(bar(C::S_FULL + b));
             if (t > 0 && !issue_pv(t - 1)) {
               give_up();
