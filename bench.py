@@ -392,6 +392,7 @@ class Problem:
         params.set_kv_group_num(self.hq_l // self.hkv_l)
         params.set_q_tile_sizes([max(1, 64 // (hq // hkv)), max(1, 16 // (hq // hkv))])
         params.set_kv_tile_sizes([32, 32])
+        params.set_kv_dtype(self.dtype)
         params.set_planner(args.planner)
         if args.planner_opt:
             from dataclasses import replace

@@ -190,11 +190,22 @@ def _plan_b200(batch, md, node_to_reqs, covered, order, offsets, parents, req_id
         base = stride * int(req_idx[first])
         return [(base + start, base + offsets[i] + tree[i].seqlen)]
 
+    # Radix nodes that only one request passes through (the unique end of its prompt) are contiguous with that
+    # request's tail in its row of req_to_token: they leave the tree and the tail starts where they began, which
+    # makes one few-row task per request out of two or more.
+    tail_start = list(covered)
+    if getattr(md, "merge_private_nodes", True):
+        for i in range(len(tree) - 1, 0, -1):      # children come after their parents in breadth-first order
+            if len(tree[i].requests) == 1 and tree[i].num_children <= 1:
+                rid = tree[i].requests[0]
+                tail_start[rid] = min(tail_start[rid], offsets[i])
+                tree[i].requests = []
+                tree[tree[i].parent].num_children -= 1
     extra = []
     for rid, req in enumerate(batch.reqs):
         end = len(req.origin_input_ids) + len(req.output_ids) + 1
         base = stride * int(req_idx[rid])
-        extra.append(([(base + covered[rid], base + end)], [rid]))
+        extra.append(([(base + tail_start[rid], base + end)], [rid]))
     if getattr(md, "native_planner", True):
         # the native splitter of the shared library; the Python branch below is its specification
         node_base = [stride * int(req_idx[nd.requests[0]]) if nd.requests else 0 for nd in tree]

@@ -578,6 +578,10 @@ def b200_model_for(params, head_dim, model=None):
     if explicit is None and head_dim == 128:
         # the tcgen05 stage-1 kernel holds 128 query rows per CTA (head_dim 128 only)
         m = replace(m, rows_per_cta=128, ridge_flop_per_byte=4 * m.ridge_flop_per_byte)
+    if explicit is None and getattr(params, "kv_elem_bytes", 2) == 4:
+        # fp32 storage runs on the CUDA-core kernel: 32-token tiles, one warp per scheduler, so a chunk costs
+        # several microseconds per tile and a small problem is better cut down to single tiles
+        m = replace(m, elem_bytes=4, tile_tokens=32, min_chunk=32)
     return m
 
 

@@ -30,7 +30,10 @@ class FastTreeParams:
     and KV tile sizes; ``kv_group_num`` is query heads per KV head.  ``planner``
     selects the splitter: ``"b200"`` (default) or ``"reference"`` (bit-identical
     tables to the reference planner).  As in the reference, the planner may
-    overwrite ``TSQs``/``TSKs`` with the tile sizes it settled on."""
+    overwrite ``TSQs``/``TSKs`` with the tile sizes it settled on.
+    ``kv_elem_bytes`` (B200 splitter only, no counterpart in the reference, whose
+    preparation never sees the dtype): 4 tells the splitter that K/V are fp32, which
+    run on the 32-token CUDA-core kernel and are cut as fine as 32 tokens."""
     alpha = 0.66
     beta = 0.33
     gamma = 0.1
@@ -40,6 +43,7 @@ class FastTreeParams:
     planner = "b200"
     native_planner = True
     verbose = False
+    kv_elem_bytes = 2
 
     def set_values(self, alpha, beta, gamma):
         self.alpha = alpha
@@ -54,6 +58,13 @@ class FastTreeParams:
 
     def set_kv_tile_sizes(self, TSKs):
         self.TSKs = TSKs
+
+    def set_kv_dtype(self, dtype):
+        """``dtype``: a torch dtype or an element size in bytes."""
+        size = int(dtype) if isinstance(dtype, int) else int(torch.empty((), dtype=dtype).element_size())
+        if size not in (2, 4):
+            raise ValueError("K/V are 16-bit or fp32")
+        self.kv_elem_bytes = size
 
     def set_planner(self, name):
         if name not in ("b200", "reference"):

@@ -28,9 +28,11 @@ def make_params(hq, hkv, tsq, planner):
 class EngineRun:
     """One planned decode problem resident on the GPU."""
 
-    def __init__(self, nodes, ptrs, batch, q, k, v, hq, hkv, d, tsq, planner="b200", device="cuda"):
+    def __init__(self, nodes, ptrs, batch, q, k, v, hq, hkv, d, tsq, planner="b200", device="cuda", tell_dtype=False):
         self.tree = product_tree(nodes)
         self.params = make_params(hq, hkv, tsq, planner)
+        if tell_dtype:      # the splitter then cuts fp32 problems for the 32-token CUDA-core kernel
+            self.params.set_kv_dtype(k.dtype)
         self.aux, self.assign = fasttree.fasttree_preparation(
             self.tree, ptrs, batch, hq, hkv, d, [1024, 128], [132, 528], [132, 132], self.params, device=device)
         self.q, self.k, self.v = q.to(device), k.to(device), v.to(device)
@@ -65,8 +67,8 @@ class EngineRun:
         return self.o.float().cpu()
 
 
-def run_case(c, planner="b200", path="auto"):
+def run_case(c, planner="b200", path="auto", tell_dtype=False):
     run = EngineRun(c["nodes"], c["ptrs"], c["batch"], c["q"], c["k"], c["v"], c["hq"], c["hkv"], c["d"],
-                    c["tsq"], planner=planner)
+                    c["tsq"], planner=planner, tell_dtype=tell_dtype)
     out = run.decode(path=path)
     return run, out

@@ -131,9 +131,10 @@ def test_edge_shapes_against_oracle(spec, dtype):
     tol = atol_for(dtype)
     if dtype == torch.bfloat16:
         tol += float(truth.abs().max()) * 2 ** -8     # output rounding to bf16
-    for planner in ("reference", "b200"):
+    # fp32 storage additionally with the splitter told so (32-token cuts for the CUDA-core kernel)
+    for planner, told in [("reference", False), ("b200", False)] + ([("b200", True)] if dtype == torch.float32 else []):
         for path in paths_for(c):
-            run, out = gpu_utils.run_case(c, planner=planner, path=path)
+            run, out = gpu_utils.run_case(c, planner=planner, path=path, tell_dtype=told)
             assert lib.read_device_status() == 0
             assert (out - truth).abs().max().item() <= tol, (planner, path)
             np.testing.assert_allclose(run.o_lse.cpu().numpy(), truth_lse.numpy(), rtol=1e-4, atol=2e-5)

@@ -232,6 +232,26 @@ def test_b200_plan_splits_long_prefix_and_keeps_leaves_whole():
     assert plan.num_partial_rows < 1000
 
 
+@pytest.mark.parametrize("native", [True, False], ids=["native", "spec"])
+def test_fp32_hint_cuts_a_small_problem_into_single_tiles(native):
+    """With the splitter told that K/V are fp32 (FastTreeParams.set_kv_dtype), a problem too small to fill the
+    machine is cut into 32-token chunks (one tile of the CUDA-core kernel each) instead of 128-token ones."""
+    import torch
+    tree, batch, ptrs = product_tree(ref_inputs.layered_tree([1, 4], [512, 64]))
+    plans = []
+    for told in (False, True):
+        p = make_params(8, 2, [16, 4], planner_name="b200")
+        p.native_planner = native
+        if told:
+            p.set_kv_dtype(torch.float32)
+        plans.append(fasttree.build_plan(tree, ptrs, batch, 8, 2, 128, [1024, 128], [132, 528], [132, 132], p))
+        check_plan_covers_every_path_once(tree, ptrs, batch, plans[-1])
+    assert sorted(set(plans[0].vnode_to_kv_lens.tolist())) == [64, 128]
+    assert set(plans[1].vnode_to_kv_lens.tolist()) == {32}
+    with pytest.raises(ValueError):
+        make_params(8, 2, [16, 4], planner_name="b200").set_kv_dtype(torch.float64)
+
+
 def test_reference_mode_covers_every_path_once():
     tree, batch, ptrs = product_tree(ref_inputs.layered_tree([1, 2, 16], [8, 40, 19]))
     p = make_params(8, 2, [16, 4])
