@@ -171,6 +171,8 @@ ft::Stage1Params stage1_params(const ft_decode_args* a) {
   p.q_lens = a->vnode_to_q_lens;
   p.q_ranges = a->vnode_q_kv_ranges;
   p.dev_phase = a->device_phase_info;
+  p.kv_entries_aux = a->vnode_to_kv_entries_aux;
+  p.kv_entries_aux_len = a->vnode_to_kv_entries_aux != nullptr ? a->kv_entries_aux_len : 0;
   p.mid_o = a->mid_o;
   p.mid_lse = a->mid_lse;
   p.q_s0 = a->q_stride0;
@@ -789,6 +791,100 @@ int ft_bump_kv_lens(int32_t* vnode_to_kv_lens, const int32_t* last_vnodes, int32
   if (vnode_to_kv_lens == nullptr || last_vnodes == nullptr)
     return fail(FT_ERR_INVALID_ARGUMENT, "vnode_to_kv_lens / last_vnodes is NULL");
   bump_kv_lens_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(vnode_to_kv_lens, last_vnodes, n);
+  FT_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return FT_OK;
+}
+
+namespace {
+// one warp per segment of the auxiliary row-id table
+__global__ void gather_kv_entries_kernel(const int32_t* __restrict__ src, int64_t src_len, const int32_t* __restrict__ seg_src,
+                                         const int32_t* __restrict__ seg_len, const int32_t* __restrict__ seg_dst,
+                                         const int32_t* __restrict__ seg_room, int n, int32_t* __restrict__ aux, int64_t aux_len) {
+  const int seg = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (seg >= n) return;
+  const int64_t from = seg_src[seg], len = seg_len[seg], to = seg_dst[seg], room = seg_room[seg];
+  if (len <= 0 || room < 0 || from < 0 || from + len > src_len || to < 0 || to + len + room > aux_len) {
+    if (lane == 0 && (len != 0 || room != 0)) ft::flag_error(FT_DEV_BAD_KV_INDEX);
+    return;
+  }
+  for (int64_t i = lane; i < len; i += 32) aux[to + i] = src[from + i];
+  const int32_t filler = src[from];
+  for (int64_t i = lane; i < room; i += 32) aux[to + len + i] = filler;
+}
+
+__global__ void bump_tails_kernel(int32_t* __restrict__ state, int n, int32_t* __restrict__ ranges, int64_t rows,
+                                  int32_t* __restrict__ kv_lens, int n_vnodes) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int32_t* st = state + 4 * (int64_t)i;
+  const int aux_pos = st[0], index = st[2], room = st[3];
+  if (aux_pos < 0) {
+    if (index >= 0 && index < n_vnodes) kv_lens[index] += 1;
+    else if (index != -1) ft::flag_error(FT_DEV_BAD_ROW_INDEX);  // {-1, x, -1, x}: an unused entry
+    return;
+  }
+  if (room <= 0 || ranges == nullptr || index < 0 || index >= rows) {
+    ft::flag_error(FT_DEV_BAD_KV_INDEX);
+    return;
+  }
+  ranges[2 * (int64_t)index + 1] += 1;
+  st[0] = aux_pos + 1;
+  st[1] += 1;
+  st[3] = room - 1;
+}
+
+__global__ void refresh_tails_kernel(const int32_t* __restrict__ state, int n, const int32_t* __restrict__ src, int64_t src_len,
+                                     int32_t* __restrict__ aux, int64_t aux_len) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int32_t* st = state + 4 * (int64_t)i;
+  const int64_t aux_pos = st[0], src_pos = st[1];
+  if (aux_pos < 0) return;
+  if (aux_pos < 1 || aux_pos > aux_len || src_pos < 1 || src_pos > src_len) {
+    ft::flag_error(FT_DEV_BAD_KV_INDEX);
+    return;
+  }
+  aux[aux_pos - 1] = src[src_pos - 1];
+}
+}  // namespace
+
+int ft_gather_kv_entries(const int32_t* src_table, int64_t src_len, const int32_t* seg_src, const int32_t* seg_len,
+                         const int32_t* seg_dst, const int32_t* seg_room, int32_t n_segments, int32_t* aux_table,
+                         int64_t aux_len, void* stream) {
+  if (n_segments < 0 || src_len < 0 || aux_len < 0) return fail(FT_ERR_INVALID_ARGUMENT, "negative size");
+  if (n_segments == 0) return FT_OK;
+  if (src_table == nullptr || seg_src == nullptr || seg_len == nullptr || seg_dst == nullptr || seg_room == nullptr ||
+      aux_table == nullptr)
+    return fail(FT_ERR_INVALID_ARGUMENT, "a table of ft_gather_kv_entries is NULL");
+  gather_kv_entries_kernel<<<(n_segments + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      src_table, src_len, seg_src, seg_len, seg_dst, seg_room, n_segments, aux_table, aux_len);
+  FT_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return FT_OK;
+}
+
+int ft_bump_tails(int32_t* tail_state, int32_t n, int32_t* vnode_q_kv_ranges, int64_t num_partial_rows,
+                  int32_t* vnode_to_kv_lens, int32_t num_vnodes, void* stream) {
+  if (n < 0 || num_partial_rows < 0 || num_vnodes < 0) return fail(FT_ERR_INVALID_ARGUMENT, "negative size");
+  if (n == 0) return FT_OK;
+  if (tail_state == nullptr || vnode_to_kv_lens == nullptr)
+    return fail(FT_ERR_INVALID_ARGUMENT, "tail_state / vnode_to_kv_lens is NULL");
+  bump_tails_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      tail_state, n, vnode_q_kv_ranges, num_partial_rows, vnode_to_kv_lens, num_vnodes);
+  FT_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return FT_OK;
+}
+
+int ft_refresh_tails(const int32_t* tail_state, int32_t n, const int32_t* src_table, int64_t src_len, int32_t* aux_table,
+                     int64_t aux_len, void* stream) {
+  if (n < 0 || src_len < 0 || aux_len < 0) return fail(FT_ERR_INVALID_ARGUMENT, "negative size");
+  if (n == 0) return FT_OK;
+  if (tail_state == nullptr || src_table == nullptr || aux_table == nullptr)
+    return fail(FT_ERR_INVALID_ARGUMENT, "tail_state / src_table / aux_table is NULL");
+  refresh_tails_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(tail_state, n, src_table, src_len,
+                                                                                        aux_table, aux_len);
   FT_CUDA_OK(cudaGetLastError());
   count_launch();
   return FT_OK;

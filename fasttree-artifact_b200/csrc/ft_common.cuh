@@ -73,6 +73,8 @@ struct Stage1Params {
   const int32_t* q_lens;
   const int32_t* q_ranges;  // optional [num_partial_rows][2]: the chunk tokens [begin, end) a partial row attends to
   const int32_t* dev_phase; // optional device array {n0, n1, o0, o1}: the persistent kernel reads its vnode range here
+  const int32_t* kv_entries_aux;  // optional second row-id table: vnodes whose kv_offs value has bit 30 set index it
+  int64_t kv_entries_aux_len;
   float* mid_o;
   float* mid_lse;
   int64_t q_s0, q_s1, k_s0, k_s1, v_s0, v_s1, mo_s0, mo_s1, ml_s0;
@@ -90,6 +92,22 @@ struct Stage1Params {
   int32_t workers;      // fused launch: persistent few-row workers (0: one CTA per few-row task)
   float sm_scale;
 };
+
+// Row ids of a vnode's KV chunk.  vnode_to_kv_offs normally indexes vnode_to_kv_entries; with bit 30 set (and an
+// auxiliary table given) the low 30 bits index vnode_to_kv_entries_aux instead: the serving path addresses tree
+// nodes straight through req_to_token and keeps the concatenated row ids of grouped private tails in a table of its own.
+constexpr int FT_AUX_BIT = 1 << 30;
+__device__ __forceinline__ const int32_t* kv_ids_base(const Stage1Params& p, int kv_off) {
+  return (kv_off & FT_AUX_BIT) != 0 && p.kv_entries_aux != nullptr ? p.kv_entries_aux + (kv_off & (FT_AUX_BIT - 1))
+                                                                   : p.kv_entries + kv_off;
+}
+// readable row ids of the chunk (a table that ends early is a plan error: the caller flags it, those tokens become padding)
+__device__ __forceinline__ int kv_ids_limit(const Stage1Params& p, int kv_off, int kv_len) {
+  if (kv_off < 0) return 0;
+  const bool aux = (kv_off & FT_AUX_BIT) != 0 && p.kv_entries_aux != nullptr;
+  const int64_t readable = aux ? p.kv_entries_aux_len - (int64_t)(kv_off & (FT_AUX_BIT - 1)) : p.kv_entries_len - (int64_t)kv_off;
+  return (int)(readable < (int64_t)kv_len ? (readable < 0 ? 0 : readable) : kv_len);
+}
 
 struct Stage2Params {
   const int32_t* r2v_entries;

@@ -11,6 +11,7 @@
 // 0), longest first inside each phase (stable).  All cost arithmetic is IEEE double in the same order as the
 // Python code, so the decisions agree bit for bit.
 #include <algorithm>
+#include <climits>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -51,6 +52,7 @@ struct ft_plan {
   std::vector<int32_t> kv_entries, kv_offs, kv_lens, q_entries, q_offs, q_lens, r2v_entries, r2v_offs, r2v_lens;
   std::vector<int32_t> assignments;
   std::vector<int32_t> q_ranges;  // [partial rows][2] when the plan holds groups of short nodes, else empty
+  std::vector<int32_t> aux_segments;  // serving plans with groups: per member {source position, length, position in the auxiliary table, room}
   ft_plan_info info;
 };
 
@@ -60,7 +62,13 @@ namespace {
 // an existing row-id table (SGLang's flattened req_to_token): [base[i] + offset[top carried ancestor],
 // base[i] + offset[i] + seqlen[i]).  No row-id table is emitted; vnode_to_kv_offs are positions in that table.
 // `extra` pairings (one request each: its private tail) join the byte budget and come last in emission order.
+// tail_room >= 0 lets short nodes and tails run as groups (one many-row vnode, per-row token ranges): a group's row
+// ids cannot be one run of the table, so they go to an auxiliary table that the caller fills on the device from the
+// segment list this plan reports; the vnode's offset carries FT_KV_OFFSET_AUX.  A tail grows by one token per step
+// of the burst: inside a group it is followed by tail_room spare entries, which no row attends to until the
+// caller moves the row's range end.
 struct Direct {
+  int32_t tail_room = -1;
   const int64_t* node_base = nullptr;
   const int64_t* node_offset = nullptr;
   int64_t n_extra = 0;
@@ -175,6 +183,8 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
       int64_t length;
       int64_t chunk;
       std::vector<std::pair<int32_t, int32_t>> row_ranges;  // group of short nodes: per request, its tokens of the chunk
+      int64_t room = 0;                 // spare row ids kept behind this pairing when it becomes a member of a group
+      std::vector<int64_t> member_room;  // group in the serving path: room behind each of its ranges
     };
     std::vector<Spec> specs;
     const int64_t row_bytes = 2LL * head_dim * m.elem_bytes;
@@ -241,6 +251,7 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
         s.ranges.emplace_back(direct->extra_begin[e], direct->extra_end[e]);
         s.reqs.push_back(r);
         s.length = length;
+        s.room = std::max(direct->tail_room, 0);
         total_stream += ceil_div(1, q_tile) * length * row_bytes;
         specs.push_back(std::move(s));
       }
@@ -261,11 +272,27 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
     // group_min_members members, or not more requests than small_tile, are dissolved.  Result: the other virtual
     // nodes in their order, then groups and dissolved candidates in the order they were closed.
     bool any_groups = false;
-    if (direct == nullptr && head_dim == 128 && m.elem_bytes == 2 && m.group_member_tokens > 0) {
+    if ((direct == nullptr || direct->tail_room >= 0) && head_dim == 128 && m.elem_bytes == 2 && m.group_member_tokens > 0) {
       const int64_t tile = m.tile_tokens;
       const int64_t target_tokens = (int64_t)std::floor(target / (double)row_bytes);
-      const int64_t hard_cap = 16 * tile;
-      const int64_t cap = std::min(std::max(target_tokens / tile * tile, 4 * tile), hard_cap);
+      int64_t hard_cap = 16 * tile;
+      int64_t cap = std::min(std::max(target_tokens / tile * tile, 4 * tile), hard_cap);
+      if (direct != nullptr) {
+        // Serving path: the groups are sized to fill twice what the other tasks leave of one round of resident CTAs
+        // (measured: their tiles are gathered row by row, and two shorter groups per slot hide that latency better
+        // than one long one; the average-based target above overshoots when the shared nodes' tasks are short), up
+        // to 24 tiles.
+        int64_t cand_tokens = 0, other = 0;
+        for (const Spec& s : specs) {
+          const int64_t nreq = (int64_t)s.reqs.size();
+          if (nreq <= small_tile && s.length + s.room <= m.group_member_tokens) cand_tokens += s.length + s.room;
+          else other += ceil_div(s.length, s.chunk) * ceil_div(nreq, q_tile);
+        }
+        const int64_t round = std::max<int64_t>((int64_t)slots / std::max(num_kv_heads, 1), 1);
+        const int64_t free_tasks = 2 * std::max<int64_t>(std::max(round - other, round / 4), 1);
+        hard_cap = 24 * tile;
+        cap = std::min(std::max(ceil_div(ceil_div(cand_tokens, free_tasks), tile) * tile, 4 * tile), hard_cap);
+      }
       std::vector<Spec> kept, tail;
       std::vector<Spec> cur;
       std::vector<uint8_t> in_group((size_t)std::max(batch, 1), 0);
@@ -280,7 +307,8 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
             g.ranges.insert(g.ranges.end(), c.ranges.begin(), c.ranges.end());
             g.reqs.insert(g.reqs.end(), c.reqs.begin(), c.reqs.end());
             g.row_ranges.insert(g.row_ranges.end(), c.reqs.size(), std::make_pair((int32_t)start, (int32_t)(start + c.length)));
-            start += c.length;
+            if (direct != nullptr) g.member_room.push_back(c.room);  // one range per member in the serving path
+            start += c.length + c.room;
           }
           g.length = start;
           g.chunk = ceil_div(start, tile) * tile;
@@ -294,14 +322,17 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
       };
       for (Spec& s : specs) {
         const int64_t nreq = (int64_t)s.reqs.size();
-        if (nreq <= small_tile && s.length <= m.group_member_tokens) {
+        const int64_t span = s.length + s.room;
+        if (nreq <= small_tile && span <= m.group_member_tokens) {
           bool shared = false;
           for (int32_t r : s.reqs) shared = shared || in_group[r] != 0;
-          if (!cur.empty() && (cur_n + nreq > q_tile || cur_tokens + s.length > hard_cap ||
-                               (cur_tokens + s.length > cap && cur_n > small_tile) || shared))
+          // (serving path: a group is closed once it has reached the cap, not before it would pass it, so that
+          // the groups number no more than the tasks they were sized for)
+          const bool full = direct != nullptr ? cur_tokens >= cap : cur_tokens + span > cap;
+          if (!cur.empty() && (cur_n + nreq > q_tile || cur_tokens + span > hard_cap || (full && cur_n > small_tile) || shared))
             close();
           for (int32_t r : s.reqs) in_group[r] = 1;
-          cur_tokens += s.length;
+          cur_tokens += span;
           cur_n += nreq;
           cur.push_back(std::move(s));
         } else {
@@ -315,10 +346,27 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
 
     // ---- emission: chunk-major, request-tile-minor; every chunk repeats the node's request list
     std::vector<int64_t> kv_offs, kv_lens, q_offs, q_lens;
-    int64_t kv_total = 0, q_total = 0;
+    int64_t kv_total = 0, q_total = 0, aux_total = 0;
     for (const Spec& s : specs) {
       const int64_t nreq = (int64_t)s.reqs.size();
-      const int64_t kv_base = direct != nullptr ? s.ranges[0].first : kv_total;
+      int64_t kv_base = direct != nullptr ? s.ranges[0].first : kv_total;
+      if (direct != nullptr && !s.member_room.empty()) {  // a group of the serving path: its row ids live in the auxiliary table
+        kv_base = (int64_t)FT_KV_OFFSET_AUX + aux_total;
+        int64_t at = aux_total;
+        for (size_t k = 0; k < s.ranges.size(); ++k) {
+          const int64_t len = s.ranges[k].second - s.ranges[k].first;
+          if (s.ranges[k].first >= (int64_t)FT_KV_OFFSET_AUX || at + len + s.member_room[k] >= (int64_t)FT_KV_OFFSET_AUX) {
+            delete plan;
+            return FT_ERR_TOO_LARGE;
+          }
+          plan->aux_segments.push_back((int32_t)s.ranges[k].first);
+          plan->aux_segments.push_back((int32_t)len);
+          plan->aux_segments.push_back((int32_t)at);
+          plan->aux_segments.push_back((int32_t)s.member_room[k]);
+          at += len + s.member_room[k];
+        }
+        aux_total = at;
+      }
       if (direct == nullptr)
         for (auto& r : s.ranges)
           for (int64_t row = r.first; row < r.second; ++row) plan->kv_entries.push_back((int32_t)row);
@@ -336,7 +384,10 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
         if (any_groups) {
           for (int64_t r = 0; r < nreq; ++r) {
             plan->q_ranges.push_back(s.row_ranges.empty() ? 0 : s.row_ranges[(size_t)r].first);
-            plan->q_ranges.push_back(s.row_ranges.empty() ? (int32_t)c_len : s.row_ranges[(size_t)r].second);
+            // a row of a plain vnode sees its whole chunk; in the serving path that chunk may grow during the burst
+            // (vnode_to_kv_lens is bumped), so the end is left open there - the kernels clip it to the chunk
+            plan->q_ranges.push_back(s.row_ranges.empty() ? (direct != nullptr ? INT32_MAX : (int32_t)c_len)
+                                                          : s.row_ranges[(size_t)r].second);
           }
         }
       }
@@ -405,6 +456,8 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
     info.small_tile = small_tile;
     info.tile_tokens = m.tile_tokens;
     info.has_row_ranges = any_groups ? 1 : 0;
+    info.aux_entries = aux_total;
+    info.aux_segments = (int64_t)(plan->aux_segments.size() / 4);
     info.target_bytes = target;
     info.virtual_nodes = (int64_t)specs.size();
   } catch (const std::bad_alloc&) {
@@ -429,9 +482,10 @@ int ft_plan_b200_build(const int32_t* parent, const int32_t* seqlen, int32_t n_n
 int ft_plan_b200_build_direct(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, const int64_t* req_offs,
                               const int32_t* req_ids, const int64_t* node_base, const int64_t* node_offset,
                               int64_t n_extra, const int64_t* extra_begin, const int64_t* extra_end,
-                              const int32_t* extra_req, int32_t batch, int32_t num_qo_heads, int32_t num_kv_heads,
-                              int32_t head_dim, const ft_b200_model* model, ft_plan** out) {
+                              const int32_t* extra_req, int32_t tail_room, int32_t batch, int32_t num_qo_heads,
+                              int32_t num_kv_heads, int32_t head_dim, const ft_b200_model* model, ft_plan** out) {
   Direct d;
+  d.tail_room = tail_room;
   d.node_base = node_base;
   d.node_offset = node_offset;
   d.n_extra = n_extra;
@@ -472,6 +526,12 @@ int ft_plan_copy_tables(const ft_plan* plan, int32_t* kv_entries, int32_t* kv_of
 int ft_plan_copy_row_ranges(const ft_plan* plan, int32_t* q_kv_ranges) {
   if (plan == nullptr || q_kv_ranges == nullptr || plan->q_ranges.empty()) return FT_ERR_INVALID_ARGUMENT;
   std::memcpy(q_kv_ranges, plan->q_ranges.data(), plan->q_ranges.size() * sizeof(int32_t));
+  return FT_OK;
+}
+
+int ft_plan_copy_aux_segments(const ft_plan* plan, int32_t* segments) {
+  if (plan == nullptr || segments == nullptr || plan->aux_segments.empty()) return FT_ERR_INVALID_ARGUMENT;
+  std::memcpy(segments, plan->aux_segments.data(), plan->aux_segments.size() * sizeof(int32_t));
   return FT_OK;
 }
 

@@ -48,6 +48,8 @@ __global__ void __launch_bounds__(128) stage1_f32_kernel(Stage1Params p) {
   if (rows <= 0) return;
   // the grid's row blocks come from the caller's request tile: a vnode with more rows than that is a plan error
   if (blockIdx.z == gridDim.z - 1 && q_len * G - row0 > C::ROWS && threadIdx.x == 0) flag_error(FT_DEV_BAD_ROW_INDEX);
+  const int32_t* ids = kv_ids_base(p, kv_off);
+  const int id_lim = kv_ids_limit(p, kv_off, kv_len);
   const float* kbase = reinterpret_cast<const float*>(p.k) + (int64_t)kvh * p.k_s1;
   const float* vbase = reinterpret_cast<const float*>(p.v) + (int64_t)kvh * p.v_s1;
 
@@ -104,8 +106,7 @@ __global__ void __launch_bounds__(128) stage1_f32_kernel(Stage1Params p) {
       const int pos = t * C::TILE + tok;
       int64_t row = -1;
       if (pos < kv_len) {
-        const int64_t e = (int64_t)kv_off + pos;
-        if (e >= 0 && e < p.kv_entries_len) row = p.kv_entries[e];
+        if (pos < id_lim) row = ids[pos];
         if (row < 0 || row >= p.kv_rows) {
           bad = true;
           row = -1;

@@ -26,6 +26,8 @@ __global__ void __launch_bounds__(128) stage1_generic_kernel(Stage1Params p) {
   const int kv_off = p.kv_offs[vn], kv_len = p.kv_lens[vn];
   const int G = p.group, D = p.head_dim;
   const int rows = q_len * G;
+  const int32_t* ids = kv_ids_base(p, kv_off);
+  const int id_lim = kv_ids_limit(p, kv_off, max(kv_len, 0));
   const T* __restrict__ kbase = reinterpret_cast<const T*>(p.k) + (int64_t)kvh * p.k_s1;
   const T* __restrict__ vbase = reinterpret_cast<const T*>(p.v) + (int64_t)kvh * p.v_s1;
 
@@ -63,10 +65,9 @@ __global__ void __launch_bounds__(128) stage1_generic_kernel(Stage1Params p) {
       bool bad = false;  // flagged once after the loads: an atomic between them would serialise them
 #pragma unroll
       for (int u = 0; u < TB; ++u) {
-        const int64_t e = (int64_t)kv_off + t0 + u;
         int64_t idx = -1;
         if (t0 + u < r_hi) {
-          if (e >= 0 && e < p.kv_entries_len) idx = p.kv_entries[e];
+          if (t0 + u < id_lim) idx = ids[t0 + u];
           if (idx < 0 || idx >= p.kv_rows) {
             bad = true;
             idx = -1;

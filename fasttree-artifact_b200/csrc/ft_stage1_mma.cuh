@@ -145,6 +145,7 @@ struct KvPipe {
   const T* kbase;
   const T* vbase;
   const int* idx_ptr;
+  const int32_t* ids;  // the chunk's row ids in global memory
   uint32_t idx_sm, pipe_sm, row_lim;
   int kv_off, kv_len, id_lim, ntiles, tid, ld_c, ld_r;
 
@@ -155,8 +156,8 @@ struct KvPipe {
         kv_len(kv_len_) {
     tid = threadIdx.x;
     // row ids past the end of the table are a plan error: flagged once, those tokens become padding
-    const int64_t readable = p.kv_entries_len - (int64_t)kv_off;
-    id_lim = kv_off < 0 ? 0 : (int)(readable < (int64_t)kv_len ? (readable < 0 ? 0 : readable) : kv_len);
+    id_lim = kv_ids_limit(p, kv_off, kv_len);
+    ids = kv_ids_base(p, kv_off);
     if (id_lim < kv_len && tid == 0) flag_error(FT_DEV_BAD_KV_INDEX);
     row_lim = (uint32_t)(p.kv_rows < 0x7fffffffLL ? p.kv_rows : 0x7fffffffLL);
     ld_c = tid % C::CPR;
@@ -172,7 +173,7 @@ struct KvPipe {
     for (int i = 0; i < IDXB / C::THREADS; ++i) {
       const int t = i * C::THREADS + tid;
       const int pos = b * IDXB + t;
-      if (pos < id_lim) cp_async4(dst + t * 4, p.kv_entries + kv_off + pos);
+      if (pos < id_lim) cp_async4(dst + t * 4, ids + pos);
     }
   }
   // blocks 0 and 1: issue early (their round trip then overlaps the caller's own dependent loads), wait before

@@ -246,8 +246,7 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
     return true;
   };
   auto id_limit = [&](int kv_off, int kv_len) {  // readable row ids of a chunk (a table that ends early is a plan error)
-    const int64_t readable = p.kv_entries_len - (int64_t)kv_off;
-    return kv_off < 0 ? 0 : (int)(readable < (int64_t)kv_len ? (readable < 0 ? 0 : readable) : kv_len);
+    return kv_ids_limit(p, kv_off, kv_len);
   };
   // one K or V tile into `buf`, signalling `full`: TMA when its 64 row ids (cur: two per lane) are consecutive
   auto load_tile = [&](const CUtensorMap* map, const T* base, int64_t s0, int kvh, int tt, int id_lim, const int (&cur)[2],
@@ -292,7 +291,7 @@ __global__ void __launch_bounds__(PsCfg::THREADS, 2) stage1_persist_kernel(const
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int pos = tile * C::TILE + lane + 32 * h;
-      dst[h] = pos < lim ? __ldg(p.kv_entries + kv_off + pos) : -1;
+      dst[h] = pos < lim ? __ldg(kv_ids_base(p, kv_off) + pos) : -1;
     }
   };
 

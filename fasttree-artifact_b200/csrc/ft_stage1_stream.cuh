@@ -184,8 +184,7 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
 
   // readable row ids of a task (a table that ends early is a plan error: flagged, the tokens become padding)
   auto id_limit = [&](int kv_off, int kv_len) {
-    const int64_t readable = p.kv_entries_len - (int64_t)kv_off;
-    return kv_off < 0 ? 0 : (int)(readable < (int64_t)kv_len ? (readable < 0 ? 0 : readable) : kv_len);
+    return kv_ids_limit(p, kv_off, kv_len);
   };
   // row ids of tile `t` of the task in metadata slot `m` -> ids ring slot `rs`; at t == 0 also the request ids
   auto issue_ids = [&](int m, int t, int rs, int qs) {
@@ -194,7 +193,7 @@ __device__ __forceinline__ void stream_worker(const TcParams& tp, uint8_t* smem,
       const int kv_off = meta_ptr[m * 8 + 2], kv_len = max(meta_ptr[m * 8 + 3], 0);
       const int lim = id_limit(kv_off, kv_len);
       const int pos = t * C::TILE + i;
-      if (pos < lim) cp_async4(ids_sm + (rs * C::TILE + i) * 4, p.kv_entries + kv_off + pos);
+      if (pos < lim) cp_async4(ids_sm + (rs * C::TILE + i) * 4, kv_ids_base(p, kv_off) + pos);
       if (i == 0 && t == 0 && lim < kv_len) flag_error(FT_DEV_BAD_KV_INDEX);
     } else if (warp == 1 && t == 0) {  // warp 1: request ids of the task's (at most 16) slots
       const int q_off = meta_ptr[m * 8 + 0], q_len = meta_ptr[m * 8 + 1];

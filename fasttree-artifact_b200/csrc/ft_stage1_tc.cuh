@@ -300,8 +300,8 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
   const float scale2 = p.sm_scale * 1.4426950408889634f;
   const int ntiles = (kv_len + C::TILE - 1) / C::TILE;
   // row ids past the end of the table are a plan error: flag once, treat those tokens as padding
-  const int64_t readable = p.kv_entries_len - (int64_t)kv_off;
-  const int id_lim = kv_off < 0 ? 0 : (int)(readable < (int64_t)kv_len ? (readable < 0 ? 0 : readable) : kv_len);
+  const int id_lim = kv_ids_limit(p, kv_off, kv_len);
+  const int32_t* ids_of_chunk = kv_ids_base(p, kv_off);
   if (rows > 0 && id_lim < kv_len && tid == 0) flag_error(FT_DEV_BAD_KV_INDEX);
   const uint32_t row_lim = (uint32_t)(p.kv_rows < 0x7fffffffLL ? p.kv_rows : 0x7fffffffLL);
   auto k_buf = [&](int t) { return sm + C::K_OFF + (t % C::NSK) * 16384; };
@@ -585,7 +585,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               const int pos = t * C::TILE + lane + 32 * h;
-              dst[h] = pos < id_lim ? __ldg(p.kv_entries + kv_off + pos) : -1;
+              dst[h] = pos < id_lim ? __ldg(ids_of_chunk + pos) : -1;
             }
           };
           int cur[2] = {-1, -1}, nxt[2] = {-1, -1};
@@ -645,7 +645,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int i = lane + 32 * h, pos = t * C::TILE + i;
-            if (pos < id_lim) cp_async4(idx_sm + ((t % C::IDX_SLOTS) * C::TILE + i) * 4, p.kv_entries + kv_off + pos);
+            if (pos < id_lim) cp_async4(idx_sm + ((t % C::IDX_SLOTS) * C::TILE + i) * 4, ids_of_chunk + pos);
           }
         };
         // one operand tile (K or V of tile t) into `buf`, signalling `full`

@@ -19,6 +19,8 @@ import os
 
 import torch
 
+from ft_b200 import engine as _engine
+
 from .attn_kernels import fasttree_decode
 from .metadata import FastTreeMetadata
 
@@ -37,6 +39,16 @@ def _replace_radix_attn():
             o = torch.empty_like(q)
         self.store_kv_cache(k, v, input_metadata)       # the new token's K/V must be in the pool first
         md = input_metadata.fasttree
+        if md.refresh_pending or (md.graph_safe and md.group_tails and md.refresh_layer == self.layer_id):
+            # First attention call of a step: the newest token of every request has its KV-pool slot by now, and
+            # the grouped tails take its row id into their table.  In graph-safe mode the layer that did this
+            # first keeps doing it on every call (over the whole state table; unused entries are skipped), so a
+            # captured step carries the copy whenever it was captured.
+            _engine.refresh_tails(md.tail_state, md.max_batch_size if md.graph_safe else q.shape[0],
+                                  input_metadata.req_to_token_pool.req_to_token, md.kv_entries_aux)
+            md.refresh_pending = False
+            if md.refresh_layer is None:
+                md.refresh_layer = self.layer_id
         fasttree_decode(
             q.view(-1, self.tp_q_head_num, self.qk_head_dim),
             input_metadata.token_to_kv_pool.get_key_buffer(self.layer_id),
@@ -50,6 +62,8 @@ def _replace_radix_attn():
             md.phase_node_nums, md.phase_node_offsets, md.phase_q_tile_sizes, md.phase_kv_tile_sizes,
             sm_scale=self.scaling, logit_cap=self.logit_cap,
             phase_info=md.phase_info_dev if md.graph_safe else None,
+            row_ranges=md.vnode_q_kv_ranges if md.group_tails else None,
+            kv_entries_aux=md.kv_entries_aux if md.group_tails else None,
         )
         return o
 

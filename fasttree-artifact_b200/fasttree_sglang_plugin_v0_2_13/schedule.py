@@ -68,11 +68,17 @@ def _bfs(batch, node_to_reqs):
     return order, offsets, parents
 
 
-def _upload(md, tabs, last_vnodes):
+def _upload(md, tabs, last_vnodes, tail_state=None, src_table=None):
     nv, rows, bsz = tabs["vnode_to_kv_offs"].size, tabs["vnode_to_q_entries"].size, tabs["req_to_vnode_offs"].size
     if nv > md.max_vnodes or rows > md.max_vnode_to_q_entries or bsz > md.max_batch_size:
         raise ValueError(f"plan ({nv} vnodes, {rows} partial rows, batch {bsz}) exceeds the capacity of "
                          f"FastTreeMetadata ({md.max_vnodes}, {md.max_vnode_to_q_entries}, {md.max_batch_size})")
+    segs = tabs.get("aux_segments")
+    n_seg = 0 if segs is None else int(segs.shape[0])
+    if getattr(md, "group_tails", False):
+        if n_seg > md.aux_segments.shape[1] or int(tabs.get("aux_entries", 0)) > md.kv_entries_aux.numel():
+            raise ValueError(f"plan ({n_seg} grouped runs, {tabs.get('aux_entries', 0)} auxiliary row ids) exceeds the "
+                             f"capacity of FastTreeMetadata ({md.aux_segments.shape[1]}, {md.kv_entries_aux.numel()})")
 
     def put(dst, arr):
         t = torch.from_numpy(np.ascontiguousarray(arr, dtype=np.int32))
@@ -88,6 +94,36 @@ def _upload(md, tabs, last_vnodes):
     put(md.req_to_vnode_lens, tabs["req_to_vnode_lens"])
     put(md.req_last_vnodes_dev, np.asarray(last_vnodes, dtype=np.int32))
     put(md.phase_info_dev, np.asarray(list(tabs["phase_node_nums"]) + list(tabs["phase_node_offsets"]), dtype=np.int32))
+    state = np.full((bsz, 4), -1, dtype=np.int32)
+    if tail_state is None:                      # every tail is a vnode of its own
+        state[:, 2] = np.asarray(last_vnodes, dtype=np.int32)
+    else:
+        state[:] = tail_state
+    md.tail_state[:bsz].copy_(torch.from_numpy(state), non_blocking=True)
+    stale = getattr(md, "tail_rows", 0)
+    if stale > bsz:                             # entries of a larger earlier batch must read "unused"
+        md.tail_state[bsz:stale].fill_(-1)
+    md.tail_rows = bsz
+    md.num_grouped_tails = int((state[:, 0] >= 0).sum())
+    md.steps_since_plan = 0
+    if getattr(md, "group_tails", False):
+        # the decode call always passes the range table: rows of plain vnodes see their whole chunk
+        ranges = tabs.get("vnode_q_kv_ranges")
+        if ranges is None:
+            ranges = np.zeros((rows, 2), dtype=np.int32)
+            ranges[:, 1] = np.iinfo(np.int32).max
+        md.vnode_q_kv_ranges[:rows].copy_(torch.from_numpy(np.ascontiguousarray(ranges, dtype=np.int32)), non_blocking=True)
+        if n_seg:
+            md.aux_segments[:, :n_seg].copy_(torch.from_numpy(np.ascontiguousarray(segs.T, dtype=np.int32)), non_blocking=True)
+            if md.kv_entries_aux.is_cuda:
+                _engine.gather_kv_entries(src_table, md.aux_segments[0], md.aux_segments[1], md.aux_segments[2],
+                                          md.aux_segments[3], n_seg, md.kv_entries_aux)
+            else:       # plan tables kept on the host (planner tests, tools): the same table, built with torch
+                flat = src_table.reshape(-1)
+                for src, length, dst, room in segs.tolist():
+                    md.kv_entries_aux[dst:dst + length] = flat[src:src + length]
+                    md.kv_entries_aux[dst + length:dst + length + room] = flat[src]
+        md.refresh_pending = md.num_grouped_tails > 0 or (md.graph_safe and md.refresh_layer is None)
     md.phase_node_nums = list(tabs["phase_node_nums"])
     md.phase_node_offsets = list(tabs["phase_node_offsets"])
     md.req_last_vnodes = [int(v) for v in last_vnodes]
@@ -206,18 +242,30 @@ def _plan_b200(batch, md, node_to_reqs, covered, order, offsets, parents, req_id
         end = len(req.origin_input_ids) + len(req.output_ids) + 1
         base = stride * int(req_idx[rid])
         extra.append(([(base + tail_start[rid], base + end)], [rid]))
-    if getattr(md, "native_planner", True):
-        # the native splitter of the shared library; the Python branch below is its specification
-        node_base = [stride * int(req_idx[nd.requests[0]]) if nd.requests else 0 for nd in tree]
-        tabs, q_tile, small_tile, tile_tokens = _planner.b200_tables_native_direct(
-            tree, node_base, offsets, [(r[0][0], r[0][1], q[0]) for r, q in extra], len(batch.reqs),
-            md.num_qo_heads, md.num_kv_heads, md.head_dim, model)
-    else:
+    def run(tail_room, model):
+        if getattr(md, "native_planner", True):
+            # the native splitter of the shared library; the Python branch below is its specification
+            node_base = [stride * int(req_idx[nd.requests[0]]) if nd.requests else 0 for nd in tree]
+            return _planner.b200_tables_native_direct(
+                tree, node_base, offsets, [(r[0][0], r[0][1], q[0]) for r, q in extra], len(batch.reqs),
+                md.num_qo_heads, md.num_kv_heads, md.head_dim, model, tail_room=tail_room)
         vnodes, _assign, q_tile, small_tile, _target = _planner.b200_virtual_nodes(
-            tree, md.num_qo_heads, md.num_kv_heads, md.head_dim, model, ranges_of, extra=extra)
+            tree, md.num_qo_heads, md.num_kv_heads, md.head_dim, model, ranges_of, extra=extra, tail_room=tail_room)
         tabs = _planner.emit_tables(vnodes, len(batch.reqs), small_tile=small_tile, direct_offsets=True,
                                     order_key=_planner.b200_task_order)
-        tile_tokens = model.tile_tokens
+        return tabs, q_tile, small_tile, model.tile_tokens
+
+    tabs, q_tile, small_tile, tile_tokens = run(-1, model)
+    if getattr(md, "group_tails", False):
+        # Groups pay when the few-row tasks alone would queue up several deep behind the resident CTAs; then the
+        # burst is planned again with short runs packed into many-row vnodes.  A group needs more than 16 query
+        # rows anyway (only the many-row kernels honour row ranges); past that, a handful of one-tile tails
+        # already costs less as one task than as one task each.
+        few_row_ctas = tabs["phase_node_nums"][1] * md.num_kv_heads
+        if few_row_ctas >= md.group_tails_min_load * model.num_sms * model.ctas_per_sm:
+            from dataclasses import replace
+            tabs, q_tile, small_tile, tile_tokens = run(
+                md.tail_room, replace(model, group_min_members=min(model.group_min_members, 4)))
     md.phase_q_tile_sizes = [q_tile, small_tile]
     md.phase_kv_tile_sizes = [tile_tokens, tile_tokens]
     # the task holding the END of each request's tail (the one that grows during the burst)
@@ -225,14 +273,37 @@ def _plan_b200(batch, md, node_to_reqs, covered, order, offsets, parents, req_id
     for rid, req in enumerate(batch.reqs):
         ends[stride * int(req_idx[rid]) + len(req.origin_input_ids) + len(req.output_ids) + 1] = rid
     last = [-1] * len(batch.reqs)
-    kv_end = tabs["vnode_to_kv_offs"].astype(np.int64) + tabs["vnode_to_kv_lens"]
-    for task in np.flatnonzero(tabs["vnode_to_q_lens"] == 1):
+    kv_offs = tabs["vnode_to_kv_offs"].astype(np.int64)
+    kv_end = kv_offs + tabs["vnode_to_kv_lens"]
+    for task in np.flatnonzero((tabs["vnode_to_q_lens"] == 1) & (kv_offs < _planner.AUX_BIT)):
         rid = ends.get(int(kv_end[task]))
         if rid is not None and int(tabs["vnode_to_q_entries"][tabs["vnode_to_q_offs"][task]]) == rid:
             last[rid] = int(task)
+    # tails that became members of a group: the run that ends where the request ends and has room behind it
+    state = np.full((len(batch.reqs), 4), -1, dtype=np.int32)
+    segs = tabs.get("aux_segments")
+    if segs is not None and len(segs):
+        groups = np.flatnonzero(kv_offs >= _planner.AUX_BIT)
+        g_base = kv_offs[groups] - _planner.AUX_BIT
+        by_base = np.argsort(g_base)
+        for src, length, dst, room in segs.tolist():
+            rid = ends.get(src + length)
+            if rid is None or room <= 0:
+                continue
+            task = int(groups[by_base[np.searchsorted(g_base[by_base], dst, side="right") - 1]])
+            q0, qn = int(tabs["vnode_to_q_offs"][task]), int(tabs["vnode_to_q_lens"][task])
+            hit = np.flatnonzero(tabs["vnode_to_q_entries"][q0:q0 + qn] == rid)
+            if hit.size != 1:
+                raise RuntimeError("internal error: a grouped tail has no partial row of its own")
+            state[rid] = (dst + length, src + length, q0 + int(hit[0]), room)
+            last[rid] = task
     if min(last, default=0) < 0:
         raise RuntimeError("internal error: a request has no tail task")
+    for rid in range(len(batch.reqs)):
+        if state[rid, 0] < 0:
+            state[rid, 2] = last[rid]
     tabs["req_to_vnode_entries"] = tabs["req_to_vnode_entries"][:-_planner.PAD_ENTRIES]
+    tabs["tail_state"] = state
     return tabs, last
 
 
@@ -248,7 +319,8 @@ def prepare_for_fasttree_meta(batch, fasttree_metadata):
         tabs, last = _plan_reference(batch, md, node_to_reqs, order, offsets, req_idx, stride)
     else:
         tabs, last = _plan_b200(batch, md, node_to_reqs, covered, order, offsets, parents, req_idx, stride)
-    _upload(md, tabs, last)
+    _upload(md, tabs, last, tail_state=tabs.get("tail_state"),
+            src_table=batch.req_to_token_pool.req_to_token if getattr(md, "group_tails", False) else None)
     batch.fasttree_metadata = md
 
 
@@ -257,4 +329,17 @@ def prepare_for_fasttree_step(batch, fasttree_metadata):
     last private chunk (reference: schedule.py:278-283).  One tiny kernel, no
     host-to-device copy."""
     md = fasttree_metadata
-    _engine.bump_kv_lens(md.vnode_to_kv_lens, md.req_last_vnodes_dev[:len(batch.reqs)])
+    md.steps_since_plan += 1
+    if md.num_grouped_tails and md.steps_since_plan > md.tail_room:
+        raise RuntimeError(f"a burst of more than {md.tail_room} steps after one plan: raise FastTreeMetadata.tail_room")
+    if md.tail_state.is_cuda:
+        _engine.bump_tails(md.tail_state, len(batch.reqs), md.vnode_q_kv_ranges, md.vnode_to_kv_lens)
+    else:               # plan tables kept on the host (planner tests, tools)
+        for rid in range(len(batch.reqs)):
+            aux_pos, _src, index, room = md.tail_state[rid].tolist()
+            if aux_pos < 0:
+                md.vnode_to_kv_lens[index] += 1
+            else:
+                md.vnode_q_kv_ranges[index, 1] += 1
+                md.tail_state[rid] += torch.tensor([1, 1, 0, -1], dtype=torch.int32)
+    md.refresh_pending = md.num_grouped_tails > 0

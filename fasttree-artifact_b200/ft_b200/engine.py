@@ -109,8 +109,10 @@ def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, 
                vnode_to_q_entries, vnode_to_q_offs, vnode_to_q_lens, req_to_vnode_entries,
                req_to_vnode_offs, req_to_vnode_lens, mid_o, mid_lse, phase_node_nums, phase_node_offsets,
                phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap=-1, path="auto", o_lse=None,
-               stream=None, row_ranges="detect", phase_info=None):
-    """Validate the tensors and fill a :class:`DecodeArgs` struct.  ``phase_info``: an
+               stream=None, row_ranges="detect", phase_info=None, kv_entries_aux=None):
+    """Validate the tensors and fill a :class:`DecodeArgs` struct.  ``kv_entries_aux``: an
+    int32 CUDA tensor, the second row-id table that vnodes with bit 30 of their
+    ``vnode_to_kv_offs`` value set read (grouped private tails of the serving path).  ``phase_info``: an
     int32 CUDA tensor ``[n0, n1, o0, o1]`` that stage 1 reads on the device in
     place of ``phase_node_nums`` / ``phase_node_offsets`` (the launch then does not
     depend on the plan and survives a re-plan inside a captured CUDA graph).  ``row_ranges``:
@@ -154,6 +156,8 @@ def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, 
         _table("phase_info", phase_info)
         if phase_info.numel() < 4:
             raise ValueError("phase_info needs four entries: n0, n1, o0, o1")
+    if kv_entries_aux is not None:
+        _table("kv_entries_aux", kv_entries_aux)
     for cnt, off in ((n0, f0), (n1, f1)):
         if phase_info is None and (cnt < 0 or off < 0 or off + cnt > nv):
             raise ValueError("phase_node_nums / phase_node_offsets do not fit the vnode tables")
@@ -184,6 +188,8 @@ def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, 
     a = _lib.DecodeArgs()
     a.vnode_q_kv_ranges = ranges.data_ptr() if ranges is not None else None
     a.device_phase_info = phase_info.data_ptr() if phase_info is not None else None
+    a.vnode_to_kv_entries_aux = kv_entries_aux.data_ptr() if kv_entries_aux is not None else None
+    a.kv_entries_aux_len = kv_entries_aux.numel() if kv_entries_aux is not None else 0
     a.q, a.k_buffer, a.v_buffer, a.o = q.data_ptr(), k_buffer.data_ptr(), v_buffer.data_ptr(), o.data_ptr()
     a.o_lse = o_lse.data_ptr() if o_lse is not None else None
     a.dtype = _DTYPES[q.dtype]
@@ -213,7 +219,7 @@ def build_args(q, k_buffer, v_buffer, o, vnode_to_kv_entries, vnode_to_kv_offs, 
     return a
 
 
-def _cached_args(tensors, rest, path, o_lse, row_ranges, phase_info=None):
+def _cached_args(tensors, rest, path, o_lse, row_ranges, phase_info=None, kv_entries_aux=None):
     """Argument structs are memoised so that a steady-state decode loop pays for
     one dict lookup and a few pointer stores instead of rebuilding ~45 fields.
     The key names only what persists across calls - the K/V buffers, the plan
@@ -232,7 +238,8 @@ def _cached_args(tensors, rest, path, o_lse, row_ranges, phase_info=None):
     ranges_key = row_ranges if is_detect or row_ranges is None else id(row_ranges)
     key = (tuple(map(id, persistent)), pn[0], pn[1], po[0], po[1], pq[0], pq[1], pk[0], pk[1], sm_scale, logit_cap,
            path, stream, ranges_key, q.shape, q.stride(), q.dtype, o.shape, o.stride(), o.dtype, o_lse is None,
-           id(phase_info) if phase_info is not None else None)
+           id(phase_info) if phase_info is not None else None,
+           (id(kv_entries_aux), kv_entries_aux.data_ptr(), kv_entries_aux.numel()) if kv_entries_aux is not None else None)
     ptrs = tuple([t.data_ptr() for t in persistent])
     hit = _ARG_CACHE.get(key)
     if hit is not None and hit[1] == ptrs and (not is_detect or hit[3] == _version_of(tensors[7])):
@@ -241,10 +248,10 @@ def _cached_args(tensors, rest, path, o_lse, row_ranges, phase_info=None):
             raise ValueError("q / o must live on a CUDA device; the engine has no CPU path")
     else:
         a = build_args(*tensors, pn, po, pq, pk, sm_scale, logit_cap, path=path, o_lse=o_lse, stream=stream,
-                       row_ranges=row_ranges, phase_info=phase_info)
+                       row_ranges=row_ranges, phase_info=phase_info, kv_entries_aux=kv_entries_aux)
         if len(_ARG_CACHE) >= _ARG_CACHE_MAX:
             _ARG_CACHE.clear()
-        keep = (row_ranges if isinstance(row_ranges, torch.Tensor) else None, phase_info)
+        keep = (row_ranges if isinstance(row_ranges, torch.Tensor) else None, phase_info, kv_entries_aux)
         _ARG_CACHE[key] = (a, ptrs, persistent, _version_of(tensors[7]), keep)
     a.q, a.o = q.data_ptr(), o.data_ptr()
     if o_lse is not None:
@@ -260,12 +267,12 @@ def _cached_args(tensors, rest, path, o_lse, row_ranges, phase_info=None):
 def _call(fn_name, q, k_buffer, v_buffer, o, kv_entries, kv_offs, kv_lens, q_entries, q_offs, q_lens,
           r2v_entries, r2v_offs, r2v_lens, mid_o, mid_lse, phase_node_nums, phase_node_offsets,
           phase_q_tile_sizes, phase_kv_tile_sizes, sm_scale, logit_cap, path, o_lse, row_ranges="detect",
-          phase_info=None):
+          phase_info=None, kv_entries_aux=None):
     tensors = (q, k_buffer, v_buffer, o, kv_entries, kv_offs, kv_lens, q_entries, q_offs, q_lens,
                r2v_entries, r2v_offs, r2v_lens, mid_o, mid_lse)
     rest = (phase_node_nums, phase_node_offsets, phase_q_tile_sizes, phase_kv_tile_sizes,
             float(sm_scale), float(logit_cap))
-    a = _cached_args(tensors, rest, path, o_lse, row_ranges, phase_info)
+    a = _cached_args(tensors, rest, path, o_lse, row_ranges, phase_info, kv_entries_aux)
     lib = _lib.load()
     if q.device.index != torch.cuda.current_device():
         with torch.cuda.device(q.device):
@@ -275,14 +282,14 @@ def _call(fn_name, q, k_buffer, v_buffer, o, kv_entries, kv_offs, kv_lens, q_ent
     _lib.check(rc)
 
 
-def decode(*args, logit_cap=-1, path="auto", o_lse=None, row_ranges="detect", phase_info=None):
+def decode(*args, logit_cap=-1, path="auto", o_lse=None, row_ranges="detect", phase_info=None, kv_entries_aux=None):
     """Stage 1 + stage 2.  Positional arguments are those of the reference's
     ``fasttree_decode`` up to and including ``sm_scale``."""
-    _call("ft_decode", *args, logit_cap, path, o_lse, row_ranges, phase_info)
+    _call("ft_decode", *args, logit_cap, path, o_lse, row_ranges, phase_info, kv_entries_aux)
 
 
-def stage1(*args, logit_cap=-1, path="auto", row_ranges="detect", phase_info=None):
-    _call("ft_stage1", *args, logit_cap, path, None, row_ranges, phase_info)
+def stage1(*args, logit_cap=-1, path="auto", row_ranges="detect", phase_info=None, kv_entries_aux=None):
+    _call("ft_stage1", *args, logit_cap, path, None, row_ranges, phase_info, kv_entries_aux)
 
 
 def stage2(*args, logit_cap=-1, o_lse=None):
@@ -356,3 +363,47 @@ def bump_kv_lens(vnode_to_kv_lens, last_vnodes):
     stream = torch.cuda.current_stream(vnode_to_kv_lens.device).cuda_stream
     _lib.check(_lib.load().ft_bump_kv_lens(vnode_to_kv_lens.data_ptr(), last_vnodes.data_ptr(),
                                            last_vnodes.numel(), stream))
+
+
+def gather_kv_entries(src_table, seg_src, seg_len, seg_dst, seg_room, n_segments, aux_table):
+    """Build the auxiliary row-id table on the device (``ft_gather_kv_entries``): segment ``i`` copies
+    ``seg_len[i]`` ids from ``src_table[seg_src[i]:]`` to ``aux_table[seg_dst[i]:]`` and pads ``seg_room[i]``
+    entries behind them with the segment's first id.  All tensors int32 on one CUDA device; current stream."""
+    for name, t in (("src_table", src_table), ("seg_src", seg_src), ("seg_len", seg_len), ("seg_dst", seg_dst),
+                    ("seg_room", seg_room), ("aux_table", aux_table)):
+        _table(name, t)
+    if min(seg_src.numel(), seg_len.numel(), seg_dst.numel(), seg_room.numel()) < n_segments:
+        raise ValueError("segment tables are shorter than n_segments")
+    stream = torch.cuda.current_stream(aux_table.device).cuda_stream
+    _lib.check(_lib.load().ft_gather_kv_entries(src_table.data_ptr(), src_table.numel(), seg_src.data_ptr(),
+                                                seg_len.data_ptr(), seg_dst.data_ptr(), seg_room.data_ptr(),
+                                                int(n_segments), aux_table.data_ptr(), aux_table.numel(), stream))
+
+
+def bump_tails(tail_state, n, row_ranges, vnode_to_kv_lens):
+    """One step of a burst (``ft_bump_tails``): per request, either the grouped tail's partial row sees one
+    token more (its range end in ``row_ranges`` moves up), or the tail's own vnode grows by one.
+    ``tail_state`` is an int32 ``[n, 4]`` CUDA tensor ``{aux_pos | -1, src_pos, partial row | vnode, room}``."""
+    _table("tail_state", tail_state)
+    _table("vnode_to_kv_lens", vnode_to_kv_lens)
+    if tail_state.numel() < 4 * n:
+        raise ValueError("tail_state is shorter than 4 * n")
+    if row_ranges is not None:
+        _table("row_ranges", row_ranges)
+    stream = torch.cuda.current_stream(tail_state.device).cuda_stream
+    _lib.check(_lib.load().ft_bump_tails(
+        tail_state.data_ptr(), int(n), row_ranges.data_ptr() if row_ranges is not None else None,
+        row_ranges.numel() // 2 if row_ranges is not None else 0, vnode_to_kv_lens.data_ptr(), vnode_to_kv_lens.numel(),
+        stream))
+
+
+def refresh_tails(tail_state, n, src_table, aux_table):
+    """``aux_table[aux_pos - 1] = src_table[src_pos - 1]`` for every grouped tail (``ft_refresh_tails``): the
+    newest token's row id, which exists only once the step's batch has been prepared.  Current stream."""
+    for name, t in (("tail_state", tail_state), ("src_table", src_table), ("aux_table", aux_table)):
+        _table(name, t)
+    if tail_state.numel() < 4 * n:
+        raise ValueError("tail_state is shorter than 4 * n")
+    stream = torch.cuda.current_stream(tail_state.device).cuda_stream
+    _lib.check(_lib.load().ft_refresh_tails(tail_state.data_ptr(), int(n), src_table.data_ptr(), src_table.numel(),
+                                            aux_table.data_ptr(), aux_table.numel(), stream))

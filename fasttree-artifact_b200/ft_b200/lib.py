@@ -21,8 +21,10 @@ FT_DEV_BAD_KV_INDEX, FT_DEV_BAD_Q_INDEX, FT_DEV_BAD_ROW_INDEX, FT_DEV_WAIT_TIMEO
 
 EXPORTS = ["ft_version", "ft_decode_args_size", "ft_last_error", "ft_decode", "ft_stage1", "ft_stage2",
            "ft_decode_static_scratch", "ft_decode_host_io", "ft_selftest_bounded_wait", "ft_read_wait_diagnostics", "ft_bump_kv_lens",
+           "ft_gather_kv_entries", "ft_bump_tails", "ft_refresh_tails",
            "ft_read_device_status", "ft_launch_count", "ft_stage1_path_name",
            "ft_plan_b200_build", "ft_plan_b200_build_direct", "ft_plan_get_info", "ft_plan_copy_tables", "ft_plan_copy_row_ranges",
+           "ft_plan_copy_aux_segments",
            "ft_plan_free"]
 
 
@@ -49,7 +51,8 @@ class PlanInfo(ctypes.Structure):
                 ("batch", ctypes.c_int64), ("nodes", ctypes.c_int64), ("virtual_nodes", ctypes.c_int64),
                 ("phase_node_nums", ctypes.c_int32 * 2), ("phase_node_offsets", ctypes.c_int32 * 2),
                 ("q_tile", ctypes.c_int32), ("small_tile", ctypes.c_int32), ("tile_tokens", ctypes.c_int32),
-                ("has_row_ranges", ctypes.c_int32), ("target_bytes", ctypes.c_double)]
+                ("has_row_ranges", ctypes.c_int32), ("target_bytes", ctypes.c_double),
+                ("aux_entries", ctypes.c_int64), ("aux_segments", ctypes.c_int64)]
 
 
 class DecodeArgs(ctypes.Structure):
@@ -80,6 +83,8 @@ class DecodeArgs(ctypes.Structure):
         ("stream", ctypes.c_void_p),
         ("vnode_q_kv_ranges", ctypes.c_void_p),
         ("device_phase_info", ctypes.c_void_p),
+        ("vnode_to_kv_entries_aux", ctypes.c_void_p),
+        ("kv_entries_aux_len", ctypes.c_int64),
     ]
 
 
@@ -129,6 +134,13 @@ def load():
         lib.ft_selftest_bounded_wait.restype = ctypes.c_int
         lib.ft_bump_kv_lens.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]
         lib.ft_bump_kv_lens.restype = ctypes.c_int
+        vp, i32, i64 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64
+        lib.ft_gather_kv_entries.argtypes = [vp, i64, vp, vp, vp, vp, i32, vp, i64, vp]
+        lib.ft_gather_kv_entries.restype = ctypes.c_int
+        lib.ft_bump_tails.argtypes = [vp, i32, vp, i64, vp, i32, vp]
+        lib.ft_bump_tails.restype = ctypes.c_int
+        lib.ft_refresh_tails.argtypes = [vp, i32, vp, i64, vp, i64, vp]
+        lib.ft_refresh_tails.restype = ctypes.c_int
         lib.ft_read_device_status.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
         lib.ft_read_device_status.restype = ctypes.c_int
         lib.ft_launch_count.restype = ctypes.c_int64
@@ -141,7 +153,8 @@ def load():
         lib.ft_plan_b200_build.restype = ctypes.c_int
         lib.ft_plan_b200_build_direct.argtypes = [i32p, i32p, ctypes.c_int32, i64p, i32p, i64p, i64p, ctypes.c_int64, i64p,
                                                   i64p, i32p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
-                                                  ctypes.POINTER(B200ModelStruct), ctypes.POINTER(ctypes.c_void_p)]
+                                                  ctypes.c_int32, ctypes.POINTER(B200ModelStruct),
+                                                  ctypes.POINTER(ctypes.c_void_p)]
         lib.ft_plan_b200_build_direct.restype = ctypes.c_int
         lib.ft_plan_get_info.argtypes = [ctypes.c_void_p, ctypes.POINTER(PlanInfo)]
         lib.ft_plan_get_info.restype = ctypes.c_int
@@ -149,6 +162,8 @@ def load():
         lib.ft_plan_copy_tables.restype = ctypes.c_int
         lib.ft_plan_copy_row_ranges.argtypes = [ctypes.c_void_p, i32p]
         lib.ft_plan_copy_row_ranges.restype = ctypes.c_int
+        lib.ft_plan_copy_aux_segments.argtypes = [ctypes.c_void_p, i32p]
+        lib.ft_plan_copy_aux_segments.restype = ctypes.c_int
         lib.ft_plan_free.argtypes = [ctypes.c_void_p]
         lib.ft_plan_free.restype = None
         _lib = lib

@@ -27,6 +27,8 @@ from dataclasses import dataclass, field, replace
 import numpy as np
 
 PAD_ENTRIES = 32  # the reference appends 32 x -1 to both index lists (fasttree.py:261-262)
+AUX_BIT = 1 << 30     # FT_KV_OFFSET_AUX: a vnode_to_kv_offs value with this bit indexes the auxiliary row-id table
+GROUP_MAX_TILES_DIRECT = 24  # ... and a group of the serving path never more than this
 GROUP_MAX_TILES = 16  # a group of short nodes never spans more KV tiles than this (same constant in csrc/ft_planner.cu)
 
 
@@ -38,6 +40,8 @@ class VirtualNode:
     q_tile: int            # requests per task
     kv_split: int          # tokens per task
     row_ranges: list = None  # group of short nodes: per request the (begin, end) tokens of the chunk it attends to
+    room: int = 0            # serving path: spare row ids kept behind this pairing when it joins a group (a tail grows)
+    member_room: list = None  # group in the serving path: the room behind each of its ranges
 
 
 @dataclass
@@ -55,6 +59,8 @@ class Plan:
     phase_node_offsets: list
     node_assignments: list
     vnode_q_kv_ranges: np.ndarray = None   # optional [partial rows, 2]: tokens of its chunk a partial row attends to
+    aux_segments: np.ndarray = None        # serving plans with groups: [n, 4] {source, length, position, room} of the auxiliary row-id table
+    aux_entries: int = 0
     phase_q_tile_sizes: list = field(default_factory=list)
     phase_kv_tile_sizes: list = field(default_factory=list)
     kv_split_sizes: list = field(default_factory=list)
@@ -87,13 +93,23 @@ def emit_tables(vnodes, batch_size, small_tile, order_key=None, order_out=None, 
     ``vnode_to_kv_offs`` are those offsets."""
     kv_chunks, kv_offs, kv_lens, q_chunks, q_offs, q_lens = [], [], [], [], [], []
     range_chunks, any_ranges = [], False
-    kv_total = q_total = 0
+    kv_total = q_total = aux_total = 0
+    aux_segments = []
     for vn in vnodes:
         reqs = np.asarray(vn.requests, dtype=np.int32)
         nreq = int(reqs.size)
         if nreq == 0:
             continue
-        if direct_offsets:
+        if direct_offsets and vn.member_room is not None:
+            # a group of the serving path: its row ids are gathered into an auxiliary table
+            kv_base, length = AUX_BIT + aux_total, 0
+            for (rb, re_), room in zip(vn.kv_ranges, vn.member_room):
+                if rb >= AUX_BIT or aux_total + length + (re_ - rb) + room >= AUX_BIT:
+                    raise ValueError("plan does not fit the auxiliary table's 30-bit offsets")
+                aux_segments.append((int(rb), int(re_ - rb), aux_total + length, int(room)))
+                length += int(re_ - rb) + int(room)
+            aux_total += length
+        elif direct_offsets:
             (rb, re_), = vn.kv_ranges
             length = int(re_ - rb)
             if length <= 0:
@@ -126,7 +142,8 @@ def emit_tables(vnodes, batch_size, small_tile, order_key=None, order_out=None, 
             any_ranges = True
         else:                                  # every row of chunk c sees the whole chunk
             full = np.zeros((n_kv, nreq, 2), dtype=np.int32)
-            full[:, :, 1] = c_len[:, None]
+            # (serving path: a chunk may grow during the burst, so the end is left open; the kernels clip it)
+            full[:, :, 1] = np.iinfo(np.int32).max if direct_offsets else c_len[:, None]
             range_chunks.append(full.reshape(-1, 2))
         kv_total += length
         q_total += n_kv * nreq
@@ -166,6 +183,7 @@ def emit_tables(vnodes, batch_size, small_tile, order_key=None, order_out=None, 
         vnode_q_kv_ranges=np.ascontiguousarray(np.concatenate(range_chunks)) if any_ranges else None,
         phase_node_nums=[int(big.size), int(small.size)],
         phase_node_offsets=[0, int(big.size)],
+        aux_segments=np.asarray(aux_segments, dtype=np.int32).reshape(-1, 4), aux_entries=int(aux_total),
     )
 
 
@@ -413,7 +431,7 @@ def plan_b200(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, p
                 info={"planner": "b200", "target_bytes": float(target), "vnodes": len(vnodes)}, **tabs)
 
 
-def b200_group_short_nodes(vnodes, q_tile, small_tile, m, target_tokens):
+def b200_group_short_nodes(vnodes, q_tile, small_tile, m, target_tokens, direct=False, num_kv_heads=1):
     """Packs short virtual nodes with pairwise disjoint request sets into groups
     that run as ONE many-row task: the members' KV is concatenated, their requests
     are concatenated, and each request attends only to its own member's tokens
@@ -427,39 +445,63 @@ def b200_group_short_nodes(vnodes, q_tile, small_tile, m, target_tokens):
     more than ``small_tile`` requests, or shares a request with it.  Groups
     with fewer than ``group_min_members`` members, or not more requests than
     ``small_tile``, are dissolved.  Result: the other virtual nodes in their
-    order, then groups and dissolved candidates in the order they were closed."""
+    order, then groups and dissolved candidates in the order they were closed.
+    ``direct`` (serving path): every candidate is one run of an existing row-id
+    table and a member's ``room`` - spare entries behind a tail that grows during
+    the burst - counts as part of its length."""
     if m.group_member_tokens <= 0:
         return vnodes
     tile = m.tile_tokens
     hard_cap = GROUP_MAX_TILES * tile
     cap = min(max(target_tokens // tile * tile, 4 * tile), hard_cap)
+    if direct:
+        # serving path: the groups are sized to fill twice what the other tasks leave of one round of resident CTAs
+        # (measured: their tiles are gathered row by row, and two shorter groups per slot hide that latency better
+        # than one long one; the average-based target overshoots when the shared nodes' tasks are short), up to 24 tiles
+        cand_tokens = other = 0
+        for vn in vnodes:
+            length = sum(e - b for b, e in vn.kv_ranges)
+            if len(vn.requests) <= small_tile and length + vn.room <= m.group_member_tokens:
+                cand_tokens += length + vn.room
+            else:
+                other += -(-length // vn.kv_split) * -(-len(vn.requests) // vn.q_tile)
+        round_ = max(int(m.num_sms * m.ctas_per_sm * m.waves) // max(num_kv_heads, 1), 1)
+        free_tasks = 2 * max(round_ - other, round_ // 4, 1)
+        hard_cap = GROUP_MAX_TILES_DIRECT * tile
+        cap = min(max(-(-(-(-cand_tokens // free_tasks)) // tile) * tile, 4 * tile), hard_cap)
     kept, tail = [], []
     cur, cur_reqs, cur_tokens, cur_n = [], set(), 0, 0
 
     def close():
         if len(cur) >= m.group_min_members and cur_n > small_tile:
-            ranges, row_ranges, start = [], [], 0
+            ranges, row_ranges, rooms, start = [], [], [], 0
             for vn, length in cur:
                 ranges.extend(vn.kv_ranges)
                 row_ranges.extend([(start, start + length)] * len(vn.requests))
-                start += length
+                rooms.append(vn.room)
+                start += length + vn.room
             tail.append(VirtualNode(ranges, np.concatenate([vn.requests for vn, _ in cur]), q_tile=q_tile,
-                                    kv_split=-(-start // tile) * tile, row_ranges=row_ranges))
+                                    kv_split=-(-start // tile) * tile, row_ranges=row_ranges,
+                                    member_room=rooms if direct else None))
         else:
             tail.extend(vn for vn, _ in cur)
 
     for vn in vnodes:
         length = sum(e - b for b, e in vn.kv_ranges)
+        span = length + vn.room
         n = len(vn.requests)
-        if n <= small_tile and length <= m.group_member_tokens:
-            if cur and (cur_n + n > q_tile or cur_tokens + length > hard_cap
-                        or (cur_tokens + length > cap and cur_n > small_tile)
+        if n <= small_tile and span <= m.group_member_tokens:
+            # (serving path: a group is closed once it has reached the cap, not before it would pass it, so that
+            # the groups number no more than the tasks they were sized for)
+            full = cur_tokens >= cap if direct else cur_tokens + span > cap
+            if cur and (cur_n + n > q_tile or cur_tokens + span > hard_cap
+                        or (full and cur_n > small_tile)
                         or any(int(r) in cur_reqs for r in vn.requests)):
                 close()
                 cur, cur_reqs, cur_tokens, cur_n = [], set(), 0, 0
             cur.append((vn, length))
             cur_reqs.update(int(r) for r in vn.requests)
-            cur_tokens += length
+            cur_tokens += span
             cur_n += n
         else:
             kept.append(vn)
@@ -504,6 +546,10 @@ def _native_tables(build, direct):
         if info.has_row_ranges:
             tabs["vnode_q_kv_ranges"] = np.empty((info.partial_rows, 2), dtype=np.int32)
             _lib.check(L.ft_plan_copy_row_ranges(handle, as32(tabs["vnode_q_kv_ranges"])))
+        tabs["aux_segments"] = np.empty((info.aux_segments, 4), dtype=np.int32)
+        tabs["aux_entries"] = int(info.aux_entries)
+        if info.aux_segments:
+            _lib.check(L.ft_plan_copy_aux_segments(handle, as32(tabs["aux_segments"])))
     finally:
         L.ft_plan_free(handle)
     if direct:
@@ -547,7 +593,7 @@ def plan_b200_native(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head
 
 
 def b200_tables_native_direct(tree, node_base, node_offset, extra, batch_size, num_qo_heads, num_kv_heads, head_dim,
-                              model):
+                              model, tail_room=-1):
     """The serving path's tables from the native splitter (``ft_plan_b200_build_direct``): what
     :func:`b200_virtual_nodes` + :func:`emit_tables` (``direct_offsets=True``, ordered by
     :func:`b200_task_order`) produce for a tree whose node i covers positions
@@ -567,8 +613,8 @@ def b200_tables_native_direct(tree, node_base, node_offset, extra, batch_size, n
     tabs, _assign, info = _native_tables(
         lambda L, out: L.ft_plan_b200_build_direct(as32(parent), as32(seqlen), len(tree), as64(req_offs), as32(req_ids),
                                                    as64(base), as64(offs), int(ex.shape[0]), as64(eb), as64(ee), as32(er),
-                                                   batch_size, num_qo_heads, num_kv_heads, head_dim, ctypes.byref(ms),
-                                                   out), direct=True)
+                                                   int(tail_room), batch_size, num_qo_heads, num_kv_heads, head_dim,
+                                                   ctypes.byref(ms), out), direct=True)
     return tabs, int(info.q_tile), int(info.small_tile), int(info.tile_tokens)
 
 
@@ -590,12 +636,15 @@ def b200_task_order(kv_len, q_len):
     return kv_len * 64 + np.minimum(q_len, 63)
 
 
-def b200_virtual_nodes(tree, num_qo_heads, num_kv_heads, head_dim, m, ranges_of, extra=()):
+def b200_virtual_nodes(tree, num_qo_heads, num_kv_heads, head_dim, m, ranges_of, extra=(), tail_room=-1):
     """Steps 1-3 of :func:`plan_b200` on any tree of node records (``parent``,
     ``seqlen``, ``num_children``, ``requests``).  ``ranges_of(assign, i)`` gives the
     KV row ranges of node i preceded by the ancestors it carries.  ``extra`` is a
     list of ``(ranges, requests)`` pairings outside the tree (per-request private
     tails) that take part in the byte budget and come last in emission order.
+    ``tail_room >= 0`` (serving path, head_dim 128, 16-bit K/V): short pairings are
+    then packed into groups (:func:`b200_group_short_nodes`, ``direct=True``), each
+    ``extra`` member followed by ``tail_room`` spare row ids.
     Returns (virtual nodes, assignments, request tile, small request tile, byte target)."""
     group = max(1, num_qo_heads // num_kv_heads)
     q_tile = max(1, m.rows_per_cta // group)
@@ -617,21 +666,24 @@ def b200_virtual_nodes(tree, num_qo_heads, num_kv_heads, head_dim, m, ranges_of,
         length = sum(e - b for b, e in ranges)
         if length <= 0:
             continue
-        specs.append((ranges, reqs, length))
+        specs.append((ranges, reqs, length, 0))
         total_stream += -(-len(reqs) // q_tile) * length * row_bytes
     for ranges, reqs in extra:
         length = sum(e - b for b, e in ranges)
         if length > 0 and len(reqs) > 0:
-            specs.append((ranges, list(reqs), length))
+            specs.append((ranges, list(reqs), length, max(tail_room, 0)))
             total_stream += -(-len(reqs) // q_tile) * length * row_bytes
     slots = m.num_sms * m.ctas_per_sm * m.waves
     target = max(total_stream * num_kv_heads / slots, m.min_chunk * row_bytes)
 
     vnodes = []
-    for ranges, reqs, length in specs:
+    for ranges, reqs, length, room in specs:
         want = int(round(length * row_bytes / target))
         n_chunks = max(1, min(want, -(-length // m.min_chunk)))
         chunk = -(-length // n_chunks)
         chunk = -(-chunk // m.tile_tokens) * m.tile_tokens
-        vnodes.append(VirtualNode(ranges, np.asarray(reqs, dtype=np.int32), q_tile=q_tile, kv_split=chunk))
+        vnodes.append(VirtualNode(ranges, np.asarray(reqs, dtype=np.int32), q_tile=q_tile, kv_split=chunk, room=room))
+    if tail_room >= 0 and head_dim == 128 and m.elem_bytes == 2:
+        vnodes = b200_group_short_nodes(vnodes, q_tile, small_tile, m, int(math.floor(target / row_bytes)), direct=True,
+                                        num_kv_heads=num_kv_heads)
     return vnodes, assign, q_tile, small_tile, target

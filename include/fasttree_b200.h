@@ -134,6 +134,16 @@ typedef struct ft_decode_args {
                                          off, fasttree_sglang_plugin_v0_2_13/plugin.py:209-211).  batch, the table
                                          pointers and num_partial_rows (the capacity of mid_o / mid_lse) stay
                                          host-side arguments. */
+  const int32_t* vnode_to_kv_entries_aux; /* NULL, or a second row-id table: a vnode whose vnode_to_kv_offs value has
+                                         bit 30 set (FT_KV_OFFSET_AUX) takes its row ids from this table at the
+                                         offset in the low 30 bits.  The serving path addresses tree nodes straight
+                                         through req_to_token (one run of positions per vnode) and keeps here the
+                                         concatenated row ids of private tails that run as one many-row vnode with
+                                         vnode_q_kv_ranges (ft_gather_kv_entries builds it; ft_bump_tails and
+                                         ft_refresh_tails extend it between the steps of a burst).  No counterpart in the reference, whose
+                                         serving plan has one few-row task per request tail
+                                         (fasttree_sglang_plugin_v0_2_13/schedule.py:212-232). */
+  int64_t kv_entries_aux_len;         /* readable entries of vnode_to_kv_entries_aux */
 } ft_decode_args;
 
 /* Library version (major*10000 + minor*100 + patch). */
@@ -197,6 +207,32 @@ int ft_decode_static_scratch(const ft_decode_args* args);
  * just generated joins each request's last private KV chunk.
  * Replaces prepare_for_fasttree_step (fasttree_sglang_plugin_v0_2_13/schedule.py:278-283). */
 int ft_bump_kv_lens(int32_t* vnode_to_kv_lens, const int32_t* last_vnodes, int32_t n, void* stream);
+
+#define FT_KV_OFFSET_AUX (1 << 30)
+
+/* Builds the auxiliary row-id table of a burst on the device: segment i copies seg_len[i] row ids from
+ * src_table[seg_src[i] ...] (the flat req_to_token table) to aux_table[seg_dst[i] ...] and fills the next
+ * seg_room[i] entries - room for the tokens the burst will generate - with the segment's first row id, a valid
+ * row that no query row attends to.  Segments that reach outside either table are skipped and flagged
+ * (FT_DEV_BAD_KV_INDEX).  All arrays are device arrays.  No counterpart in the reference. */
+int ft_gather_kv_entries(const int32_t* src_table, int64_t src_len, const int32_t* seg_src, const int32_t* seg_len,
+                         const int32_t* seg_dst, const int32_t* seg_room, int32_t n_segments, int32_t* aux_table,
+                         int64_t aux_len, void* stream);
+
+/* Between two steps of a burst, per request i < n, with tail_state[i] = {aux_pos, src_pos, index, room}:
+ *   aux_pos >= 0 (the tail is a member of a grouped vnode; aux_pos / src_pos are one past its last row id in the
+ *     auxiliary table / in req_to_token): the end of partial row `index` in vnode_q_kv_ranges moves up by one,
+ *     aux_pos and src_pos advance, room shrinks (room exhausted: nothing changes, FT_DEV_BAD_KV_INDEX is flagged);
+ *   aux_pos < 0 (the tail is a vnode of its own): vnode_to_kv_lens[index] += 1, as ft_bump_kv_lens does
+ *     (index -1: unused entry).
+ * Replaces prepare_for_fasttree_step (fasttree_sglang_plugin_v0_2_13/schedule.py:278-283) for plans with grouped tails. */
+int ft_bump_tails(int32_t* tail_state, int32_t n, int32_t* vnode_q_kv_ranges, int64_t num_partial_rows,
+                  int32_t* vnode_to_kv_lens, int32_t num_vnodes, void* stream);
+/* aux_table[aux_pos - 1] = src_table[src_pos - 1] for every grouped tail: the newest token of a request gets its
+ * KV-pool slot (and its req_to_token entry) only when the step's batch is prepared, after the plan or the bump, so
+ * the copy of that one row id is made at the start of the step's first attention call.  Idempotent. */
+int ft_refresh_tails(const int32_t* tail_state, int32_t n, const int32_t* src_table, int64_t src_len, int32_t* aux_table,
+                     int64_t aux_len, void* stream);
 
 /* Synchronises `stream`, copies the device status word of the current device
  * to *flags (bits of enum ft_device_flag) and clears it.  Kernels only ever
@@ -264,6 +300,8 @@ typedef struct ft_plan_info {
   int32_t tile_tokens;
   int32_t has_row_ranges; /* 1: the plan holds groups of short nodes and ft_plan_copy_row_ranges has a table to give */
   double target_bytes;  /* streamed bytes one task was sized for */
+  int64_t aux_entries;  /* serving plans with groups: entries of the auxiliary row-id table the vnode offsets assume */
+  int64_t aux_segments; /* ... and the number of segments ft_plan_copy_aux_segments reports */
 } ft_plan_info;
 
 /* Tree: n_nodes records in id order, node 0 the root, parents before children (parent[0] = -1); seqlen tokens per
@@ -277,12 +315,22 @@ int ft_plan_b200_build(const int32_t* parent, const int32_t* seqlen, int32_t n_n
  * flattened req_to_token): [node_base[i] + node_offset[top carried ancestor], node_base[i] + node_offset[i] +
  * seqlen[i]).  n_extra further pairings of one request with one run (each request's private tail) take part in
  * the byte budget and are emitted last.  No vnode_to_kv_entries table is built (ft_plan_info.kv_entries = 0);
- * vnode_to_kv_offs are positions in the existing table; req_to_vnode_entries still gets its 32 trailing -1. */
+ * vnode_to_kv_offs are positions in the existing table; req_to_vnode_entries still gets its 32 trailing -1.
+ * tail_room < 0: every vnode is one run, as above.  tail_room >= 0 (head_dim 128): short runs with few requests -
+ * above all the private tails, thousands of one-tile tasks in a large burst - may be packed into groups that run as
+ * ONE many-row vnode with per-row token ranges (ft_plan_copy_row_ranges; rows of plain vnodes get an open end there,
+ * which the kernels clip to the chunk).  A group's row ids are the concatenation of its members' runs, each tail
+ * followed by tail_room spare entries for the tokens the burst will add; they live in an auxiliary table
+ * (ft_decode_args.vnode_to_kv_entries_aux) that the caller fills on the device with ft_gather_kv_entries from the
+ * segment list of ft_plan_copy_aux_segments, and the group's vnode_to_kv_offs value is FT_KV_OFFSET_AUX + its
+ * position in that table. */
 int ft_plan_b200_build_direct(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, const int64_t* req_offs,
                               const int32_t* req_ids, const int64_t* node_base, const int64_t* node_offset,
                               int64_t n_extra, const int64_t* extra_begin, const int64_t* extra_end,
-                              const int32_t* extra_req, int32_t batch, int32_t num_qo_heads, int32_t num_kv_heads,
-                              int32_t head_dim, const ft_b200_model* model, ft_plan** out);
+                              const int32_t* extra_req, int32_t tail_room, int32_t batch, int32_t num_qo_heads,
+                              int32_t num_kv_heads, int32_t head_dim, const ft_b200_model* model, ft_plan** out);
+/* segments: int32 [ft_plan_info.aux_segments][4] = {source position, length, position in the auxiliary table, room} */
+int ft_plan_copy_aux_segments(const ft_plan* plan, int32_t* segments);
 int ft_plan_get_info(const ft_plan* plan, ft_plan_info* info);
 int ft_plan_copy_tables(const ft_plan* plan, int32_t* vnode_to_kv_entries, int32_t* vnode_to_kv_offs,
                         int32_t* vnode_to_kv_lens, int32_t* vnode_to_q_entries, int32_t* vnode_to_q_offs,

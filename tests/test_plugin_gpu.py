@@ -11,7 +11,7 @@ sglang_standin.install()
 
 import plugin_cases  # noqa: E402
 from fasttree_sglang_plugin_v0_2_13 import metadata, plugin, schedule  # noqa: E402
-from ft_b200 import lib  # noqa: E402
+from ft_b200 import engine, lib  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 
@@ -45,27 +45,54 @@ def test_serving_traffic_shapes_through_the_hook(name):
     run_burst(name, "b200", 2, torch.float16, steps=2)
 
 
+@pytest.mark.parametrize("name", ["system_4x128", "few_shot_8x16", "long_tail"])
+@pytest.mark.parametrize("grouped", [True, False], ids=["grouped", "one_task_per_tail"])
+def test_grouped_private_tails_through_the_hook(name, grouped):
+    """The plan packs the requests' private tails into many-row vnodes whose row ids are gathered into the
+    auxiliary table once per burst; every step extends each member by the token just decoded (its row id arrives
+    in the step's first attention call, its partial row's range grows in the bump).  Four steps against fp32
+    attention, with and without grouping; the grouped plan has far fewer tasks."""
+    md = run_burst(name, "b200", 2, torch.float16, steps=4, group_tails=grouped)
+    assert (md.num_grouped_tails > 0) == grouped
+    if grouped:
+        plain = metadata.FastTreeMetadata(md.num_qo_heads, md.num_kv_heads, 128, "cpu", max_vnodes=4096,
+                                          max_vnode_to_q_entries=8192, max_batch_size=512, group_tails=False)
+        batch, _rows, _, _ = plugin_cases.build(name, extra_prompt=2, steps=4)
+        schedule.prepare_for_fasttree_meta(batch, plain)
+        assert md.num_vnodes < plain.num_vnodes
+
+
 @pytest.mark.parametrize("name", ["long_tail", "system_4x128", "small_g4"])
 def test_decode_burst_in_graph_safe_mode(name):
     """The same bursts with the phase split read on the device and the persistent stage-1 kernel behind the hook."""
     run_burst(name, "b200", 2, torch.float16, steps=3, graph_safe=True)
 
 
-def run_burst(name, planner, extra, dtype, steps, graph_safe=False):
+def run_burst(name, planner, extra, dtype, steps, graph_safe=False, group_tails=True):
     from sglang.srt.layers.radix_attention import RadixAttention
     from sglang.srt.model_executor.forward_batch_info import InputMetadata
 
     batch, rows, hq, hkv = plugin_cases.build(name, device="cuda", dtype=dtype, extra_prompt=extra, steps=steps)
     d = 128
     md = metadata.FastTreeMetadata(hq, hkv, d, "cuda", max_vnodes=4096, max_vnode_to_q_entries=8192,
-                                   max_batch_size=512, planner=planner, graph_safe=graph_safe)
+                                   max_batch_size=512, planner=planner, graph_safe=graph_safe, group_tails=group_tails,
+                                   group_tails_min_load=0.0)     # groups whenever the tails allow, whatever the burst's size
     plugin._replace_fwd_batch_info()
     plugin._replace_radix_attn()
     attn = RadixAttention(hq, d, 1.0 / d ** 0.5, hkv, 0)
     g = torch.Generator(device="cuda").manual_seed(11)
+    # As in SGLang, a token's KV-pool slot enters req_to_token only when its step's batch is prepared - after the
+    # plan, and after the bump between steps: entries of tokens not yet decoded hold -1 until then.
+    r2t = batch.req_to_token_pool.req_to_token
+    pool_rows = batch.req_pool_indices.tolist()
+    first_new = [len(req.origin_input_ids) + len(req.output_ids) for req in batch.reqs]
+    for r, row in enumerate(pool_rows):
+        r2t[row, first_new[r]:] = -1
     schedule.prepare_for_fasttree_meta(batch, md)
     bsz = len(batch.reqs)
     for step in range(steps):
+        for r, row in enumerate(pool_rows):
+            r2t[row, first_new[r] + step] = rows[r][first_new[r] + step]
         q = (torch.randn(bsz, hq * d, generator=g, device="cuda") * 0.5).to(dtype)
         k_new = torch.randn(bsz, hkv * d, generator=g, device="cuda").to(dtype)
         v_new = torch.randn(bsz, hkv * d, generator=g, device="cuda").to(dtype)
@@ -85,6 +112,7 @@ def run_burst(name, planner, extra, dtype, steps, graph_safe=False):
             batch.out_cache_loc = torch.stack([rows[r][len(req.origin_input_ids) + len(req.output_ids)]
                                                for r, req in enumerate(batch.reqs)]).cuda()
             schedule.prepare_for_fasttree_step(batch, md)
+    return md
 
 
 def test_captured_decode_step_survives_a_replan():
@@ -114,11 +142,15 @@ def test_captured_decode_step_survives_a_replan():
     scale = 1.0 / d ** 0.5
 
     def call():
+        # what the attention hook does for the first layer of a step: the grouped tails take their newest row id,
+        # then the decode call with the range table and the auxiliary row-id table of the plan
+        engine.refresh_tails(md.tail_state, md.max_batch_size, r2t, md.kv_entries_aux)
         attn_kernels.fasttree_decode(q, k_buf, v_buf, o, r2t, md.vnode_to_kv_offs, md.vnode_to_kv_lens,
                                      md.vnode_to_q_entries, md.vnode_to_q_offs, md.vnode_to_q_lens,
                                      md.req_to_vnode_entries, md.req_to_vnode_offs, md.req_to_vnode_lens,
                                      md.mid_o, md.mid_lse, md.phase_node_nums, md.phase_node_offsets,
-                                     md.phase_q_tile_sizes, md.phase_kv_tile_sizes, scale, phase_info=md.phase_info_dev)
+                                     md.phase_q_tile_sizes, md.phase_kv_tile_sizes, scale, phase_info=md.phase_info_dev,
+                                     row_ranges=md.vnode_q_kv_ranges, kv_entries_aux=md.kv_entries_aux)
 
     schedule.prepare_for_fasttree_meta(base, md)
     side = torch.cuda.Stream()
