@@ -1,14 +1,16 @@
 // Stage 1 for fp32 storage (head_dim 64 or 128): exact fp32 arithmetic on the
 // CUDA cores, tiled through shared memory.
 //
-// One CTA (4 warps) per (vnode, kv head, block of 16 packed query rows).  The KV
+// One CTA (8 warps) per (vnode, kv head, block of 16 packed query rows).  The KV
 // chunk is walked 32 tokens at a time: the tile's K and V rows are gathered by
 // row id with 16-byte loads, one tile ahead of the arithmetic (the loads of tile
 // t+1 are in flight, in registers, while tile t is computed from shared memory).
-//   S[16 x 32]   lane = token, warp w owns rows w, w+4, w+8, w+12: 4 dot products of
-//                length head_dim per thread, Q broadcast from shared memory
+//   S[16 x 32]   lane = token, warp w owns rows w and w+8: 2 dot products of length
+//                head_dim per thread, Q broadcast from shared memory (two warps per
+//                scheduler: the arithmetic of a tile is one dependent chain per warp,
+//                and with four warps of four rows a tile took twice as long)
 //   softmax      a row's 32 scores sit in the 32 lanes of one warp: shuffles
-//   O[16 x D]    thread owns columns lane, lane+32, ... of its warp's 4 rows; the
+//   O[16 x D]    thread owns columns lane, lane+32, ... of its warp's 2 rows; the
 //                probabilities are broadcast by shuffle, V read conflict-free
 // Same conventions as the other stage-1 kernels (kernel_bench/fasttree.py:360-413):
 // scores scaled after the dot product, normalised partial output, lse = log(sum) + max;
@@ -21,7 +23,8 @@ namespace ft {
 
 template <int D>
 struct F32Cfg {
-  static constexpr int ROWS = 16, TILE = 32, THREADS = 128;
+  static constexpr int ROWS = 16, TILE = 32, THREADS = 256;
+  static constexpr int WARPS = THREADS / 32, RPW = ROWS / WARPS;  // rows per warp
   static constexpr int KSTRIDE = D + 1;              // floats between K rows: lane = token reads are conflict-free
   static constexpr int Q_FLOATS = ROWS * D, K_FLOATS = TILE * KSTRIDE, V_FLOATS = TILE * D;
   static constexpr int K_OFF = ((Q_FLOATS + 3) / 4) * 4, V_OFF = ((K_OFF + K_FLOATS + 3) / 4) * 4;
@@ -31,7 +34,7 @@ struct F32Cfg {
 };
 
 template <int D>
-__global__ void __launch_bounds__(128) stage1_f32_kernel(Stage1Params p) {
+__global__ void __launch_bounds__(256) stage1_f32_kernel(Stage1Params p) {
   using C = F32Cfg<D>;
   allow_dependent_launch();
   wait_for_prior_grid();  // nothing of the preceding kernel's is read or overwritten before this
@@ -74,18 +77,19 @@ __global__ void __launch_bounds__(128) stage1_f32_kernel(Stage1Params p) {
     *reinterpret_cast<float4*>(q_s + r * D + 4 * c4) = x;
   }
 
-  // per-thread state: rows warp + 4 i
-  float m_run[4], l_run[4], acc[4][D / 32];
-  int r_lo[4], r_hi[4];
+  // per-thread state: rows warp + WARPS * i
+  constexpr int RPW = C::RPW, NW = C::WARPS;
+  float m_run[RPW], l_run[RPW], acc[RPW][D / 32];
+  int r_lo[RPW], r_hi[RPW];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < RPW; ++i) {
     m_run[i] = -INFINITY;
     l_run[i] = 0.f;
 #pragma unroll
     for (int j = 0; j < D / 32; ++j) acc[i][j] = 0.f;
     r_lo[i] = 0;
     r_hi[i] = kv_len;
-    const int r = warp + 4 * i;
+    const int r = warp + NW * i;
     if (p.q_ranges != nullptr && r < rows) {
       const int64_t part = (int64_t)q_off + (row0 + r) / G;
       if (part >= 0 && part < p.num_partial_rows) {
@@ -141,15 +145,17 @@ __global__ void __launch_bounds__(128) stage1_f32_kernel(Stage1Params p) {
     __syncthreads();
     if (t + 1 < ntiles) fetch(t + 1);  // in flight during the arithmetic below
 
-    // ---- S = Q K^T for this thread's 4 rows and its token
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    // ---- S = Q K^T for this thread's rows and its token
+    float s[RPW];
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) s[i] = 0.f;
     const float* kr = k_s + lane * C::KSTRIDE;
 #pragma unroll 4
     for (int d4 = 0; d4 < C::C4; ++d4) {
       const float k0 = kr[4 * d4], k1 = kr[4 * d4 + 1], k2 = kr[4 * d4 + 2], k3 = kr[4 * d4 + 3];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float4 qv = *reinterpret_cast<const float4*>(q_s + (warp + 4 * i) * D + 4 * d4);
+      for (int i = 0; i < RPW; ++i) {
+        const float4 qv = *reinterpret_cast<const float4*>(q_s + (warp + NW * i) * D + 4 * d4);
         s[i] = fmaf(qv.x, k0, s[i]);
         s[i] = fmaf(qv.y, k1, s[i]);
         s[i] = fmaf(qv.z, k2, s[i]);
@@ -158,9 +164,9 @@ __global__ void __launch_bounds__(128) stage1_f32_kernel(Stage1Params p) {
     }
     // ---- online softmax per row (32 tokens = 32 lanes)
     const int pos = t * C::TILE + lane;
-    float pr[4];
+    float pr[RPW];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < RPW; ++i) {
       const bool seen = pos >= r_lo[i] && pos < r_hi[i];
       const float x = seen ? s[i] * p.sm_scale : -INFINITY;
       const float m_new = fmaxf(m_run[i], warp_max(x));
@@ -182,7 +188,7 @@ __global__ void __launch_bounds__(128) stage1_f32_kernel(Stage1Params p) {
 #pragma unroll
       for (int j = 0; j < D / 32; ++j) vv[j] = v_s[tok * D + lane + 32 * j];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < RPW; ++i) {
         const float w = __shfl_sync(0xffffffffu, pr[i], tok);
 #pragma unroll
         for (int j = 0; j < D / 32; ++j) acc[i][j] = fmaf(w, vv[j], acc[i][j]);
@@ -192,8 +198,8 @@ __global__ void __launch_bounds__(128) stage1_f32_kernel(Stage1Params p) {
 
   // ---- normalise and write the partial rows
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int r = warp + 4 * i;
+  for (int i = 0; i < RPW; ++i) {
+    const int r = warp + NW * i;
     if (r >= rows) continue;
     const int prow = row0 + r, slot = prow / G, gg = prow - slot * G;
     const int64_t part = (int64_t)q_off + slot;
