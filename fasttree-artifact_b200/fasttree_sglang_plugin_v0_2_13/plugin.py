@@ -119,6 +119,9 @@ def _replace_tp_server_fwd(enable_fasttree=True, annotate_breakdown=False):
         # one schedule per burst of decode steps, patched in place between the steps
         burst = global_config.num_continue_decode_steps
         if enable_fasttree:
+            # grouped tails reserve room for the tokens of this burst: never less than its number of steps
+            md = self.fasttree_metadata
+            md.tail_room = max(getattr(md, "tail_room", 0), burst)
             fasttree_schedule.prepare_for_fasttree_meta(self.running_batch, self.fasttree_metadata)
             planned_for = len(self.running_batch.reqs)
         for step in range(burst):
