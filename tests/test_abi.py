@@ -51,3 +51,12 @@ def test_null_and_invalid_arguments_return_error_codes():
         lib.check(-2)
     assert handle.ft_bump_kv_lens(None, None, -1, None) == -1
     assert handle.ft_bump_kv_lens(None, None, 0, None) == 0
+    # the grouped-tails calls: nothing to do is fine, missing tables and negative sizes are refused before any launch
+    assert handle.ft_gather_kv_entries(None, 0, None, None, None, None, 0, None, 0, None) == 0
+    assert handle.ft_gather_kv_entries(None, 0, None, None, None, None, 3, None, 0, None) == -1
+    assert handle.ft_gather_kv_entries(None, -1, None, None, None, None, 0, None, 0, None) == -1
+    assert handle.ft_bump_tails(None, 0, None, 0, None, 0, None) == 0
+    assert handle.ft_bump_tails(None, 2, None, 0, None, 0, None) == -1
+    assert handle.ft_refresh_tails(None, 0, None, 0, None, 0, None) == 0
+    assert handle.ft_refresh_tails(None, 2, None, 0, None, 0, None) == -1
+    assert handle.ft_refresh_tails(None, 0, None, -5, None, 0, None) == -1
