@@ -26,12 +26,12 @@ TRAFFIC_SHAPES = {
 }
 
 
-def build(name, device="cpu", dtype=torch.float16, extra_prompt=0, head_dim=128, steps=1):
+def build(name, device="cpu", dtype=torch.float16, extra_prompt=0, head_dim=128, steps=1, slot_layout="scattered"):
     sizes, lens, gen, hq, hkv = (CASES.get(name) or TRAFFIC_SHAPES[name])
     nodes = ref_inputs.layered_tree(sizes, lens)
     batch_size = sum(1 for n in nodes if n.num_children == 0)
     generated = [gen[i % len(gen)] for i in range(batch_size)]
     total = sum(n.seqlen for n in nodes) + sum(g + steps + extra_prompt for g in generated)
     batch, rows = sglang_standin.build_batch(nodes, extra_prompt, generated, total + 64, hkv, head_dim, dtype,
-                                             device, seed=len(name) * 7, steps=steps)
+                                             device, seed=len(name) * 7, steps=steps, slot_layout=slot_layout)
     return batch, rows, hq, hkv

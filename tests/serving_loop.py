@@ -129,7 +129,8 @@ def run_shape(name, args, rank, world, dev):
     total_steps = args.steps * args.bursts * (2 if args.mode == "both" else 1) + 2
     pool = sum(n.seqlen for n in nodes) + sum(g + total_steps + args.extra_prompt for g in generated) + 64
     batch, rows = sglang_standin.build_batch(nodes, args.extra_prompt, generated, pool, hkv_l, HEAD_DIM, dtype, dev,
-                                             seed=len(name) * 7, num_layers=1, steps=total_steps)
+                                             seed=len(name) * 7, num_layers=1, steps=total_steps,
+                                             slot_layout=args.pool_layout)
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     kv = batch.token_to_kv_pool
     for _ in range(1, args.layers):      # the remaining layers' pools, drawn on the device
@@ -141,7 +142,8 @@ def run_shape(name, args, rank, world, dev):
     plugin._replace_radix_attn()
     from sglang.srt.model_executor.forward_batch_info import InputMetadata
     blocks = [Block(i, hq_l, hkv_l, inter_l, dtype, dev, g, world) for i in range(args.layers)]
-    out = {"shape": name, "tp": world, "requests": bsz, "context_tokens": context_tokens, "layers": args.layers,
+    out = {"shape": name, "tp": world, "pool_layout": args.pool_layout, "requests": bsz, "context_tokens": context_tokens,
+           "layers": args.layers,
            "dtype": args.dtype, "steps_per_burst": args.steps, "bursts": args.bursts}
     modes = ["eager", "graph"] if args.mode == "both" else [args.mode]
     out_loc = batch.out_cache_loc.clone()             # static: the graph reads it, the loop rewrites it
@@ -259,6 +261,9 @@ def main(argv=None):
     ap.add_argument("--bursts", type=int, default=2)
     ap.add_argument("--extra-prompt", type=int, default=2, help="private prompt tokens per request (not in the radix cache)")
     ap.add_argument("--mode", default="both", choices=["eager", "graph", "both"])
+    ap.add_argument("--pool-layout", default="scattered", choices=["scattered", "prefill"],
+                    help="KV-pool slots: a random permutation (every row gathered on its own), or what a serving process "
+                         "leaves behind (radix nodes in consecutive slots, generated tokens interleaved across requests)")
     ap.add_argument("--dtype", default="fp16", choices=["fp16", "bf16"])
     args = ap.parse_args(argv)
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -225,13 +225,17 @@ def install():
 
 
 def build_batch(tree_nodes, extra_prompt, generated, pool_size, num_kv_heads, head_dim, dtype, device, seed,
-                num_layers=1, max_context_len=None, steps=1):
+                num_layers=1, max_context_len=None, steps=1, slot_layout="scattered"):
     """A decode batch whose prompts share prefixes the way ``tree_nodes`` (a list of
     oracle/product tree nodes: parent, seqlen, num_children) does.  Each leaf is one
     request: prompt = tokens of its root->leaf path + ``extra_prompt`` private tokens
     that are NOT in the radix cache; ``generated[r]`` tokens already generated;
     pool slots are reserved for ``steps`` decode steps.
-    KV pool slots are a random permutation.  Returns (batch, token lists per request)."""
+    ``slot_layout``: "scattered" - KV pool slots are a random permutation, the hardest case for the kernels'
+    loaders (every row is fetched on its own); "prefill" - what a serving process produces: the tokens of a
+    radix node and of a private prompt tail sit in consecutive slots (one prefill wrote them), generated tokens
+    are interleaved across the requests (every decode step allocates one slot per request).
+    Returns (batch, token lists per request)."""
     g = torch.Generator().manual_seed(seed)
     node_tokens, next_tok = [], 1000
     for nd in tree_nodes:
@@ -245,7 +249,12 @@ def build_batch(tree_nodes, extra_prompt, generated, pool_size, num_kv_heads, he
                 chain.append(cur)
                 cur = tree_nodes[cur].parent
             paths.append(chain[::-1])
-    perm = torch.randperm(pool_size, generator=g).to(torch.int32)
+    if slot_layout == "scattered":
+        perm = torch.randperm(pool_size, generator=g).to(torch.int32)
+    elif slot_layout == "prefill":
+        perm = torch.arange(pool_size, dtype=torch.int32)
+    else:
+        raise ValueError("slot_layout must be 'scattered' or 'prefill'")
     used = 0
     node_slots = []
     for nd in tree_nodes:
@@ -253,13 +262,28 @@ def build_batch(tree_nodes, extra_prompt, generated, pool_size, num_kv_heads, he
         used += nd.seqlen
     cache = RadixCache()
     reqs, rows = [], []
+    prompt_tail = []
+    if slot_layout == "prefill":        # private prompt tails first, then one slot per request and decode step
+        for r in range(len(paths)):
+            prompt_tail.append(perm[used:used + extra_prompt])
+            used += extra_prompt
+        # step-major numbering: step i hands one slot to every request that still decodes at step i
+        decode_slots_of = [[] for _ in paths]
+        for i in range(max(generated, default=0) + steps):
+            for r in range(len(paths)):
+                if i < generated[r] + steps:
+                    decode_slots_of[r].append(used)
+                    used += 1
     for r, chain in enumerate(paths):
         shared = [t for n in chain for t in node_tokens[n]]
         shared_slots = torch.cat([node_slots[n] for n in chain]) if chain else perm[:0]
         cache.insert(shared, shared_slots)
         n_priv = extra_prompt + generated[r] + steps       # private prompt tail + generated + the tokens being decoded
-        priv_slots = perm[used:used + n_priv]
-        used += n_priv
+        if slot_layout == "prefill":
+            priv_slots = torch.cat([prompt_tail[r], perm[torch.tensor(decode_slots_of[r], dtype=torch.long)]])
+        else:
+            priv_slots = perm[used:used + n_priv]
+            used += n_priv
         prompt = shared + list(range(next_tok, next_tok + extra_prompt))
         next_tok += extra_prompt
         outs = list(range(next_tok, next_tok + generated[r]))

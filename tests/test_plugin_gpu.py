@@ -40,9 +40,12 @@ def test_decode_burst_through_the_hook(name, planner, extra, dtype):
 
 
 @pytest.mark.parametrize("name", sorted(plugin_cases.TRAFFIC_SHAPES))
-def test_serving_traffic_shapes_through_the_hook(name):
-    """The tree shapes of the reference's four serving benchmarks (synthetic token counts), two decode steps."""
-    run_burst(name, "b200", 2, torch.float16, steps=2)
+@pytest.mark.parametrize("slot_layout", ["scattered", "prefill"])
+def test_serving_traffic_shapes_through_the_hook(name, slot_layout):
+    """The tree shapes of the reference's four serving benchmarks (synthetic token counts), two decode steps, on
+    a pool whose slots are a random permutation (every row gathered) and on one laid out as a serving process
+    leaves it (radix nodes in consecutive slots: tiled copies; generated tokens interleaved across requests)."""
+    run_burst(name, "b200", 2, torch.float16, steps=2, slot_layout=slot_layout)
 
 
 @pytest.mark.parametrize("name", ["system_4x128", "few_shot_8x16", "long_tail"])
@@ -68,11 +71,12 @@ def test_decode_burst_in_graph_safe_mode(name):
     run_burst(name, "b200", 2, torch.float16, steps=3, graph_safe=True)
 
 
-def run_burst(name, planner, extra, dtype, steps, graph_safe=False, group_tails=True):
+def run_burst(name, planner, extra, dtype, steps, graph_safe=False, group_tails=True, slot_layout="scattered"):
     from sglang.srt.layers.radix_attention import RadixAttention
     from sglang.srt.model_executor.forward_batch_info import InputMetadata
 
-    batch, rows, hq, hkv = plugin_cases.build(name, device="cuda", dtype=dtype, extra_prompt=extra, steps=steps)
+    batch, rows, hq, hkv = plugin_cases.build(name, device="cuda", dtype=dtype, extra_prompt=extra, steps=steps,
+                                              slot_layout=slot_layout)
     d = 128
     md = metadata.FastTreeMetadata(hq, hkv, d, "cuda", max_vnodes=4096, max_vnode_to_q_entries=8192,
                                    max_batch_size=512, planner=planner, graph_safe=graph_safe, group_tails=group_tails,
