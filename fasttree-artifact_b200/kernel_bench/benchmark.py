@@ -74,7 +74,8 @@ def main(args):
     params.set_planner(args.planner)
 
     tree_info = retrive_from_file(args.load_file_path)
-    want_padded = args.choice in ("flash_attn", "all")
+    want_deft = args.choice in ("DeFT", "all") and bool(args.deft_module)
+    want_padded = args.choice in ("flash_attn", "all") or want_deft
     Q, K_cache, V_cache, cache_seqlens, K_tree, V_tree, KV_ptrs = qkv_preparation(
         tree_info, args.num_qo_heads, args.num_kv_heads, args.head_dim, "cuda", dtype, padded_cache=want_padded)
     batch_size = Q.shape[0]
@@ -139,9 +140,34 @@ def main(args):
         except Exception as exc:          # optional baseline: not installed, or no kernel for this GPU / shape
             print(f"cascade skipped ({type(exc).__name__}: {str(exc)[:120]})")
 
-    for name in ("sglang_triton", "DeFT"):
-        if args.choice in (name, "all"):
-            print(f"{name} skipped (baseline kernels are not part of this build)")
+    # DeFT: the reference ships its own Triton implementation of that baseline (kernel_bench/DeFT.py:57-573).  It is
+    # not part of this build; --deft_module points at that file in a checkout of the reference and it is driven
+    # exactly as the reference's benchmark drives it (kernel_bench/benchmark.py:181-211: subtrees of 128 tokens,
+    # 64-bit masks, the phase-0 tile sizes, the padded per-request cache).
+    out_deft = None
+    if args.choice in ("DeFT", "all"):
+        if not args.deft_module:
+            print("DeFT skipped (pass --deft_module <reference checkout>/kernel_bench/DeFT.py to time it)")
+        else:
+            try:
+                import importlib.util
+                spec = importlib.util.spec_from_file_location("reference_deft", args.deft_module)
+                deft = importlib.util.module_from_spec(spec)
+                spec.loader.exec_module(deft)      # imports kv_tree_simple: this package's, same record type
+                mask_len = 64
+                aux = deft.DeFT_preparation(tree_info, K_cache, 128, mask_len, args.num_qo_heads, args.head_dim)
+                o_deft = torch.empty(batch_size, args.num_qo_heads, args.head_dim, device="cuda", dtype=dtype)
+                kf, vf = (t.view(-1, t.shape[-2], t.shape[-1]) for t in (K_cache, V_cache))
+
+                def call_deft():
+                    deft.DeFT_decode(Q, kf, vf, o_deft, *aux, tsq[0], tsk[0], 1.0 / args.head_dim ** 0.5, mask_len)
+                    return o_deft
+
+                out_deft = run_and_bench(call_deft, "DeFT attn").cpu()
+            except Exception as exc:    # an optional yard-stick: never the reason the run fails
+                print(f"DeFT skipped ({type(exc).__name__}: {str(exc)[:160]})")
+    if args.choice in ("sglang_triton", "all"):
+        print("sglang_triton skipped (baseline kernels are not part of this build)")
 
     if out_flash is not None and out_tree is not None:
         ok = torch.allclose(out_flash, out_tree, rtol=1e-2, atol=1e-2)
@@ -152,6 +178,9 @@ def main(args):
     if out_cascade is not None and out_tree is not None:
         ok = torch.allclose(out_cascade, out_tree, rtol=1e-2, atol=1e-2)
         print("fasttree vs cascade Check passed!" if ok else "fasttree vs cascade Check failed!")
+    if out_deft is not None and out_tree is not None:
+        ok = torch.allclose(out_deft, out_tree, rtol=1e-2, atol=1e-2)
+        print("fasttree vs DeFT Check passed!" if ok else "fasttree vs DeFT Check failed!")
 
 
 if __name__ == "__main__":
@@ -170,6 +199,8 @@ if __name__ == "__main__":
     ap.add_argument("--num_kv_heads", type=int, default=32)
     ap.add_argument("--head_dim", type=int, default=128)
     ap.add_argument("--signature", type=str, default=None)
+    ap.add_argument("--deft_module", type=str, default=None,
+                    help="path of kernel_bench/DeFT.py in a checkout of the reference: times its DeFT baseline too")
     ap.add_argument("--choice", type=str, default="all",
                     choices=["flash_attn", "fasttree", "sglang_triton", "sglang_flashinfer", "cascade", "DeFT", "all"])
     ap.add_argument("--profile", action="store_true", default=False)

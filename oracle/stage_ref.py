@@ -9,6 +9,7 @@ leg can import them.  This script copies
     kernel_bench/fasttree.py          planner + Triton stage-1 / stage-2 kernels
     kernel_bench/kv_tree_simple.py    tree node record and file reader
     kernel_bench/tree_generation.py   layered tree generator / writer
+    kernel_bench/DeFT.py              the reference's Triton DeFT baseline (timed by the benchmark CLI's GPU test)
 
 from a reference checkout into ``oracle/_ref/kernel_bench/``.  That directory
 is git-ignored (the reference's sources are never committed here) and is not
@@ -32,7 +33,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
-FILES = ["kernel_bench/fasttree.py", "kernel_bench/kv_tree_simple.py", "kernel_bench/tree_generation.py"]
+FILES = ["kernel_bench/fasttree.py", "kernel_bench/kv_tree_simple.py", "kernel_bench/tree_generation.py",
+         "kernel_bench/DeFT.py"]
 
 
 def stage(reference_dir, dest=DEST, quiet=False):

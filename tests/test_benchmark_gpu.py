@@ -37,14 +37,17 @@ def test_benchmark_cli_with_the_optional_baselines(tmp_path):
     tree = tmp_path / "tree.txt"
     subprocess.run([sys.executable, os.path.join(KB, "tree_generation.py"), "-n", "1,4,16", "-l", "256,64,32",
                     "-o", str(tree)], check=True)
-    res = subprocess.run(
-        [sys.executable, os.path.join(KB, "benchmark.py"), "--load_file_path", str(tree), "--num_qo_heads", "32",
-         "--num_kv_heads", "8", "--q_tile_size_per_phase", "16,4", "--choice", "all"],
-        cwd=KB, capture_output=True, text=True, timeout=900)
+    cmd = [sys.executable, os.path.join(KB, "benchmark.py"), "--load_file_path", str(tree), "--num_qo_heads", "32",
+           "--num_kv_heads", "8", "--q_tile_size_per_phase", "16,4", "--choice", "all"]
+    deft = os.path.join(ROOT, "oracle", "_ref", "kernel_bench", "DeFT.py")     # staged from a reference checkout, if any
+    if os.path.isfile(deft):
+        cmd += ["--deft_module", deft]
+    res = subprocess.run(cmd, cwd=KB, capture_output=True, text=True, timeout=900)
     assert res.returncode == 0, res.stderr[-2000:]
     assert "Check failed" not in res.stdout, res.stdout
     assert "fasttree attn time:" in res.stdout
-    for name, verdict in (("flashinfer cascade time:", "fasttree vs cascade Check passed!"),
+    for name, verdict in (("DeFT attn time:", "fasttree vs DeFT Check passed!"),
+                          ("flashinfer cascade time:", "fasttree vs cascade Check passed!"),
                           ("sglang flashinfer time:", "fasttree vs flashinfer Check passed!"),
                           ("flash attn time:", "fasttree attn Check passed!")):
         if name in res.stdout:
