@@ -148,6 +148,42 @@ def test_edge_shapes_against_oracle(spec, dtype):
             assert (run.mid_o.cpu() - mid_o).abs().max().item() <= tol
 
 
+@pytest.mark.parametrize("before", ["memcpy", "memset", "kernel", "nothing"])
+def test_decode_captured_behind_any_kind_of_node(before):
+    """Stage 1 is launched with permission to be scheduled before the preceding kernel has drained (programmatic
+    dependent launch).  Captured in a CUDA graph right behind a copy node, a memset node, an ordinary kernel that
+    produces the query, or nothing at all, the replayed step must still see that node's result."""
+    c = adhoc([1, 4, 16], [300, 64, 40], 32, 8, 128, torch.float16, seed=21, q_scale=0.5)
+    scale = 1.0 / 128 ** 0.5
+    truth, _ = ref_attention.per_leaf_attention(c["nodes"], c["ptrs"], c["q"], c["k"], c["v"], scale)
+    run = gpu_utils.EngineRun(c["nodes"], c["ptrs"], c["batch"], c["q"], c["k"], c["v"], 32, 8, 128, c["tsq"])
+    run.decode()
+    q_src = run.q.clone()
+    half = (run.q.float() * 0.5).to(run.q.dtype)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            if before == "memcpy":
+                run.q.copy_(q_src)
+            elif before == "memset":
+                run.o.zero_()
+            elif before == "kernel":
+                torch.add(half, half, out=run.q)          # the query is produced by the kernel right before stage 1
+            engine.decode(run.q, run.k, run.v, run.o, *run.aux, run.tiles[0], run.tiles[1], run.scale)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        run.q.fill_(float("nan") if before in ("memcpy", "kernel") else 0.0)
+        if before not in ("memcpy", "kernel"):
+            run.q.copy_(q_src)
+        run.o.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert lib.read_device_status() == 0
+        assert (run.o.float().cpu() - truth).abs().max().item() <= ATOL16
+
+
 @pytest.mark.parametrize("spec", [t for t in EDGE_TREES if t[0] in ([1, 40], [1, 4, 64], [1, 3, 24])],
                          ids=lambda s: "n%s" % "-".join(map(str, s[0])))
 def test_short_nodes_run_as_groups_with_row_ranges(spec):
