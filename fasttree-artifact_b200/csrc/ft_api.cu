@@ -695,6 +695,9 @@ namespace {
 // and completion hand-shake dominate at that size.
 __global__ void __launch_bounds__(256) host_to_device_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, size_t n16,
                                                              unsigned char* dst_tail, const unsigned char* src_tail, int tail) {
+  // stage 1 may set itself up (barriers, tensor memory) while the query crosses PCIe; it waits for this kernel's
+  // completion before it reads anything
+  ft::allow_dependent_launch();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n16) dst[i] = src[i];
   if (i < (size_t)tail) dst_tail[i] = src_tail[i];
