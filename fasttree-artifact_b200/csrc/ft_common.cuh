@@ -51,8 +51,16 @@ __device__ __forceinline__ unsigned long long timeline_now() {
 #define FT_TL_DETAIL_MARK(i) do { } while (0)
 #define FT_TL_COARSE_MARK(i) FT_TL_MARK(i)
 #endif
+// -DFT_TL_LOADERS hands the per-tile mark slots of the softmax to the loaders and the MMA warp instead (tile n: K issue
+// start / end = 5 / 6, V issue start / end = 7 / 11, K and V seen by the MMA warp = 1 / 4).
+#ifdef FT_TL_LOADERS
+#define FT_TL_SOFTMAX_MARK(i) do { } while (0)
+#else
+#define FT_TL_SOFTMAX_MARK(i) do { if ((i) == 5 || (i) == 6 || (i) == 7) { FT_TL_DETAIL_MARK(i); } else { FT_TL_MARK(i); } } while (0)
+#endif
 #else
 #define FT_TL_MARK(i) do { } while (0)
+#define FT_TL_SOFTMAX_MARK(i) do { } while (0)
 #define FT_TL_DETAIL_MARK(i) do { } while (0)
 #define FT_TL_COARSE_MARK(i) do { } while (0)
 #define FT_TL_TILE 5

@@ -36,6 +36,11 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool v
     asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};\n" ::"r"(dst), "r"(0) : "memory");
   }
 }
+// the same without a branch: an invalid row reads nothing (source size 0) and the copy engine writes 16 zero bytes,
+// so a gather loop stays one straight instruction stream and the zeros need no proxy fence
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool valid) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(valid ? 16 : 0) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {

@@ -337,7 +337,8 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
         const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32-lane quadrant
         float m_used = -INFINITY, l_run = 0.f;
         // the chunk tokens [r_lo, r_hi) this thread's row attends to: the whole chunk unless the plan narrows it
-        int r_lo = 0, r_hi = kv_len;
+        // (a row past the end of the task attends to nothing: its results are never stored)
+        int r_lo = 0, r_hi = row0 + tid < rows ? kv_len : 0;
         if (p.q_ranges != nullptr && row0 + tid < rows) {
           const int64_t part = (int64_t)q_off + (row0 + tid) / G;
           if (part >= 0 && part < p.num_partial_rows) {
@@ -345,6 +346,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
             r_hi = min(p.q_ranges[2 * part + 1], kv_len);
           }
         }
+        const bool warp_has_rows = row0 + warp * 32 < rows;
         for (int j = 0; j < ntiles && !dead; ++j) {
           const int g = g0 + j, b = g & 1;
           if (!tc_wait(bar(C::S_FULL + b), (uint32_t)(g >> 1) & 1u, abort_flag)) {
@@ -355,12 +357,28 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           if (j == 0 && tid == 0) FT_TL_COARSE_MARK(2);
           if (j == FT_TL_TILE && tid == 0) FT_TL_MARK(10);
           if (j == FT_TL_TILE + 1 && tid == 0) FT_TL_DETAIL_MARK(2);
+          // A warp none of whose 32 rows attends to a token of this tile has no softmax to do: in a group of short
+          // nodes (block-diagonal ranges) that is most warps in most tiles, and in a task of fewer than 128 rows the
+          // warps past its end in every tile.  Its rows of P are zero (rows past the end of the task may hold
+          // anything: no result of theirs is stored); the wait above still paces it, one arrival per tile.
+          if (!__any_sync(0xffffffffu, r_lo < min(r_hi, (j + 1) * C::TILE) && r_hi > j * C::TILE)) {
+            if (warp_has_rows) {
+              float zero[32];
+#pragma unroll
+              for (int c = 0; c < 32; ++c) zero[c] = 0.f;
+              tmem_st32(t_lane + C::S_COL + b * C::TILE, zero);
+              tmem_wait_st();
+            }
+            tc_fence_before();
+            mbar_arrive(bar(C::P_FULL + b));
+            continue;
+          }
           float s[64];
           const uint32_t s_col = t_lane + C::S_COL + b * C::TILE;
           tmem_ld32_nowait(s_col, *reinterpret_cast<float(*)[32]>(&s[0]));  // both halves in flight, one wait
           tmem_ld32_nowait(s_col + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
           tmem_wait_ld();
-          if (j == FT_TL_TILE && tid == 0) FT_TL_DETAIL_MARK(5);
+          if (j == FT_TL_TILE && tid == 0) FT_TL_SOFTMAX_MARK(5);
           // columns outside [lo, hi) are padding (last tile) or tokens this row does not attend to
           const int lo = r_lo - j * C::TILE, hi = r_hi - j * C::TILE;
           if (lo > 0 || hi < C::TILE) {
@@ -377,7 +395,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           }
           float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
           mx *= scale2;  // scale2 > 0
-          if (j == FT_TL_TILE && tid == 0) FT_TL_DETAIL_MARK(6);
+          if (j == FT_TL_TILE && tid == 0) FT_TL_SOFTMAX_MARK(6);
           float corr = 1.f;
           bool grow = false;
           if (mx > m_used + 8.f || m_used == -INFINITY) {  // the offset may lag the true maximum by up to 2^8
@@ -411,7 +429,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           }
           // Only a rescale of O has to wait for P.V of the previous tile.  (That tile's barrier phase cannot be
           // confused with an older one: S_g was committed after P.V of tile g-2, so that phase is long complete.)
-          if (j == FT_TL_TILE && tid == 0) FT_TL_MARK(11);
+          if (j == FT_TL_TILE && tid == 0) FT_TL_SOFTMAX_MARK(11);
           if (j > 0 && __any_sync(0xffffffffu, grow)) {
             if (!tc_wait(bar(C::PV_DONE + ((g - 1) & 1)), (uint32_t)((g - 1) >> 1) & 1u, abort_flag)) {
               give_up();
@@ -427,14 +445,14 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
               tmem_st32(t_lane + C::O_COL + cb * 32, o);
             }
           }
-          if (j == FT_TL_TILE && tid == 0) FT_TL_MARK(1);
+          if (j == FT_TL_TILE && tid == 0) FT_TL_SOFTMAX_MARK(1);
           // P_g takes the place of the scores just read: 64 16-bit values = the first 32 columns of S buffer b
           tmem_st32(s_col, *reinterpret_cast<float(*)[32]>(&w[0]));
           tmem_wait_st();
-          if (j == FT_TL_TILE && tid == 0) FT_TL_DETAIL_MARK(7);
+          if (j == FT_TL_TILE && tid == 0) FT_TL_SOFTMAX_MARK(7);
           tc_fence_before();  // orders this thread's tcgen05.ld/st before the hand-off
           mbar_arrive(bar(C::P_FULL + b));
-          if (j == FT_TL_TILE && tid == 0) FT_TL_MARK(4);
+          if (j == FT_TL_TILE && tid == 0) FT_TL_SOFTMAX_MARK(4);
         }
         // ---- epilogue: wait for the last P.V, normalise, write this thread's partial row
         if (!dead && ntiles > 0 &&
@@ -605,6 +623,9 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
               break;
             }
             const uint32_t buf = v_buf(g), full = bar(C::V_FULL + b);
+#ifdef FT_TL_LOADERS
+            if (t == FT_TL_TILE && lane == 0) FT_TL_MARK(7);
+#endif
             if (dense) {
               if (lane == 0) {
                 mbar_arrive_expect_tx(full, 16384);
@@ -615,24 +636,25 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
               }
             } else {
               const int c = lane & 15;
-              bool bad = false, stored = false;
+              bool bad = false;
 #pragma unroll
               for (int h = 0; h < 2; ++h) {
-#pragma unroll 4
+#pragma unroll 8
                 for (int i = 0; i < 16; ++i) {
                   const int r = (lane >> 4) + 2 * i + 32 * h, pos = t * C::TILE + r;  // row r: slot h of lane r & 31
                   const int id = __shfl_sync(0xffffffffu, cur[h], r & 31);
                   const uint32_t row = pos < id_lim ? (uint32_t)id : 0xffffffffu;
                   const bool ok = row < row_lim;  // padding (0xffffffff), negative and too-large ids all fail this test
                   bad |= !ok && pos < id_lim;
-                  stored |= !ok;
-                  cp_async16(buf + tc_swz(r, c, 8192), vbase + (int64_t)(ok ? row : 0u) * p.v_s0 + c * 8, ok);
+                  cp_async16_zfill(buf + tc_swz(r, c, 8192), vbase + (int64_t)(ok ? row : 0u) * p.v_s0 + c * 8, ok);
                 }
               }
               if (bad) flag_error(FT_DEV_BAD_KV_INDEX);
-              if (stored) proxy_fence();  // the zero rows were plain shared stores
               mbar_arrive_on_cp_async(full);
             }
+#ifdef FT_TL_LOADERS
+            if (t == FT_TL_TILE && lane == 0) FT_TL_MARK(11);
+#endif
             cur[0] = nxt[0];
             cur[1] = nxt[1];
           }
@@ -663,18 +685,16 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           }
           const int* ids = ring + (t % C::IDX_SLOTS) * C::TILE;
           const int c = lane & 15;
-          bool bad = false, stored = false;
-#pragma unroll 4
+          bool bad = false;
+#pragma unroll 8
           for (int i = 0; i < 32; ++i) {
             const int r = (lane >> 4) + 2 * i, pos = t * C::TILE + r;
             const uint32_t row = pos < id_lim ? (uint32_t)ids[r] : 0xffffffffu;
             const bool ok = row < row_lim;  // padding (0xffffffff), negative and too-large ids all fail this test
             bad |= !ok && pos < id_lim;
-            stored |= !ok;
-            cp_async16(buf + tc_swz(r, c, 8192), base + (int64_t)(ok ? row : 0u) * stride + c * 8, ok);
+            cp_async16_zfill(buf + tc_swz(r, c, 8192), base + (int64_t)(ok ? row : 0u) * stride + c * 8, ok);
           }
           if (bad) flag_error(FT_DEV_BAD_KV_INDEX);
-          if (stored) proxy_fence();  // the zero rows were plain shared stores
           mbar_arrive_on_cp_async(full);
         };
         const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)kvh * p.k_s1;
@@ -702,7 +722,13 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
             give_up();
             break;
           }
+#ifdef FT_TL_LOADERS
+          if (s == FT_TL_TILE && lane == 0) FT_TL_MARK(5);
+#endif
           load_tile(s, k_buf(g), bar(C::K_FULL + b), &tp.k_map, kbase, p.k_s0, dense, first_row);
+#ifdef FT_TL_LOADERS
+          if (s == FT_TL_TILE && lane == 0) FT_TL_MARK(6);
+#endif
           if (s + 2 < ntiles) issue_ids(s + 2);  // into the slot of tile s-1, whose ids were last used a step ago
           cp_async_commit();
         }
@@ -718,6 +744,9 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
             const uint32_t use = (uint32_t)(g >> 1) & 1u;
             if (!tc_wait(bar(C::P_FULL + b), use, abort_flag)) return false;
             if (!tc_wait(bar(C::V_FULL + b), use, abort_flag)) return false;
+#ifdef FT_TL_LOADERS
+            if (t == FT_TL_TILE) FT_TL_MARK(4);
+#endif
             proxy_fence();
             tc_fence_after();
             const uint32_t p_tmem = tmem + C::S_COL + b * C::TILE;
@@ -744,6 +773,9 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
               break;
             }
             if (t == 0) FT_TL_COARSE_MARK(6);
+#ifdef FT_TL_LOADERS
+            if (t == FT_TL_TILE) FT_TL_MARK(1);
+#endif
             proxy_fence();
             tc_fence_after();
             const uint64_t k_desc = tc_desc(k_buf(g), 16, 1024);
