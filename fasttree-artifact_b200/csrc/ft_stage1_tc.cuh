@@ -222,6 +222,46 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
   return false;
 }
 
+// Row-by-row gather of one 64-token operand tile (scattered pool slots, the ragged last tile): 16-byte copies that
+// zero-fill invalid rows themselves, so the loop has no branch.  Kept out of line: tiles of consecutive rows - every
+// tile of the benchmark shapes - never come here, and their loaders' code stays as small as it was.
+// ids in shared memory (K loader); returns true when a row id inside the chunk was out of range
+template <typename T>
+__device__ __noinline__ bool tc_gather_tile_smem(uint32_t buf, const T* base, int64_t stride, const int* ids, int t, int id_lim,
+                                                 uint32_t row_lim, int lane) {
+  const int c = lane & 15;
+  bool bad = false;
+#pragma unroll 4
+  for (int i = 0; i < 32; ++i) {
+    const int r = (lane >> 4) + 2 * i, pos = t * TcCfg::TILE + r;
+    const uint32_t row = pos < id_lim ? (uint32_t)ids[r] : 0xffffffffu;
+    const bool ok = row < row_lim;  // padding (0xffffffff), negative and too-large ids all fail this test
+    bad |= !ok && pos < id_lim;
+    cp_async16_zfill(buf + tc_swz(r, c, 8192), base + (int64_t)(ok ? row : 0u) * stride + c * 8, ok);
+  }
+  return bad;
+}
+// ids in registers, two per lane: row r is slot r >> 5 of lane r & 31 (V loader)
+template <typename T>
+__device__ __noinline__ bool tc_gather_tile_regs(uint32_t buf, const T* base, int64_t stride, int id0, int id1, int t, int id_lim,
+                                                 uint32_t row_lim, int lane) {
+  const int c = lane & 15;
+  bool bad = false;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+#pragma unroll 4
+    for (int i = 0; i < 16; ++i) {
+      const int r = (lane >> 4) + 2 * i + 32 * h, pos = t * TcCfg::TILE + r;
+      const int id = __shfl_sync(0xffffffffu, h == 0 ? id0 : id1, r & 31);
+      const uint32_t row = pos < id_lim ? (uint32_t)id : 0xffffffffu;
+      const bool ok = row < row_lim;
+      bad |= !ok && pos < id_lim;
+      cp_async16_zfill(buf + tc_swz(r, c, 8192), base + (int64_t)(ok ? row : 0u) * stride + c * 8, ok);
+    }
+  }
+  return bad;
+}
+
 template <typename T>
 __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const int vn, const int kvh) {
   using C = TcCfg;
@@ -496,7 +536,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           __syncwarp();
           float* my_dst = store ? p.mid_o + part * p.mo_s0 + (int64_t)head * p.mo_s1 : nullptr;
           const uint32_t warp_rows = sm + (uint32_t)(warp * 32) * C::OUT_STRIDE + lane * 16;
-#pragma unroll 8
+#pragma unroll 4
           for (int i = 0; i < 32; ++i) {
             float* dst = reinterpret_cast<float*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_dst), i));
             float4 x;
@@ -635,20 +675,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
                 mbar_arrive(full);
               }
             } else {
-              const int c = lane & 15;
-              bool bad = false;
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-#pragma unroll 8
-                for (int i = 0; i < 16; ++i) {
-                  const int r = (lane >> 4) + 2 * i + 32 * h, pos = t * C::TILE + r;  // row r: slot h of lane r & 31
-                  const int id = __shfl_sync(0xffffffffu, cur[h], r & 31);
-                  const uint32_t row = pos < id_lim ? (uint32_t)id : 0xffffffffu;
-                  const bool ok = row < row_lim;  // padding (0xffffffff), negative and too-large ids all fail this test
-                  bad |= !ok && pos < id_lim;
-                  cp_async16_zfill(buf + tc_swz(r, c, 8192), vbase + (int64_t)(ok ? row : 0u) * p.v_s0 + c * 8, ok);
-                }
-              }
+              const bool bad = tc_gather_tile_regs<T>(buf, vbase, p.v_s0, cur[0], cur[1], t, id_lim, row_lim, lane);
               if (bad) flag_error(FT_DEV_BAD_KV_INDEX);
               mbar_arrive_on_cp_async(full);
             }
@@ -684,16 +711,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
             return;
           }
           const int* ids = ring + (t % C::IDX_SLOTS) * C::TILE;
-          const int c = lane & 15;
-          bool bad = false;
-#pragma unroll 8
-          for (int i = 0; i < 32; ++i) {
-            const int r = (lane >> 4) + 2 * i, pos = t * C::TILE + r;
-            const uint32_t row = pos < id_lim ? (uint32_t)ids[r] : 0xffffffffu;
-            const bool ok = row < row_lim;  // padding (0xffffffff), negative and too-large ids all fail this test
-            bad |= !ok && pos < id_lim;
-            cp_async16_zfill(buf + tc_swz(r, c, 8192), base + (int64_t)(ok ? row : 0u) * stride + c * 8, ok);
-          }
+          const bool bad = tc_gather_tile_smem<T>(buf, base, stride, ids, t, id_lim, row_lim, lane);
           if (bad) flag_error(FT_DEV_BAD_KV_INDEX);
           mbar_arrive_on_cp_async(full);
         };
