@@ -18,6 +18,7 @@
 #include <deque>
 #include <new>
 #include <numeric>
+#include <queue>
 #include <vector>
 
 #include "fasttree_b200.h"
@@ -342,6 +343,86 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
       close();
       specs.swap(kept);
       for (Spec& t : tail) specs.push_back(std::move(t));
+    }
+
+    // ---- tail split (table-building mode).  The hardware hands CTAs to slots in grid order, so a step of 2.05 or 2.6
+    // rounds ends with a round in which a fraction of the slots run whole tasks while the rest of the GPU idles.  On a
+    // simulated list schedule of the tasks in emission order (integer time: a fixed cost per task plus one unit per
+    // KV tile; a task = the CTAs of all KV heads of one chunk x request tile, which start side by side), when the
+    // makespan exceeds the perfectly packed time by more than an eighth, every plain (ungrouped) virtual node whose
+    // first task starts after time 0 and ends in the later half of that excess is cut to half its chunk length (never
+    // below min_chunk); the cut is kept if the simulated makespan drops.
+    if (direct == nullptr) {
+      const int64_t start_cost[2] = {5, 4};  // many-row / few-row task, in tile times
+      const int64_t sched_slots = std::max<int64_t>((int64_t)(m.num_sms * m.ctas_per_sm) / std::max(num_kv_heads, 1), 1);
+      struct SimTask {
+        int phase;
+        int64_t key, seq, dur;
+        size_t spec;
+      };
+      auto simulate = [&](const std::vector<int64_t>& chunk_of, std::vector<int64_t>& first_start, int64_t& total) {
+        std::vector<SimTask> tasks;
+        for (size_t si = 0; si < specs.size(); ++si) {
+          const Spec& s = specs[si];
+          const int64_t nreq = (int64_t)s.reqs.size();
+          if (nreq == 0 || s.length <= 0) continue;
+          const int64_t n_kv = ceil_div(s.length, chunk_of[si]), n_q = ceil_div(nreq, q_tile);
+          for (int64_t c = 0; c < n_kv; ++c) {
+            const int64_t c_len = std::min((c + 1) * chunk_of[si], s.length) - c * chunk_of[si];
+            for (int64_t t = 0; t < n_q; ++t) {
+              const int64_t q_len = std::min((t + 1) * (int64_t)q_tile, nreq) - t * q_tile;
+              const int phase = q_len > small_tile ? 0 : 1;
+              tasks.push_back({phase, c_len * 64 + std::min<int64_t>(q_len, 63), (int64_t)tasks.size(),
+                               start_cost[phase] + ceil_div(c_len, m.tile_tokens), si});
+            }
+          }
+        }
+        std::stable_sort(tasks.begin(), tasks.end(), [](const SimTask& a, const SimTask& b) {
+          return a.phase != b.phase ? a.phase < b.phase : a.key > b.key;
+        });
+        std::priority_queue<int64_t, std::vector<int64_t>, std::greater<int64_t>> free_at;
+        for (int64_t k = 0; k < sched_slots; ++k) free_at.push(0);
+        first_start.assign(specs.size(), -1);
+        int64_t makespan = 0;
+        total = 0;
+        for (const SimTask& t : tasks) {
+          const int64_t start = free_at.top();
+          free_at.pop();
+          free_at.push(start + t.dur);
+          if (first_start[t.spec] < 0 || start < first_start[t.spec]) first_start[t.spec] = start;
+          makespan = std::max(makespan, start + t.dur);
+          total += t.dur;
+        }
+        return makespan;
+      };
+      std::vector<int64_t> chunk_of(specs.size()), first_start;
+      for (size_t si = 0; si < specs.size(); ++si) chunk_of[si] = specs[si].chunk;
+      int64_t total = 0;
+      const int64_t makespan = simulate(chunk_of, first_start, total);
+      const int64_t bound = ceil_div(total, sched_slots);
+      if ((makespan - bound) * 8 > makespan) {
+        const int64_t late_from = makespan - (makespan - bound + 1) / 2;
+        std::vector<int64_t> trial(chunk_of);
+        bool any = false;
+        for (size_t si = 0; si < specs.size(); ++si) {
+          const Spec& s = specs[si];
+          if (!s.row_ranges.empty() || first_start[si] <= 0) continue;
+          const int64_t cur = std::min(chunk_of[si], s.length);
+          const int64_t half = ceil_div(ceil_div(cur, 2), m.tile_tokens) * m.tile_tokens;
+          const int64_t first_q = std::min<int64_t>((int64_t)s.reqs.size(), q_tile);
+          const int64_t dur = start_cost[first_q > small_tile ? 0 : 1] + ceil_div(cur, m.tile_tokens);
+          if (first_start[si] + dur > late_from && half >= m.min_chunk && half < cur) {
+            trial[si] = half;
+            any = true;
+          }
+        }
+        if (any) {
+          std::vector<int64_t> fs2;
+          int64_t total2 = 0;
+          if (simulate(trial, fs2, total2) < makespan)
+            for (size_t si = 0; si < specs.size(); ++si) specs[si].chunk = trial[si];
+        }
+      }
     }
 
     // ---- emission: chunk-major, request-tile-minor; every chunk repeats the node's request list

@@ -536,7 +536,7 @@ __device__ __forceinline__ void tc_body(const TcParams& tp, uint8_t* smem, const
           __syncwarp();
           float* my_dst = store ? p.mid_o + part * p.mo_s0 + (int64_t)head * p.mo_s1 : nullptr;
           const uint32_t warp_rows = sm + (uint32_t)(warp * 32) * C::OUT_STRIDE + lane * 16;
-#pragma unroll 4
+#pragma unroll 16
           for (int i = 0; i < 32; ++i) {
             float* dst = reinterpret_cast<float*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_dst), i));
             float4 x;

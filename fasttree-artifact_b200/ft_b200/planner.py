@@ -20,6 +20,7 @@ The emitted table family is the reference's (fasttree.py:282-296):
 ``req_to_vnode_entries/offs/lens`` (entries are partial-ROW ids),
 ``phase_node_nums/offsets``.
 """
+import heapq
 import math
 from collections import deque
 from dataclasses import dataclass, field, replace
@@ -423,6 +424,7 @@ def plan_b200(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, p
     if head_dim == 128 and m.elem_bytes == 2:      # the kernels that honour row ranges exist for this shape
         vnodes = b200_group_short_nodes(vnodes, q_tile, small_tile, m,
                                         int(math.floor(target / (2 * head_dim * m.elem_bytes))))
+    vnodes = b200_split_tail(vnodes, q_tile, small_tile, m, num_kv_heads)
     tabs = emit_tables(vnodes, batch_size, small_tile=small_tile, order_key=b200_task_order)
     params.set_q_tile_sizes([q_tile, small_tile])
     params.set_kv_tile_sizes([m.tile_tokens, m.tile_tokens])
@@ -507,6 +509,87 @@ def b200_group_short_nodes(vnodes, q_tile, small_tile, m, target_tokens, direct=
             kept.append(vn)
     close()
     return kept + tail
+
+
+TAIL_START_COST = (5, 4)   # fixed cost of a many-row / few-row task, in units of one 64-token tile's time
+TAIL_ROUNDS = 1            # a late task is halved this many times at most (measured: quarters cost more in partial rows than they gain)
+
+
+def b200_simulated_schedule(vnodes, q_tile, small_tile, m, slots):
+    """List schedule of the tasks the virtual nodes will be cut into, in emission
+    order (phase, then longest chunk first), on ``slots`` task slots - a task being
+    the CTAs of all KV heads of one (chunk, request tile), which start side by side.
+    Integer time: :data:`TAIL_START_COST` per task plus one unit per KV tile.
+    Returns (makespan, total time of all tasks, per virtual node the earliest start
+    of any of its tasks)."""
+    tasks = []
+    for vi, vn in enumerate(vnodes):
+        length = sum(e - b for b, e in vn.kv_ranges)
+        nreq = len(vn.requests)
+        if nreq == 0 or length <= 0:
+            continue
+        n_kv = -(-length // vn.kv_split)
+        n_q = -(-nreq // vn.q_tile)
+        for c in range(n_kv):
+            c_len = min((c + 1) * vn.kv_split, length) - c * vn.kv_split
+            for t in range(n_q):
+                q_len = min((t + 1) * vn.q_tile, nreq) - t * vn.q_tile
+                phase = 0 if q_len > small_tile else 1
+                tasks.append((phase, -(c_len * 64 + min(q_len, 63)), len(tasks), vi,
+                              TAIL_START_COST[phase] + -(-c_len // m.tile_tokens)))
+    tasks.sort(key=lambda t: t[:3])
+    free = [0] * max(slots, 1)
+    heapq.heapify(free)
+    first_start = [None] * len(vnodes)
+    makespan = total = 0
+    for _, _, _, vi, dur in tasks:
+        start = heapq.heappop(free)
+        heapq.heappush(free, start + dur)
+        if first_start[vi] is None or start < first_start[vi]:
+            first_start[vi] = start
+        makespan = max(makespan, start + dur)
+        total += dur
+    return makespan, total, first_start
+
+
+def b200_split_tail(vnodes, q_tile, small_tile, m, num_kv_heads):
+    """Halves the KV chunks of the virtual nodes whose tasks run in the last, partly
+    filled round of the step.  The hardware hands CTAs to slots in grid order, so a
+    step of 2.05 or 2.6 rounds ends with a round in which a fraction of the slots
+    run whole tasks while the rest of the GPU idles; tasks half as long in that
+    round end it sooner at the price of a few more partial rows (cfg2: stage 1
+    25.0 -> 23.8 us, cfg3: 36.2 -> 33.2 us).  Decided on a simulated schedule
+    (:func:`b200_simulated_schedule`): when the makespan exceeds the perfectly
+    packed time by more than an eighth, every plain (ungrouped) virtual node whose
+    first task starts after time 0 and ends in the later half of that excess is cut
+    to half its chunk length (never below ``min_chunk``); the cut is kept if the
+    simulated makespan drops."""
+    slots = max((m.num_sms * m.ctas_per_sm) // max(num_kv_heads, 1), 1)
+    for _ in range(TAIL_ROUNDS):
+        makespan, total, first_start = b200_simulated_schedule(vnodes, q_tile, small_tile, m, slots)
+        bound = -(-total // slots)
+        if (makespan - bound) * 8 <= makespan:
+            break
+        late_from = makespan - (makespan - bound + 1) // 2
+        cut = []
+        for vi, vn in enumerate(vnodes):
+            if vn.row_ranges is not None or first_start[vi] is None or first_start[vi] == 0:
+                continue
+            length = sum(e - b for b, e in vn.kv_ranges)
+            cur = min(vn.kv_split, length)
+            half = -(-(-(-cur // 2)) // m.tile_tokens) * m.tile_tokens
+            dur = TAIL_START_COST[0 if min(len(vn.requests), vn.q_tile) > small_tile else 1] + -(-cur // m.tile_tokens)
+            if first_start[vi] + dur > late_from and half >= m.min_chunk and half < cur:
+                cut.append((vi, half))
+        if not cut:
+            break
+        trial = list(vnodes)
+        for vi, half in cut:
+            trial[vi] = replace(vnodes[vi], kv_split=half)
+        if b200_simulated_schedule(trial, q_tile, small_tile, m, slots)[0] >= makespan:
+            break
+        vnodes = trial
+    return vnodes
 
 
 def _tree_arrays(tree):

@@ -192,6 +192,54 @@ def test_native_splitter_matches_on_random_trees_and_models(seed):
     check_plan_covers_every_path_once(tree, ptrs, batch, native)
 
 
+@pytest.mark.parametrize("name", ["cfg2", "cfg3"])
+def test_last_round_of_the_schedule_is_halved(name):
+    """planner.b200_split_tail: the benchmark trees whose CTAs fill 2.05 / 1.3 rounds of the GPU get the chunks of their
+    last round halved (simulated makespan 24 -> 22 and 34 -> 30 tile times), identically in the native splitter."""
+    sizes, lens, makespans, halved = {"cfg2": ([1, 64], [4096, 256], (24, 22), 14),
+                                      "cfg3": ([1, 16, 256], [2048, 512, 64], (34, 30), 6)}[name]
+    tree, batch, ptrs = product_tree(ref_inputs.layered_tree(sizes, lens))
+    p = make_params(32, 8, [16, 4], planner_name="b200")
+    m = planner.b200_model_for(p, 128)
+    vnodes, _, q_tile, small_tile, target = planner.b200_virtual_nodes(
+        tree, 32, 8, 128, m, lambda a, i: planner._chain_ranges(tree, ptrs, a, i))
+    vnodes = planner.b200_group_short_nodes(vnodes, q_tile, small_tile, m, int(target // (2 * 128 * m.elem_bytes)))
+    slots = 2 * 148 // 8
+    before = planner.b200_simulated_schedule(vnodes, q_tile, small_tile, m, slots)
+    cut = planner.b200_split_tail(vnodes, q_tile, small_tile, m, 8)
+    after = planner.b200_simulated_schedule(cut, q_tile, small_tile, m, slots)
+    assert (before[0], after[0]) == makespans
+    changed = [(a.kv_split, b.kv_split) for a, b in zip(vnodes, cut) if a.kv_split != b.kv_split]
+    assert len(changed) == halved and all(new * 2 == old for old, new in changed)
+    assert all(a.row_ranges is None for a, b in zip(vnodes, cut) if a.kv_split != b.kv_split)   # groups stay whole
+    pa, pb = make_params(32, 8, [16, 4], planner_name="b200"), make_params(32, 8, [16, 4], planner_name="b200")
+    spec = planner.plan_b200(tree, ptrs, batch, 32, 8, 128, pa)
+    native = planner.plan_b200_native(tree, ptrs, batch, 32, 8, 128, pb)
+    _same_plan(spec, native)
+    check_plan_covers_every_path_once(tree, ptrs, batch, native)
+    # a GPU with room for every task at once has no last round to shorten
+    from dataclasses import replace
+    roomy = replace(m, num_sms=4 * 148)
+    assert [v.kv_split for v in planner.b200_split_tail(vnodes, q_tile, small_tile, roomy, 8)] == [v.kv_split for v in vnodes]
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_native_splitter_matches_on_small_gpus(seed):
+    """Few task slots put most random trees into several rounds, which is where the last-round pass acts."""
+    from dataclasses import replace
+    rng = np.random.default_rng(100 + seed)
+    tree, batch, ptrs = product_tree(ref_inputs.random_tree(3 + seed % 3, 100 + seed, max_children=5 + 2 * seed, lam=3.0,
+                                                            len_lo=1, len_hi=int(rng.choice([300, 2048]))))
+    hq, hkv = [(32, 8), (8, 8), (16, 1)][seed % 3]
+    model = replace(planner.B200Model(), num_sms=int(rng.choice([2, 4, 16])), rows_per_cta=128,
+                    group_member_tokens=int(rng.choice([0, 128])))
+    pa, pb = make_params(hq, hkv, [16, 4], planner_name="b200"), make_params(hq, hkv, [16, 4], planner_name="b200")
+    spec = planner.plan_b200(tree, ptrs, batch, hq, hkv, 128, pa, model=model)
+    native = planner.plan_b200_native(tree, ptrs, batch, hq, hkv, 128, pb, model=model)
+    _same_plan(spec, native)
+    check_plan_covers_every_path_once(tree, ptrs, batch, native)
+
+
 def test_native_splitter_rejects_bad_trees():
     from ft_b200 import lib
     tree, batch, ptrs = product_tree(ref_inputs.layered_tree([1, 2], [5, 5]))
@@ -223,7 +271,9 @@ def test_b200_plan_splits_long_prefix_and_keeps_leaves_whole():
     p = make_params(32, 8, [16, 4], planner_name="b200")
     plan = fasttree.build_plan(tree, ptrs, batch, 32, 8, 128, [1024, 128], [132, 528], [132, 132], p)
     lens = plan.vnode_to_kv_lens
-    assert (lens[plan.vnode_to_q_lens == 1] == 256).all()          # leaves: one task each
+    leaf = lens[plan.vnode_to_q_lens == 1]
+    # leaves: one task each, except the 14 whose CTAs would form the step's last, partly filled round - those are halved
+    assert (leaf == 256).sum() == 50 and (leaf == 128).sum() == 28 and leaf.size == 78
     assert lens.max() < 4096 and lens.max() % 64 == 0              # the shared prefix is cut on tile boundaries
     # long tasks first inside each phase
     n0 = plan.phase_node_nums[0]
@@ -318,14 +368,16 @@ def test_groups_of_short_nodes(name, native):
     if not expect:
         return
     assert plan.vnode_q_kv_ranges.shape == (plan.num_partial_rows, 2) and plan.vnode_q_kv_ranges.dtype == np.int32
-    # the same tree with grouping switched off has more tasks and the same partial rows
+    # the same tree with grouping switched off has more tasks (partial rows: equal up to the chunks either plan halves
+    # in its last round, planner.b200_split_tail)
     q = make_params(hq, hkv, [16, 4], planner_name="b200")
     q.native_planner = native
     from dataclasses import replace
     q.b200_model = replace(planner.b200_model_for(q, 128), group_member_tokens=0)
     flat = fasttree.build_plan(tree, ptrs, batch, hq, hkv, 128, [1024, 128], [132, 528], [132, 132], q)
     assert flat.vnode_q_kv_ranges is None
-    assert flat.num_vnodes > plan.num_vnodes and flat.num_partial_rows == plan.num_partial_rows
+    assert flat.num_vnodes > plan.num_vnodes
+    check_plan_covers_every_path_once(tree, ptrs, batch, flat)
     if sum(s * l for s, l in zip(sizes, lens)) > 20000:
         return                                     # the arithmetic check below is for the small trees
     qq, k, v, _, _ = ref_inputs.draw_qkv(onodes, hq, hkv, 128, torch.float32, 5, 0.5)
