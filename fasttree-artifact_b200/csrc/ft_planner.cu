@@ -349,9 +349,9 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
     // rounds ends with a round in which a fraction of the slots run whole tasks while the rest of the GPU idles.  On a
     // simulated list schedule of the tasks in emission order (integer time: a fixed cost per task plus one unit per
     // KV tile; a task = the CTAs of all KV heads of one chunk x request tile, which start side by side), when the
-    // makespan exceeds the perfectly packed time by more than an eighth, every plain (ungrouped) virtual node whose
-    // first task starts after time 0 and ends in the later half of that excess is cut to half its chunk length (never
-    // below min_chunk); the cut is kept if the simulated makespan drops.
+    // makespan exceeds the perfectly packed time by more than an eighth, every plain (ungrouped) virtual node with a
+    // task that ends in the later half of that excess is cut to half its chunk length (never below min_chunk); the
+    // cut is kept if the simulated makespan drops.  (A step of one round lasts as long as its longest task: same cut.)
     if (direct == nullptr) {
       const int64_t start_cost[2] = {5, 4};  // many-row / few-row task, in tile times
       const int64_t sched_slots = std::max<int64_t>((int64_t)(m.num_sms * m.ctas_per_sm) / std::max(num_kv_heads, 1), 1);
@@ -360,7 +360,7 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
         int64_t key, seq, dur;
         size_t spec;
       };
-      auto simulate = [&](const std::vector<int64_t>& chunk_of, std::vector<int64_t>& first_start, int64_t& total) {
+      auto simulate = [&](const std::vector<int64_t>& chunk_of, std::vector<int64_t>& last_end, int64_t& total) {
         std::vector<SimTask> tasks;
         for (size_t si = 0; si < specs.size(); ++si) {
           const Spec& s = specs[si];
@@ -382,23 +382,23 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
         });
         std::priority_queue<int64_t, std::vector<int64_t>, std::greater<int64_t>> free_at;
         for (int64_t k = 0; k < sched_slots; ++k) free_at.push(0);
-        first_start.assign(specs.size(), -1);
+        last_end.assign(specs.size(), 0);
         int64_t makespan = 0;
         total = 0;
         for (const SimTask& t : tasks) {
           const int64_t start = free_at.top();
           free_at.pop();
           free_at.push(start + t.dur);
-          if (first_start[t.spec] < 0 || start < first_start[t.spec]) first_start[t.spec] = start;
+          last_end[t.spec] = std::max(last_end[t.spec], start + t.dur);
           makespan = std::max(makespan, start + t.dur);
           total += t.dur;
         }
         return makespan;
       };
-      std::vector<int64_t> chunk_of(specs.size()), first_start;
+      std::vector<int64_t> chunk_of(specs.size()), last_end;
       for (size_t si = 0; si < specs.size(); ++si) chunk_of[si] = specs[si].chunk;
       int64_t total = 0;
-      const int64_t makespan = simulate(chunk_of, first_start, total);
+      const int64_t makespan = simulate(chunk_of, last_end, total);
       const int64_t bound = ceil_div(total, sched_slots);
       if ((makespan - bound) * 8 > makespan) {
         const int64_t late_from = makespan - (makespan - bound + 1) / 2;
@@ -406,12 +406,10 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
         bool any = false;
         for (size_t si = 0; si < specs.size(); ++si) {
           const Spec& s = specs[si];
-          if (!s.row_ranges.empty() || first_start[si] <= 0) continue;
+          if (!s.row_ranges.empty() || last_end[si] <= late_from) continue;
           const int64_t cur = std::min(chunk_of[si], s.length);
           const int64_t half = ceil_div(ceil_div(cur, 2), m.tile_tokens) * m.tile_tokens;
-          const int64_t first_q = std::min<int64_t>((int64_t)s.reqs.size(), q_tile);
-          const int64_t dur = start_cost[first_q > small_tile ? 0 : 1] + ceil_div(cur, m.tile_tokens);
-          if (first_start[si] + dur > late_from && half >= m.min_chunk && half < cur) {
+          if (half >= m.min_chunk && half < cur) {
             trial[si] = half;
             any = true;
           }

@@ -520,8 +520,8 @@ def b200_simulated_schedule(vnodes, q_tile, small_tile, m, slots):
     order (phase, then longest chunk first), on ``slots`` task slots - a task being
     the CTAs of all KV heads of one (chunk, request tile), which start side by side.
     Integer time: :data:`TAIL_START_COST` per task plus one unit per KV tile.
-    Returns (makespan, total time of all tasks, per virtual node the earliest start
-    of any of its tasks)."""
+    Returns (makespan, total time of all tasks, per virtual node the time its last
+    task ends)."""
     tasks = []
     for vi, vn in enumerate(vnodes):
         length = sum(e - b for b, e in vn.kv_ranges)
@@ -540,53 +540,46 @@ def b200_simulated_schedule(vnodes, q_tile, small_tile, m, slots):
     tasks.sort(key=lambda t: t[:3])
     free = [0] * max(slots, 1)
     heapq.heapify(free)
-    first_start = [None] * len(vnodes)
+    last_end = [0] * len(vnodes)
     makespan = total = 0
     for _, _, _, vi, dur in tasks:
         start = heapq.heappop(free)
         heapq.heappush(free, start + dur)
-        if first_start[vi] is None or start < first_start[vi]:
-            first_start[vi] = start
+        last_end[vi] = max(last_end[vi], start + dur)
         makespan = max(makespan, start + dur)
         total += dur
-    return makespan, total, first_start
+    return makespan, total, last_end
 
 
 def b200_split_tail(vnodes, q_tile, small_tile, m, num_kv_heads):
-    """Halves the KV chunks of the virtual nodes whose tasks run in the last, partly
-    filled round of the step.  The hardware hands CTAs to slots in grid order, so a
-    step of 2.05 or 2.6 rounds ends with a round in which a fraction of the slots
-    run whole tasks while the rest of the GPU idles; tasks half as long in that
-    round end it sooner at the price of a few more partial rows (cfg2: stage 1
-    25.0 -> 23.8 us, cfg3: 36.2 -> 33.2 us).  Decided on a simulated schedule
-    (:func:`b200_simulated_schedule`): when the makespan exceeds the perfectly
-    packed time by more than an eighth, every plain (ungrouped) virtual node whose
-    first task starts after time 0 and ends in the later half of that excess is cut
-    to half its chunk length (never below ``min_chunk``); the cut is kept if the
-    simulated makespan drops."""
+    """Halves the KV chunks of the virtual nodes whose tasks end the step.  The
+    hardware hands CTAs to slots in grid order, so a step of 2.05 or 2.6 rounds
+    ends with a round in which a fraction of the slots run whole tasks while the
+    rest of the GPU idles, and a step of one round lasts as long as its longest
+    task; tasks half as long end it sooner at the price of a few more partial rows
+    (cfg2: stage 1 25.0 -> 23.8 us, cfg3: 36.2 -> 33.7 us).  Decided on a simulated
+    schedule (:func:`b200_simulated_schedule`): when the makespan exceeds the
+    perfectly packed time by more than an eighth, every plain (ungrouped) virtual
+    node with a task that ends in the later half of that excess is cut to half its
+    chunk length (never below ``min_chunk``); the cut is kept if the simulated
+    makespan drops."""
     slots = max((m.num_sms * m.ctas_per_sm) // max(num_kv_heads, 1), 1)
     for _ in range(TAIL_ROUNDS):
-        makespan, total, first_start = b200_simulated_schedule(vnodes, q_tile, small_tile, m, slots)
+        makespan, total, last_end = b200_simulated_schedule(vnodes, q_tile, small_tile, m, slots)
         bound = -(-total // slots)
         if (makespan - bound) * 8 <= makespan:
             break
         late_from = makespan - (makespan - bound + 1) // 2
-        cut = []
+        trial, any_cut = list(vnodes), False
         for vi, vn in enumerate(vnodes):
-            if vn.row_ranges is not None or first_start[vi] is None or first_start[vi] == 0:
+            if vn.row_ranges is not None or last_end[vi] <= late_from:
                 continue
-            length = sum(e - b for b, e in vn.kv_ranges)
-            cur = min(vn.kv_split, length)
+            cur = min(vn.kv_split, sum(e - b for b, e in vn.kv_ranges))
             half = -(-(-(-cur // 2)) // m.tile_tokens) * m.tile_tokens
-            dur = TAIL_START_COST[0 if min(len(vn.requests), vn.q_tile) > small_tile else 1] + -(-cur // m.tile_tokens)
-            if first_start[vi] + dur > late_from and half >= m.min_chunk and half < cur:
-                cut.append((vi, half))
-        if not cut:
-            break
-        trial = list(vnodes)
-        for vi, half in cut:
-            trial[vi] = replace(vnodes[vi], kv_split=half)
-        if b200_simulated_schedule(trial, q_tile, small_tile, m, slots)[0] >= makespan:
+            if half >= m.min_chunk and half < cur:
+                trial[vi] = replace(vn, kv_split=half)
+                any_cut = True
+        if not any_cut or b200_simulated_schedule(trial, q_tile, small_tile, m, slots)[0] >= makespan:
             break
         vnodes = trial
     return vnodes
