@@ -294,6 +294,21 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
         hard_cap = 24 * tile;
         cap = std::min(std::max(ceil_div(ceil_div(cand_tokens, free_tasks), tile) * tile, 4 * tile), hard_cap);
       }
+      else {
+        // One round: when the tasks at the default cap would spill a little past one round of resident CTAs while
+        // longer groups keep everything inside it, the cap grows to what fills the round exactly.
+        int64_t cand_tokens = 0, other = 0;
+        for (const Spec& s : specs) {
+          const int64_t nreq = (int64_t)s.reqs.size();
+          if (nreq <= small_tile && s.length <= m.group_member_tokens) cand_tokens += s.length;
+          else other += ceil_div(s.length, s.chunk) * ceil_div(nreq, q_tile);
+        }
+        const int64_t round = std::max<int64_t>((int64_t)(m.num_sms * m.ctas_per_sm) / std::max(num_kv_heads, 1), 1);
+        if (other < round && other + ceil_div(cand_tokens, cap) > round) {
+          const int64_t fill = ceil_div(ceil_div(cand_tokens, round - other), tile) * tile;
+          if (fill <= hard_cap) cap = std::max(cap, fill);
+        }
+      }
       std::vector<Spec> kept, tail;
       std::vector<Spec> cur;
       std::vector<uint8_t> in_group((size_t)std::max(batch, 1), 0);

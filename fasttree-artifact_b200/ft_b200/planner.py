@@ -423,7 +423,7 @@ def plan_b200(tree, kv_ptrs, batch_size, num_qo_heads, num_kv_heads, head_dim, p
         tree, num_qo_heads, num_kv_heads, head_dim, m, lambda a, i: _chain_ranges(tree, kv_ptrs, a, i))
     if head_dim == 128 and m.elem_bytes == 2:      # the kernels that honour row ranges exist for this shape
         vnodes = b200_group_short_nodes(vnodes, q_tile, small_tile, m,
-                                        int(math.floor(target / (2 * head_dim * m.elem_bytes))))
+                                        int(math.floor(target / (2 * head_dim * m.elem_bytes))), num_kv_heads=num_kv_heads)
     vnodes = b200_split_tail(vnodes, q_tile, small_tile, m, num_kv_heads)
     tabs = emit_tables(vnodes, batch_size, small_tile=small_tile, order_key=b200_task_order)
     params.set_q_tile_sizes([q_tile, small_tile])
@@ -471,6 +471,22 @@ def b200_group_short_nodes(vnodes, q_tile, small_tile, m, target_tokens, direct=
         free_tasks = 2 * max(round_ - other, round_ // 4, 1)
         hard_cap = GROUP_MAX_TILES_DIRECT * tile
         cap = min(max(-(-(-(-cand_tokens // free_tasks)) // tile) * tile, 4 * tile), hard_cap)
+    else:
+        # One round: when the tasks at the default cap would spill a little past one round of resident CTAs while
+        # longer groups keep everything inside it, the cap grows to what fills the round exactly (cfg3 on a 4-head
+        # shard: 32 + 16 other tasks and 32 groups of 8 leaves are 80 tasks on 74 slots; 26 groups of 10 fit).
+        cand_tokens = other = 0
+        for vn in vnodes:
+            length = sum(e - b for b, e in vn.kv_ranges)
+            if len(vn.requests) <= small_tile and length <= m.group_member_tokens:
+                cand_tokens += length
+            else:
+                other += -(-length // vn.kv_split) * -(-len(vn.requests) // vn.q_tile)
+        round_ = max((m.num_sms * m.ctas_per_sm) // max(num_kv_heads, 1), 1)
+        if other < round_ and other + -(-cand_tokens // cap) > round_:
+            fill = -(-(-(-cand_tokens // (round_ - other))) // tile) * tile
+            if fill <= hard_cap:
+                cap = max(cap, fill)
     kept, tail = [], []
     cur, cur_reqs, cur_tokens, cur_n = [], set(), 0, 0
 
