@@ -543,10 +543,15 @@ int launch_stage2(const ft::Stage2Params& p, cudaStream_t st, bool after_stage1)
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = after_stage1 ? 1 : 0;
-  if (p.head_dim <= 128)
-    FT_CUDA_OK(cudaLaunchKernelEx(&cfg, ft::stage2_merge_kernel<T, 1>, p));
+  int dev = 0;
+  FT_CUDA_OK(cudaGetDevice(&dev));
+  const bool one_round = blocks <= 6LL * sm_count(dev);  // latency-bound: more rows in flight per lane
+  if (p.head_dim > 128)
+    FT_CUDA_OK(cudaLaunchKernelEx(&cfg, ft::stage2_merge_kernel<T, 2, 4>, p));
+  else if (one_round)
+    FT_CUDA_OK(cudaLaunchKernelEx(&cfg, ft::stage2_merge_kernel<T, 1, 8>, p));
   else
-    FT_CUDA_OK(cudaLaunchKernelEx(&cfg, ft::stage2_merge_kernel<T, 2>, p));
+    FT_CUDA_OK(cudaLaunchKernelEx(&cfg, ft::stage2_merge_kernel<T, 1, 4>, p));
   count_launch();
   return FT_OK;
 }

@@ -13,10 +13,13 @@
 
 namespace ft {
 
-// MAXC: float4 chunks per lane (1: head_dim <= 128, 2: head_dim <= 256); the narrower variant needs half the
-// registers for the rows in flight, which is what bounds the warps per SM here.
-template <typename T, int MAXC>
-__global__ void __launch_bounds__(128, MAXC == 1 ? 9 : 6) stage2_merge_kernel(Stage2Params p) {
+// MAXC: float4 chunks per lane (1: head_dim <= 128, 2: head_dim <= 256).  RB: partial rows in flight per lane.  A
+// request's merge is a chain of L2 round trips, one per batch of RB rows.  A launch that fits one round of CTAs is
+// bound by that chain (a head-sharded plan - one KV head per GPU, 128-token chunks - hands a request 30 and more
+// partial rows), so it runs with RB = 8 at six CTAs per SM; a launch of several rounds (cfg4: 65 536 request-head
+// pairs) is bound by how many warps the SM holds and runs with RB = 4 at nine (head_dim <= 128).
+template <typename T, int MAXC, int RB>
+__global__ void __launch_bounds__(128, (MAXC == 1 && RB == 4) ? 9 : 6) stage2_merge_kernel(Stage2Params p) {
   allow_dependent_launch();  // a following stage-1 launch may set itself up under this kernel's tail
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t pair = (int64_t)blockIdx.x * 4 + warp;
@@ -32,7 +35,6 @@ __global__ void __launch_bounds__(128, MAXC == 1 ? 9 : 6) stage2_merge_kernel(St
   // One pass with a running maximum (as in the online softmax): per batch of up to 32 partial rows the lanes
   // fetch their row's LSE while the first rows of the batch are already being loaded - the row addresses depend
   // on the plan only - so a request with few partials costs one round trip to the partial buffers, not two.
-  constexpr int RB = 4;  // partial rows in flight per lane
   float mx = -INFINITY;
   float4 acc[MAXC];
 #pragma unroll
