@@ -548,6 +548,8 @@ int launch_stage2(const ft::Stage2Params& p, cudaStream_t st, bool after_stage1)
   const bool one_round = blocks <= 6LL * sm_count(dev);  // latency-bound: more rows in flight per lane
   if (p.head_dim > 128)
     FT_CUDA_OK(cudaLaunchKernelEx(&cfg, ft::stage2_merge_kernel<T, 2, 4>, p));
+  else if (blocks <= 2LL * sm_count(dev))
+    FT_CUDA_OK(cudaLaunchKernelEx(&cfg, ft::stage2_merge_kernel<T, 1, 16>, p));
   else if (one_round)
     FT_CUDA_OK(cudaLaunchKernelEx(&cfg, ft::stage2_merge_kernel<T, 1, 8>, p));
   else

@@ -16,10 +16,11 @@ namespace ft {
 // MAXC: float4 chunks per lane (1: head_dim <= 128, 2: head_dim <= 256).  RB: partial rows in flight per lane.  A
 // request's merge is a chain of L2 round trips, one per batch of RB rows.  A launch that fits one round of CTAs is
 // bound by that chain (a head-sharded plan - one KV head per GPU, 128-token chunks - hands a request 30 and more
-// partial rows), so it runs with RB = 8 at six CTAs per SM; a launch of several rounds (cfg4: 65 536 request-head
-// pairs) is bound by how many warps the SM holds and runs with RB = 4 at nine (head_dim <= 128).
+// partial rows), so it runs with RB = 8 at six CTAs per SM - RB = 16 at four when it does not even fill two CTAs per
+// SM, which is the sharded case; a launch of several rounds (cfg4: 65 536 request-head pairs) is bound by how many
+// warps the SM holds and runs with RB = 4 at nine (head_dim <= 128).
 template <typename T, int MAXC, int RB>
-__global__ void __launch_bounds__(128, (MAXC == 1 && RB == 4) ? 9 : 6) stage2_merge_kernel(Stage2Params p) {
+__global__ void __launch_bounds__(128, RB >= 16 ? 4 : ((MAXC == 1 && RB == 4) ? 9 : 6)) stage2_merge_kernel(Stage2Params p) {
   allow_dependent_launch();  // a following stage-1 launch may set itself up under this kernel's tail
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t pair = (int64_t)blockIdx.x * 4 + warp;
@@ -29,7 +30,7 @@ __global__ void __launch_bounds__(128, (MAXC == 1 && RB == 4) ? 9 : 6) stage2_me
   const int off = p.r2v_offs[req];
   const int n = p.r2v_lens[req];
   const int chunks = p.head_dim >> 2;
-  int first_rows = lane < n ? p.r2v_entries[off + lane] : -1;  // plan data: readable before stage 1 is done
+  int batch_rows = lane < n ? p.r2v_entries[off + lane] : -1;  // plan data: readable before stage 1 is done
   wait_for_prior_grid();                                       // the partial buffers are complete from here on
 
   // One pass with a running maximum (as in the online softmax): per batch of up to 32 partial rows the lanes
@@ -43,8 +44,9 @@ __global__ void __launch_bounds__(128, (MAXC == 1 && RB == 4) ? 9 : 6) stage2_me
   for (int base = 0; base < n; base += 32) {
     const int cnt = min(32, n - base);
     int my_row = -1;
+    const int row = batch_rows;
+    batch_rows = base + 32 + lane < n ? p.r2v_entries[off + base + 32 + lane] : -1;  // the next batch's ids travel under this batch's rows
     if (lane < cnt) {
-      const int row = base == 0 ? first_rows : p.r2v_entries[off + base + lane];
       if (row >= 0 && row < p.num_partial_rows)
         my_row = row;
       else
