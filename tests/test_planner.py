@@ -224,6 +224,23 @@ def test_last_round_of_the_schedule_is_halved(name):
     assert all(a.kv_split == b.kv_split for a, b in zip(vnodes, roomy) if a.kv_split < longest)
 
 
+def test_groups_grow_to_keep_the_step_in_one_round():
+    """cfg3 on a 4-KV-head shard: at the default token target the step is 32 + 16 plain tasks and 32 groups of 8 leaves,
+    80 tasks on 74 slots; the target grows so that 26 groups of 10 leaves fill the round exactly."""
+    tree, batch, ptrs = product_tree(ref_inputs.layered_tree([1, 16, 256], [2048, 512, 64]))
+    plans = []
+    for native in (False, True):
+        p = make_params(16, 4, [16, 4], planner_name="b200")
+        p.native_planner = native
+        plans.append(fasttree.build_plan(tree, ptrs, batch, 16, 4, 128, [1024, 128], [132, 528], [132, 132], p))
+    _same_plan(*plans)
+    plan = plans[0]
+    check_plan_covers_every_path_once(tree, ptrs, batch, plan)
+    assert plan.num_vnodes == 2 * 148 // 4
+    group = plan.vnode_to_q_lens == 10                        # ten single-request leaves, 64 tokens each
+    assert group.sum() == 25 and (plan.vnode_to_kv_lens[group] == 640).all()
+
+
 @pytest.mark.parametrize("seed", range(6))
 def test_native_splitter_matches_on_small_gpus(seed):
     """Few task slots put most random trees into several rounds, which is where the last-round pass acts."""
