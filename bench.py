@@ -571,8 +571,9 @@ class Problem:
         return {"value": dev_ms / n_e2e * 1e3, "unit": "us/step",
                 "h2d_bytes_per_step": q_host.numel() * self.esize, "d2h_bytes_per_step": o_host.numel() * self.esize,
                 "steps": n_e2e, "wall_us_per_step": wall_ms / n_e2e * 1e3,
-                "call": "fasttree_decode_host_io(...): ft_decode_host_io = cudaMemcpyAsync in, stage 1 + 2, "
-                        "cudaMemcpyAsync out, stream synchronise"}
+                "call": "fasttree_decode_host_io(...): ft_decode_host_io = query fetched from pinned (mapped) host "
+                        "memory by a copy kernel, stage 1, stage 2 writing the output rows into pinned host memory, "
+                        "stream synchronise - one C-ABI call per step"}
 
     def release(self):
         self.ks = self.vs = None
