@@ -279,10 +279,9 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
       int64_t hard_cap = 16 * tile;
       int64_t cap = std::min(std::max(target_tokens / tile * tile, 4 * tile), hard_cap);
       if (direct != nullptr) {
-        // Serving path: the groups are sized to fill twice what the other tasks leave of one round of resident CTAs
-        // (measured: their tiles are gathered row by row, and two shorter groups per slot hide that latency better
-        // than one long one; the average-based target above overshoots when the shared nodes' tasks are short), up
-        // to 24 tiles.
+        // Serving path: the groups are sized so that the step fills two rounds of resident CTAs, the other tasks
+        // included (measured: their tiles are gathered row by row, and two shorter groups per slot hide that latency
+        // better than one long one, while a third round costs more than it hides), up to 24 tiles.
         int64_t cand_tokens = 0, other = 0;
         for (const Spec& s : specs) {
           const int64_t nreq = (int64_t)s.reqs.size();
@@ -290,7 +289,7 @@ int build_plan(const int32_t* parent, const int32_t* seqlen, int32_t n_nodes, co
           else other += ceil_div(s.length, s.chunk) * ceil_div(nreq, q_tile);
         }
         const int64_t round = std::max<int64_t>((int64_t)slots / std::max(num_kv_heads, 1), 1);
-        const int64_t free_tasks = 2 * std::max<int64_t>(std::max(round - other, round / 4), 1);
+        const int64_t free_tasks = std::max<int64_t>(std::max(2 * round - other, round / 2), 2);
         hard_cap = 24 * tile;
         cap = std::min(std::max(ceil_div(ceil_div(cand_tokens, free_tasks), tile) * tile, 4 * tile), hard_cap);
       }

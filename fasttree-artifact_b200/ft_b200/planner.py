@@ -457,9 +457,10 @@ def b200_group_short_nodes(vnodes, q_tile, small_tile, m, target_tokens, direct=
     hard_cap = GROUP_MAX_TILES * tile
     cap = min(max(target_tokens // tile * tile, 4 * tile), hard_cap)
     if direct:
-        # serving path: the groups are sized to fill twice what the other tasks leave of one round of resident CTAs
-        # (measured: their tiles are gathered row by row, and two shorter groups per slot hide that latency better
-        # than one long one; the average-based target overshoots when the shared nodes' tasks are short), up to 24 tiles
+        # serving path: the groups are sized so that the step fills two rounds of resident CTAs, the other tasks
+        # included (measured on the 512-request burst, 16 other tasks on 37 slots: 36 / 53 / 73 / 80 / 120 tasks run
+        # 69.7 / 61.9 / 55.7 / 68.5 / 76.1 us - their tiles are gathered row by row, and two shorter groups per slot
+        # hide that latency better than one long one, while a third round costs more than it hides), up to 24 tiles
         cand_tokens = other = 0
         for vn in vnodes:
             length = sum(e - b for b, e in vn.kv_ranges)
@@ -468,7 +469,7 @@ def b200_group_short_nodes(vnodes, q_tile, small_tile, m, target_tokens, direct=
             else:
                 other += -(-length // vn.kv_split) * -(-len(vn.requests) // vn.q_tile)
         round_ = max(int(m.num_sms * m.ctas_per_sm * m.waves) // max(num_kv_heads, 1), 1)
-        free_tasks = 2 * max(round_ - other, round_ // 4, 1)
+        free_tasks = max(2 * round_ - other, round_ // 2, 2)
         hard_cap = GROUP_MAX_TILES_DIRECT * tile
         cap = min(max(-(-(-(-cand_tokens // free_tasks)) // tile) * tile, 4 * tile), hard_cap)
     else:
