@@ -258,6 +258,42 @@ def test_native_splitter_matches_on_small_gpus(seed):
     check_plan_covers_every_path_once(tree, ptrs, batch, native)
 
 
+@pytest.mark.parametrize("block", range(4))
+def test_native_splitter_matches_on_many_shapes(block):
+    """Sweep of tree depths, fan-outs, node lengths, head counts and slot counts (ten trees per block): the two
+    splitters agree table for table, every plan covers every path once, and the schedule-aware passes act on some."""
+    from dataclasses import replace
+    acted = 0
+    for seed in range(1000 + 10 * block, 1010 + 10 * block):
+        rng = np.random.default_rng(seed)
+        tree, batch, ptrs = product_tree(ref_inputs.random_tree(
+            int(rng.integers(2, 6)), seed, max_children=int(rng.integers(3, 20)), lam=float(rng.uniform(1.5, 6)),
+            len_lo=1, len_hi=int(rng.choice([40, 300, 2048]))))
+        hq, hkv = [(32, 8), (8, 8), (16, 1), (64, 8), (4, 1)][seed % 5]
+        model = replace(planner.B200Model(), num_sms=int(rng.choice([4, 16, 148])), waves=float(rng.choice([0.5, 1.0, 2.0])),
+                        min_chunk=int(rng.choice([64, 128])), rows_per_cta=int(rng.choice([64, 128])),
+                        group_member_tokens=int(rng.choice([0, 128])))
+        pa, pb = make_params(hq, hkv, [16, 4], planner_name="b200"), make_params(hq, hkv, [16, 4], planner_name="b200")
+        spec = planner.plan_b200(tree, ptrs, batch, hq, hkv, 128, pa, model=model)
+        native = planner.plan_b200_native(tree, ptrs, batch, hq, hkv, 128, pb, model=model)
+        _same_plan(spec, native)
+        check_plan_covers_every_path_once(tree, ptrs, batch, native)
+        m = planner.b200_model_for(pa, 128, model)
+        vnodes, _, q_tile, small_tile, target = planner.b200_virtual_nodes(
+            tree, hq, hkv, 128, m, lambda a, i: planner._chain_ranges(tree, ptrs, a, i))
+        if m.elem_bytes == 2:
+            vnodes = planner.b200_group_short_nodes(vnodes, q_tile, small_tile, m, int(target // (2 * 128 * m.elem_bytes)),
+                                                    num_kv_heads=hkv)
+        cut = planner.b200_split_tail(vnodes, q_tile, small_tile, m, hkv)
+        slots = max(m.num_sms * m.ctas_per_sm // hkv, 1)
+        before = planner.b200_simulated_schedule(vnodes, q_tile, small_tile, m, slots)[0]
+        after = planner.b200_simulated_schedule(cut, q_tile, small_tile, m, slots)[0]
+        changed = any(a.kv_split != b.kv_split for a, b in zip(vnodes, cut))
+        assert after < before if changed else after == before      # a cut is kept only if the makespan drops
+        acted += changed
+    assert acted >= 1                                              # these seeds include plans the last-round pass cuts
+
+
 def test_native_splitter_rejects_bad_trees():
     from ft_b200 import lib
     tree, batch, ptrs = product_tree(ref_inputs.layered_tree([1, 2], [5, 5]))
